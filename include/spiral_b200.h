@@ -1,0 +1,128 @@
+/* libspiral_b200 -- C ABI of the B200 (sm_100a) dense-matmul / policy-MLP path.
+ *
+ * Every entry point takes plain device pointers and sizes, writes its results
+ * in place into caller-owned memory and returns an int status (SB_OK or a
+ * negative sb_status code; sb_last_error_string() holds the text).  Launches
+ * are asynchronous on the given stream (NULL = the legacy default stream).
+ * Unless a comment says otherwise no entry point allocates device memory.
+ *
+ * Each declaration cites the reference interface (file:line inside
+ * mrakgr/Spiral-s-ML-Library) that it replaces.
+ */
+#ifndef SPIRAL_B200_H
+#define SPIRAL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum sb_status {
+  SB_OK = 0,
+  SB_ERR_BAD_ARG = -1,       /* null pointer, negative size, unknown enum */
+  SB_ERR_MISALIGNED = -2,    /* base or leading dimension not 16-byte aligned */
+  SB_ERR_UNSUPPORTED = -3,   /* dtype / layout / epilogue combination not built */
+  SB_ERR_CUDA = -4,          /* a CUDA runtime or driver call failed */
+  SB_ERR_DEVICE_TIMEOUT = -5,/* a bounded device-side wait expired */
+  SB_ERR_TOO_LARGE = -6,     /* size beyond a documented fixed limit */
+  SB_ERR_NO_DEVICE = -7      /* no CUDA device / driver */
+} sb_status;
+
+/* Arithmetic classes of the GEMM inputs.  SB_F32 = fp32 storage, fp32 FMA
+ * math (1e-5 class).  SB_TF32 = fp32 storage, TF32 tensor-core multiply, the
+ * reference's own arithmetic (corecuda/wmma.spi:20,78-82).  SB_BF16 / SB_F16
+ * = 16-bit storage.  Accumulation is always fp32. */
+typedef enum sb_dtype { SB_F32 = 0, SB_TF32 = 1, SB_BF16 = 2, SB_F16 = 3, SB_I32 = 4, SB_U8 = 5 } sb_dtype;
+
+/* Epilogue flags, OR-ed.  Order of application on one output row:
+ *   v = alpha * acc + beta * C_old ; v += bias[col] ; v = relu(v) ;
+ *   v = (aux_in[row,col] > 0) ? v : 0   (RELU_GRAD) ;
+ *   row head: masked softmax, then regret matching, then argmax.
+ * The row heads need the whole row in one tile: N <= 256. */
+enum {
+  SB_EPI_NONE = 0,
+  SB_EPI_BIAS = 1,            /* bias: fp32[N] */
+  SB_EPI_RELU = 2,            /* ml/layers.spi:355 (BlockMap max 0), fused */
+  SB_EPI_RELU_GRAD = 4,       /* aux_in: activation [M,N] in out_dtype */
+  SB_EPI_MASKED_SOFTMAX = 8,  /* ml/primitives.spi:748-759; mask: uint8[M,N] or NULL = all legal */
+  SB_EPI_REGRET_MATCHING = 16,/* ml/primitives.spi:761-780, same mask */
+  SB_EPI_ARGMAX = 32          /* ml/primitives.spi:705-708; aux_out: int32[M], lowest index on ties */
+};
+
+/* ---- runtime ------------------------------------------------------------ */
+const char* sb_last_error_string(void);
+int sb_version(void);
+int sb_device_count(int* count);
+int sb_set_device(int device);
+int sb_device_sm_count(int* sms);
+/* cupy.empty / cp.cuda memory calls of corecuda/cupy.spi:20-58 are replaced by
+ * the caller's own allocator; these exist so that hosts without one (tests,
+ * bench) can still obtain device memory. */
+int sb_malloc(void** ptr, size_t bytes);
+int sb_free(void* ptr);
+int sb_malloc_host(void** ptr, size_t bytes);   /* pinned host memory */
+int sb_free_host(void* ptr);
+int sb_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+int sb_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+int sb_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+int sb_memset(void* dst, int value, size_t bytes, void* stream);
+int sb_stream_create(void** stream);
+int sb_stream_destroy(void* stream);
+int sb_stream_sync(void* stream);               /* corecuda/base.spi:45 device_sync */
+int sb_device_sync(void);
+int sb_event_create(void** event);
+int sb_event_destroy(void* event);
+int sb_event_record(void* event, void* stream);
+int sb_event_elapsed_ms(void* start, void* stop, float* ms);  /* syncs on stop */
+/* Reads (and optionally clears) the device status word written by bounded
+ * waits: status[0] = first wait site that expired (0 = healthy), status[1] =
+ * count of expired waits.  Synchronises the device. */
+int sb_device_status(int* status2, int clear);
+
+/* ---- GEMM ---------------------------------------------------------------
+ * C[M,N] <- alpha * op(A) * op(B) + beta * C, row-major, in place.
+ * a_trans = 0: A stored [M,K]; 1: stored [K,M].  b_trans = 0: B stored [K,N];
+ * 1: stored [N,K].  Replaces matmul_tf32 a_trans b_trans alpha a b beta c
+ * (ml/matmul/run.spi:21-26; template ml/matmul/kernel.spi:25-240; argument
+ * order A, B, C as in ml/matmul/run.py:1228-1232). */
+int sb_matmul_tf32(int a_trans, int b_trans, float alpha, const float* A, const float* B,
+                   float beta, float* C, int M, int N, int K, void* stream);
+
+/* Same contract with explicit input class, output dtype (SB_F32, SB_BF16,
+ * SB_F16) and fused epilogue; the dense layer of ml/layers.spi:227-240 is
+ * a_trans=0, b_trans=1, alpha=1, beta=0.  bias / mask / aux_in / aux_out may
+ * be NULL when their flag is absent. */
+int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const void* B, float beta,
+                 void* C, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                 const float* bias, const uint8_t* mask, const void* aux_in, void* aux_out,
+                 void* stream);
+
+/* Tile-shape heuristic of the tensor-core path, exposed for tests: the
+ * counterpart of matmul_config_tf32 (ml/matmul/run.spi:8-19).  Writes
+ * {block_m, block_n, block_k_elems, stages, grid}. */
+int sb_matmul_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, int epilogue,
+                   int* plan5);
+
+/* ---- elementwise / row operations (stand-alone forms) ---------------------
+ * relu: ml/layers.spi:355 + ml/primitives.spi:115-129.  Row heads:
+ * ml/primitives.spi:705-722,748-780 over x[rows, cols] fp32 row-major;
+ * `mask` uint8[rows, cols] or NULL, or prefix masking j < prefix when
+ * prefix >= 0 (ml/layers.spi:409,416).  out may alias x. */
+int sb_relu(const float* x, float* out, size_t n, void* stream);
+int sb_row_softmax(const float* x, float* out, int rows, int cols, const uint8_t* mask, int prefix,
+                   void* stream);
+int sb_row_regret_matching(const float* x, float* out, int rows, int cols, const uint8_t* mask,
+                           int prefix, void* stream);
+int sb_row_argmax(const float* x, int32_t* out, int rows, int cols, void* stream);
+int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream);  /* ml/primitives.spi:701-703 */
+/* Rounds fp32 to the storage type of a tensor-core input class (SB_BF16,
+ * SB_F16 -> 16-bit; SB_TF32 -> fp32 with the low 13 mantissa bits cleared,
+ * round-to-nearest-even). */
+int sb_convert(const float* x, void* out, size_t n, int out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPIRAL_B200_H */

@@ -1,0 +1,330 @@
+"""NumPy restatement of the reference's dense-matmul path.  TEST INFRASTRUCTURE ONLY.
+
+Each function cites the reference file:line (paths inside
+mrakgr/Spiral-s-ml-library) whose arithmetic it restates.  The product never
+imports this module; it is the checker used by tests/, the smoke check and the
+CPU-baseline timing of bench.py.
+
+Pinning.  The row operations (softmax, masked softmax, masked regret matching,
+L2 row normalisation, argmax) are pinned against the reference's own golden
+console outputs (tests/golden/primitives_golden.npz, extracted from
+test_text_outputs/primitives/ by tests/golden/make_golden.py).  The GEMM has no
+stored vectors in the reference (its self-test compares against cp.matmul on
+unsaved random inputs, ml/matmul/run.spi:41,54-58): GEMM PARITY IS UNPINNED by
+reference data and rests on the definition C = alpha*op(A)*op(B) + beta*C
+evaluated in float64.  Cross-entropy, dgrad, wgrad and SGD have no reference
+implementation at all; they are defined here.
+"""
+import numpy as np
+
+FLT_MAX = np.float32(3.402823466e38)
+
+
+# ----------------------------------------------------------------------------
+# input rounding of the tensor-core input classes
+# ----------------------------------------------------------------------------
+def round_bf16(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    r = np.where((u & np.uint32(0x7F800000)) == np.uint32(0x7F800000), u & np.uint32(0xFFFF0000), r)
+    return r.view(np.float32).reshape(np.shape(x))
+
+
+def round_f16(x):
+    return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def round_tf32(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = (u + np.uint32(0x0FFF) + ((u >> np.uint32(13)) & np.uint32(1))) & np.uint32(0xFFFFE000)
+    r = np.where((u & np.uint32(0x7F800000)) == np.uint32(0x7F800000), u, r)
+    return r.view(np.float32).reshape(np.shape(x))
+
+
+def round_input(x, in_dtype):
+    """Value the arithmetic class `in_dtype` actually multiplies (kept as fp32)."""
+    if in_dtype == "bf16":
+        return round_bf16(x)
+    if in_dtype == "f16":
+        return round_f16(x)
+    if in_dtype == "tf32":
+        return round_tf32(x)
+    return np.asarray(x, dtype=np.float32)
+
+
+# ----------------------------------------------------------------------------
+# GEMM   (ml/matmul/run.spi:21-26, ml/matmul/kernel.spi:25-240)
+# ----------------------------------------------------------------------------
+def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype="f32", exact=True):
+    """Returns alpha * op(a) @ op(b) + beta * c as float32.
+
+    a is stored [M,K] ([K,M] when a_trans); b is stored [K,N] ([N,K] when
+    b_trans); c is [M,N] (ml/matmul/run.spi:22-23, kernel.spi:51-76).  The
+    reference multiplies TF32-rounded inputs and accumulates in fp32
+    (corecuda/wmma.spi:78-82,99-105).  With exact=True the products are summed
+    in float64 (the tolerance classes absorb accumulation-order differences);
+    exact=False uses NumPy's float32 matmul, the oracle the first benchmark
+    configuration names.
+    """
+    a = round_input(a, in_dtype)
+    b = round_input(b, in_dtype)
+    opa = a.T if a_trans else a
+    opb = b.T if b_trans else b
+    if exact:
+        prod = opa.astype(np.float64) @ opb.astype(np.float64)
+        out = alpha * prod
+        if beta != 0:
+            out = out + beta * np.asarray(c, dtype=np.float64)
+        return out.astype(np.float32)
+    out = np.float32(alpha) * (opa @ opb)
+    if beta != 0:
+        out = out + np.float32(beta) * np.asarray(c, dtype=np.float32)
+    return out.astype(np.float32)
+
+
+def rel_frobenius(got, want):
+    """||got - want||_F / ||want||_F (0 when both are all zero)."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    den = np.linalg.norm(want)
+    num = np.linalg.norm(got - want)
+    return float(num / den) if den > 0 else float(num)
+
+
+# ----------------------------------------------------------------------------
+# elementwise and row operations
+# ----------------------------------------------------------------------------
+def relu(x):
+    """layers.relu: BlockMap (max 0)  (ml/layers.spi:355)."""
+    return np.maximum(np.asarray(x, dtype=np.float32), np.float32(0))
+
+
+def ln_l2(x):
+    """local_ln_l2: x / sum(x^2) per row, 0 where the sum is 0  (ml/primitives.spi:701-703)."""
+    x = np.asarray(x, dtype=np.float32)
+    s = np.sum(x * x, axis=-1, keepdims=True, dtype=np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return np.where(s != 0, x / s, np.float32(0)).astype(np.float32)
+
+
+def argmax(x):
+    """local_argmax  (ml/primitives.spi:705-708).  The reference's tie order is
+    unspecified (butterfly reduce); this oracle and the CUDA path both take the
+    lowest index."""
+    return np.argmax(np.asarray(x), axis=-1).astype(np.int32)
+
+
+def softmax(x):
+    """local_softmax: exp(x - mean(x)) normalised  (ml/primitives.spi:711-716)."""
+    x = np.asarray(x, dtype=np.float32)
+    e = np.exp(x - np.mean(x, axis=-1, keepdims=True, dtype=np.float32))
+    return (e / np.sum(e, axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+
+
+def prefix_mask(shape, size):
+    """The mask layers.masked_softmax / masked_regret_matching instantiate: j < size
+    (ml/layers.spi:409,416)."""
+    m = np.zeros(shape, dtype=bool)
+    m[..., :size] = True
+    return m
+
+
+def masked_softmax(x, mask):
+    """local_masked_softmax  (ml/primitives.spi:748-759): subtract the mean of
+    the legal entries, masked entries enter exp as -FLT_MAX (so contribute 0)."""
+    x = np.asarray(x, dtype=np.float32)
+    mask = np.asarray(mask, dtype=bool)
+    count = np.sum(mask, axis=-1, keepdims=True).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        avg = np.sum(np.where(mask, x, np.float32(0)), axis=-1, keepdims=True, dtype=np.float32) / count
+        e = np.exp(np.where(mask, x, -FLT_MAX) - avg)
+        e = np.where(mask, e, np.float32(0))
+        s = np.sum(e, axis=-1, keepdims=True, dtype=np.float32)
+        out = e / s
+    return np.where(np.isfinite(out), out, np.float32(0)).astype(np.float32)
+
+
+def regret_matching(x):
+    """local_regret_matching  (ml/primitives.spi:718-722)."""
+    return masked_regret_matching(x, np.ones(np.shape(x), dtype=bool))
+
+
+def masked_regret_matching(x, mask):
+    """local_masked_regret_matching  (ml/primitives.spi:761-780): p = max(0,x) on
+    legal entries; p / sum(p) if the sum is non-zero, else uniform over the
+    legal entries; illegal entries are 0."""
+    x = np.asarray(x, dtype=np.float32)
+    mask = np.asarray(mask, dtype=bool)
+    p = np.where(mask, np.maximum(x, np.float32(0)), np.float32(0))
+    s = np.sum(p, axis=-1, keepdims=True, dtype=np.float32)
+    count = np.sum(mask, axis=-1, keepdims=True).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = np.where(s != 0, p / s, np.float32(1) / count)
+    out = np.where(mask, out, np.float32(0))
+    return np.where(np.isfinite(out), out, np.float32(0)).astype(np.float32)
+
+
+# ----------------------------------------------------------------------------
+# dense layers and the policy MLP  (ml/layers.spi:227-240, 353-355, 408-420)
+# ----------------------------------------------------------------------------
+def dense(x, w, bias=None, in_dtype="f32"):
+    """BlockMatmul: y = x @ w.T with w stored [out, in] (NT, alpha=1, beta=0;
+    ml/layers.spi:229-235,467).  The reference has no bias; `bias` is the
+    benchmark configurations' addition."""
+    y = matmul(False, True, 1.0, x, w, 0.0, None, in_dtype=in_dtype)
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float32)
+    return y.astype(np.float32)
+
+
+def mlp_forward(x, weights, biases=None, mask=None, in_dtype="f32", head=("masked_softmax",),
+                act_dtype=None, return_activations=False):
+    """Hidden layers dense+ReLU, last layer dense + row head.
+
+    `act_dtype` rounds every hidden activation to the storage type the CUDA path
+    keeps between layers (None = fp32).  Heads apply in the order
+    masked_softmax, regret_matching; mask=None means every action is legal.
+    Returns probabilities (and optionally the list [x, h1, ..., logits]).
+    """
+    acts = [np.asarray(x, dtype=np.float32)]
+    h = acts[0]
+    n_layers = len(weights)
+    for i, w in enumerate(weights):
+        b = None if biases is None else biases[i]
+        h = dense(h, w, b, in_dtype=in_dtype)
+        if i < n_layers - 1:
+            h = relu(h)
+            if act_dtype is not None:
+                h = round_input(h, act_dtype)
+        acts.append(h)
+    logits = h
+    m = np.ones(logits.shape, dtype=bool) if mask is None else np.asarray(mask, dtype=bool)
+    out = logits
+    if "masked_softmax" in head:
+        out = masked_softmax(out, m)
+    if "regret_matching" in head:
+        out = masked_regret_matching(out, m)
+    if return_activations:
+        return out, acts
+    return out
+
+
+def cross_entropy_loss(probs, target, mask=None):
+    """Mean over rows of -sum_j target_j * log(probs_j) over legal j.  Not in the
+    reference (it has no loss); defined by the benchmark's training configurations."""
+    probs = np.asarray(probs, dtype=np.float64)
+    target = np.asarray(target, dtype=np.float64)
+    m = np.ones(probs.shape, dtype=bool) if mask is None else np.asarray(mask, dtype=bool)
+    with np.errstate(divide="ignore"):
+        lp = np.where(m, np.log(np.maximum(probs, 1e-38)), 0.0)
+    return float(-np.sum(np.where(m, target * lp, 0.0)) / probs.shape[0])
+
+
+def mlp_train_step(x, weights, biases, mask, target, lr, in_dtype="f32", act_dtype=None, global_batch=None):
+    """One SGD step on cross-entropy(masked_softmax(logits), target).  Not in the
+    reference (no backward pass exists there, ml/layers.spi:10 is CEM scratch).
+
+    d logits = (softmax - target * legal) / global_batch on legal entries (the
+    target is renormalised over legal entries by the caller); dgrad is NN
+    (dX = dY @ W), wgrad is TN (dW = dY.T @ X), db = column sums; hidden
+    gradients pass through ReLU'(h) = [h > 0].  Returns (new_weights,
+    new_biases, loss, grads) with grads = [(dW, db), ...] already divided by
+    the global batch.
+    """
+    probs, acts = mlp_forward(x, weights, biases, mask, in_dtype=in_dtype, head=("masked_softmax",),
+                              act_dtype=act_dtype, return_activations=True)
+    bsz = x.shape[0] if global_batch is None else global_batch
+    m = np.ones(probs.shape, dtype=bool) if mask is None else np.asarray(mask, dtype=bool)
+    tgt = np.where(m, np.asarray(target, dtype=np.float32), np.float32(0))
+    loss = cross_entropy_loss(probs, tgt, m)
+    tsum = np.sum(tgt, axis=-1, keepdims=True, dtype=np.float32)
+    dy = np.where(m, probs * tsum - tgt, np.float32(0)).astype(np.float32) / np.float32(bsz)
+    grads = [None] * len(weights)
+    for i in range(len(weights) - 1, -1, -1):
+        h_in = acts[i]
+        dy_r = round_input(dy, in_dtype) if in_dtype != "f32" else dy
+        dw = matmul(True, False, 1.0, dy_r, h_in, 0.0, None, in_dtype=in_dtype)   # [out,in] = dY.T @ X
+        db = np.sum(dy, axis=0, dtype=np.float64).astype(np.float32)
+        grads[i] = (dw, db)
+        if i > 0:
+            dx = matmul(False, False, 1.0, dy_r, weights[i], 0.0, None, in_dtype=in_dtype)  # dY @ W
+            dy = np.where(acts[i] > 0, dx, np.float32(0)).astype(np.float32)
+            if act_dtype is not None:
+                dy = round_input(dy, act_dtype)
+    new_w = [np.asarray(w, np.float32) - np.float32(lr) * g[0] for w, g in zip(weights, grads)]
+    new_b = None
+    if biases is not None:
+        new_b = [np.asarray(b, np.float32) - np.float32(lr) * g[1] for b, g in zip(biases, grads)]
+    return new_w, new_b, loss, grads
+
+
+# ----------------------------------------------------------------------------
+# seeded synthetic inputs of the benchmark configurations
+# ----------------------------------------------------------------------------
+def rng(seed):
+    return np.random.Generator(np.random.Philox(seed))
+
+
+def kaiming_uniform(gen, fan_out, fan_in):
+    """U(-sqrt(6/fan_in), +sqrt(6/fan_in)), stored [out, in] like layers.weight
+    (ml/layers.spi:467; the reference itself initialises N(0, 0.1), :460-463)."""
+    bound = np.sqrt(6.0 / fan_in)
+    return gen.uniform(-bound, bound, size=(fan_out, fan_in)).astype(np.float32)
+
+
+def mlp_weights(seed, sizes):
+    gen = rng(seed)
+    ws = [kaiming_uniform(gen, sizes[i + 1], sizes[i]) for i in range(len(sizes) - 1)]
+    bs = [np.zeros(sizes[i + 1], dtype=np.float32) for i in range(len(sizes) - 1)]
+    return ws, bs
+
+
+def one_hot_field(gen, rows, width, allow_none=False):
+    """A one-hot field written the way corebase/pickler.spi:20-37 writes a bounded int."""
+    out = np.zeros((rows, width), dtype=np.float32)
+    idx = gen.integers(0, width + (1 if allow_none else 0), size=rows)
+    ok = idx < width
+    out[np.arange(rows)[ok], idx[ok]] = 1.0
+    return out
+
+
+def leduc_inputs(seed, batch):
+    """[batch, 32] {0,1} states: card one-hot(3) | community one-hot(4) | pot one-hot(14)
+    | raises-left one-hot(3) | 8 history bits; plus a mask with 2 or 3 legal actions of 3."""
+    gen = rng(seed)
+    x = np.concatenate([
+        one_hot_field(gen, batch, 3), one_hot_field(gen, batch, 4), one_hot_field(gen, batch, 14),
+        one_hot_field(gen, batch, 3), (gen.random((batch, 8)) < 0.5).astype(np.float32)], axis=1)
+    mask = np.ones((batch, 3), dtype=np.uint8)
+    drop = gen.integers(0, 4, size=batch)          # 3 = keep all three legal
+    rows = np.arange(batch)[drop < 3]
+    mask[rows, drop[drop < 3]] = 0
+    return x.astype(np.float32), mask
+
+
+def holdem_inputs(seed, batch, features=512, actions=10):
+    """[batch, 512]: 7 card slots x (suit one-hot(4) + rank one-hot(13)) = 119 {0,1}
+    features (game/nl_hu_holdem/model_cem.spi:13-15,26-27; trailing board slots
+    empty according to a random street), then continuous U[0,1) stack/pot values;
+    plus a mask with 2..actions legal actions."""
+    gen = rng(seed)
+    x = np.zeros((batch, features), dtype=np.float32)
+    street_cards = np.array([2, 5, 6, 7])[gen.integers(0, 4, size=batch)]
+    for slot in range(7):
+        live = street_cards > slot
+        suit = one_hot_field(gen, batch, 4)
+        rank = one_hot_field(gen, batch, 13)
+        x[:, slot * 17:slot * 17 + 4] = suit * live[:, None]
+        x[:, slot * 17 + 4:slot * 17 + 17] = rank * live[:, None]
+    x[:, 119:] = gen.random((batch, features - 119), dtype=np.float32)
+    mask = (gen.random((batch, actions)) < 0.6).astype(np.uint8)
+    mask[:, 0] = 1
+    mask[:, 1] = 1
+    return x, mask
+
+
+def random_target(seed, mask):
+    """Random fp32 target distribution over the legal actions of each row."""
+    gen = rng(seed)
+    t = gen.random(mask.shape, dtype=np.float32) * (np.asarray(mask) != 0)
+    return (t / np.sum(t, axis=-1, keepdims=True)).astype(np.float32)

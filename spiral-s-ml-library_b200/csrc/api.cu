@@ -1,0 +1,105 @@
+// Public GEMM entry points: argument validation and dispatch between the
+// tensor-core path (TF32 / BF16 / FP16 inputs) and the fp32 FFMA path.
+// Mirrors the call surface of matmul_tf32 / matmul_tf32'
+// (ml/matmul/run.spi:21-26): C's shape gives M and N, A gives K, all tensors
+// row-major and written in place.
+#include "common.cuh"
+
+int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
+                        float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
+                        int epi, const float* bias, const uint8_t* mask, const void* aux_in,
+                        void* aux_out, cudaStream_t stream);
+int sb_umma_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, int sms, int* plan5);
+int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStream_t stream);
+int sb_umma_head_max_n();
+int sb_sgemm_launch(int a_trans, int b_trans, float alpha, const float* A, const float* B, float beta,
+                    float* C, int M, int N, int K, int epi, const float* bias, cudaStream_t stream);
+
+namespace {
+constexpr int HEAD_FLAGS = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
+constexpr int ALL_FLAGS = SB_EPI_BIAS | SB_EPI_RELU | SB_EPI_RELU_GRAD | HEAD_FLAGS;
+
+int run_heads_unfused(float* C, int M, int N, int epi, const uint8_t* mask, void* aux_out,
+                      void* stream) {
+  int rc = SB_OK;
+  if (epi & SB_EPI_MASKED_SOFTMAX) {
+    rc = sb_row_softmax(C, C, M, N, mask, -1, stream);
+    if (rc != SB_OK) return rc;
+  }
+  if (epi & SB_EPI_REGRET_MATCHING) {
+    rc = sb_row_regret_matching(C, C, M, N, mask, -1, stream);
+    if (rc != SB_OK) return rc;
+  }
+  if (epi & SB_EPI_ARGMAX) rc = sb_row_argmax(C, reinterpret_cast<int32_t*>(aux_out), M, N, stream);
+  return rc;
+}
+}  // namespace
+
+extern "C" {
+
+int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const void* B, float beta,
+                 void* C, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                 const float* bias, const uint8_t* mask, const void* aux_in, void* aux_out,
+                 void* stream) {
+  if (M < 0 || N < 0 || K < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: negative dimension (M=%d N=%d K=%d)", M, N, K);
+  if (in_dtype != SB_F32 && in_dtype != SB_TF32 && in_dtype != SB_BF16 && in_dtype != SB_F16)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: unknown input dtype %d", in_dtype);
+  if (out_dtype != SB_F32 && out_dtype != SB_BF16 && out_dtype != SB_F16)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: unknown output dtype %d", out_dtype);
+  if (epilogue & ~ALL_FLAGS) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: unknown epilogue flag in 0x%x", epilogue);
+  if (M == 0 || N == 0) return SB_OK;
+  if (!C) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: C is null");
+  if (K > 0 && (!A || !B)) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: A or B is null");
+  if ((epilogue & SB_EPI_BIAS) && !bias) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_BIAS without a bias pointer");
+  if ((epilogue & SB_EPI_RELU_GRAD) && !aux_in) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_RELU_GRAD without aux_in");
+  if ((epilogue & SB_EPI_ARGMAX) && !aux_out) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_ARGMAX without aux_out");
+  if ((epilogue & HEAD_FLAGS) && out_dtype != SB_F32)
+    return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: row heads write fp32 output only");
+  if ((epilogue & HEAD_FLAGS) && (epilogue & SB_EPI_RELU_GRAD))
+    return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: a row head cannot be combined with SB_EPI_RELU_GRAD");
+  if (reinterpret_cast<uintptr_t>(C) & 15) return sb_fail(SB_ERR_MISALIGNED, "sb_matmul: C must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+
+  if (K == 0) {
+    // Empty inner dimension: op(A) * op(B) is the zero matrix.
+    if (epilogue != SB_EPI_NONE) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: K == 0 with an epilogue");
+    return sb_scale_launch(C, (long long)M * N, beta, out_dtype, s);
+  }
+
+  if (in_dtype == SB_F32) {
+    if (out_dtype != SB_F32) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: the fp32 path writes fp32 output only");
+    if (epilogue & SB_EPI_RELU_GRAD) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_RELU_GRAD needs a tensor-core input class");
+    int rc = sb_sgemm_launch(a_trans, b_trans, alpha, (const float*)A, (const float*)B, beta, (float*)C,
+                             M, N, K, epilogue & (SB_EPI_BIAS | SB_EPI_RELU), bias, s);
+    if (rc != SB_OK) return rc;
+    if (epilogue & HEAD_FLAGS) return run_heads_unfused((float*)C, M, N, epilogue, mask, aux_out, stream);
+    return SB_OK;
+  }
+
+  if ((epilogue & HEAD_FLAGS) && N > sb_umma_head_max_n()) {
+    int rc = sb_umma_gemm_launch(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, in_dtype, out_dtype,
+                                 epilogue & ~HEAD_FLAGS, bias, nullptr, aux_in, nullptr, s);
+    if (rc != SB_OK) return rc;
+    return run_heads_unfused((float*)C, M, N, epilogue, mask, aux_out, stream);
+  }
+  return sb_umma_gemm_launch(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, in_dtype, out_dtype,
+                             epilogue, bias, mask, aux_in, aux_out, s);
+}
+
+int sb_matmul_tf32(int a_trans, int b_trans, float alpha, const float* A, const float* B,
+                   float beta, float* C, int M, int N, int K, void* stream) {
+  return sb_matmul_ex(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, SB_TF32, SB_F32, SB_EPI_NONE,
+                      nullptr, nullptr, nullptr, nullptr, stream);
+}
+
+int sb_matmul_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, int epilogue,
+                   int* plan5) {
+  (void)epilogue;
+  if (!plan5) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_plan: null output");
+  if (M <= 0 || N <= 0 || K <= 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_plan: dimensions must be positive");
+  if (in_dtype != SB_TF32 && in_dtype != SB_BF16 && in_dtype != SB_F16)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_plan: tensor-core input classes only");
+  return sb_umma_plan(a_trans, b_trans, M, N, K, in_dtype, 148, plan5);
+}
+
+}  // extern "C"

@@ -1,0 +1,228 @@
+// Stand-alone elementwise and per-row operations: the unfused forms of the
+// epilogues, for rows wider than a fused head can hold and for callers that
+// run them as separate graph nodes the way the reference does
+// (BlockMap / BlockRowMap / BlockRowReduce, ml/layers.spi:195-210;
+// row math ml/primitives.spi:701-722,748-780).
+//
+// One warp owns one row; lanes stride over the columns with warp-shuffle
+// reductions, so any column count works.
+#include "common.cuh"
+
+namespace {
+
+constexpr float NEG_MAX = -3.402823466e38f;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int warp_sum_int(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ bool is_legal(const uint8_t* mrow, int prefix, int j) {
+  if (prefix >= 0) return j < prefix;
+  if (mrow) return mrow[j] != 0;
+  return true;
+}
+
+enum RowOp { ROW_SOFTMAX = 0, ROW_REGRET = 1, ROW_LN_L2 = 2 };
+
+template <int OP>
+__global__ void row_map_kernel(const float* x, float* out, int rows, int cols,
+                               const uint8_t* __restrict__ mask, int prefix) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += (long long)gridDim.x * warps_per_block) {
+    const float* xr = x + row * cols;
+    float* orow = out + row * cols;
+    const uint8_t* mrow = mask ? mask + row * cols : nullptr;
+    if (OP == ROW_SOFTMAX) {
+      float mx = NEG_MAX;
+      for (int j = lane; j < cols; j += 32)
+        if (is_legal(mrow, prefix, j)) mx = fmaxf(mx, xr[j]);
+      mx = warp_max(mx);
+      float s = 0.f;
+      for (int j = lane; j < cols; j += 32)
+        if (is_legal(mrow, prefix, j)) s += __expf(xr[j] - mx);
+      s = warp_sum(s);
+      const float inv = s > 0.f ? 1.f / s : 0.f;
+      for (int j = lane; j < cols; j += 32)
+        orow[j] = is_legal(mrow, prefix, j) ? __expf(xr[j] - mx) * inv : 0.f;
+    } else if (OP == ROW_REGRET) {
+      float s = 0.f;
+      int count = 0;
+      for (int j = lane; j < cols; j += 32) {
+        if (is_legal(mrow, prefix, j)) {
+          s += fmaxf(xr[j], 0.f);
+          ++count;
+        }
+      }
+      s = warp_sum(s);
+      count = warp_sum_int(count);
+      const float inv_len = count > 0 ? 1.f / (float)count : 0.f;
+      for (int j = lane; j < cols; j += 32) {
+        const bool lg = is_legal(mrow, prefix, j);
+        const float q = fmaxf(xr[j], 0.f);
+        orow[j] = !lg ? 0.f : (s != 0.f ? q / s : inv_len);
+      }
+    } else {
+      float s = 0.f;
+      for (int j = lane; j < cols; j += 32) s += xr[j] * xr[j];
+      s = warp_sum(s);
+      for (int j = lane; j < cols; j += 32) orow[j] = s != 0.f ? xr[j] / s : 0.f;
+    }
+  }
+}
+
+__global__ void row_argmax_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int rows,
+                                  int cols) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += (long long)gridDim.x * warps_per_block) {
+    const float* xr = x + row * cols;
+    float bv = NEG_MAX;
+    int bi = 0x7fffffff;
+    for (int j = lane; j < cols; j += 32) {
+      const float v = xr[j];
+      if (v > bv || (v == bv && j < bi)) {
+        bv = v;
+        bi = j;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+__global__ void relu_kernel(const float* x, float* out, size_t n) {
+  const size_t n4 = n / 4;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (aligned) {
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    float4* o4 = reinterpret_cast<float4*>(out);
+    for (size_t q = i; q < n4; q += step) {
+      float4 v = x4[q];
+      v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+      o4[q] = v;
+    }
+    for (size_t q = n4 * 4 + i; q < n; q += step) out[q] = fmaxf(x[q], 0.f);
+  } else {
+    for (size_t q = i; q < n; q += step) out[q] = fmaxf(x[q], 0.f);
+  }
+}
+
+__device__ __forceinline__ float round_to_tf32(float v) {
+  // Round-to-nearest-even to 10 explicit mantissa bits; the result is an
+  // fp32 value whose low 13 bits are zero, so the tensor core's own operand
+  // truncation leaves it unchanged.
+  uint32_t u = __float_as_uint(v);
+  if ((u & 0x7f800000u) == 0x7f800000u) return v;
+  const uint32_t lsb = (u >> 13) & 1u;
+  u += 0x0fffu + lsb;
+  u &= 0xffffe000u;
+  return __uint_as_float(u);
+}
+
+__global__ void convert_kernel(const float* __restrict__ x, void* __restrict__ out, size_t n, int dt) {
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const float v = x[i];
+    if (dt == SB_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+    else if (dt == SB_F16) reinterpret_cast<__half*>(out)[i] = __float2half_rn(v);
+    else if (dt == SB_TF32) reinterpret_cast<float*>(out)[i] = round_to_tf32(v);
+    else reinterpret_cast<float*>(out)[i] = v;
+  }
+}
+
+int grid_for(long long work_items, int per_block) {
+  long long b = (work_items + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  const long long cap = 148LL * 16;
+  return (int)(b > cap ? cap : b);
+}
+
+}  // namespace
+
+extern "C" {
+
+int sb_relu(const float* x, float* out, size_t n, void* stream) {
+  if (n == 0) return SB_OK;
+  if (!x || !out) return sb_fail(SB_ERR_BAD_ARG, "sb_relu: null pointer");
+  relu_kernel<<<grid_for((long long)(n / 4 + 1), 256), 256, 0, (cudaStream_t)stream>>>(x, out, n);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+static int row_args_ok(const char* who, const void* x, const void* out, int rows, int cols) {
+  if (rows < 0 || cols < 0) return sb_fail(SB_ERR_BAD_ARG, "%s: negative size", who);
+  if (rows == 0 || cols == 0) return 1;
+  if (!x || !out) return sb_fail(SB_ERR_BAD_ARG, "%s: null pointer", who);
+  return SB_OK;
+}
+
+int sb_row_softmax(const float* x, float* out, int rows, int cols, const uint8_t* mask, int prefix,
+                   void* stream) {
+  int rc = row_args_ok("sb_row_softmax", x, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  row_map_kernel<ROW_SOFTMAX><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, mask, prefix);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_row_regret_matching(const float* x, float* out, int rows, int cols, const uint8_t* mask,
+                           int prefix, void* stream) {
+  int rc = row_args_ok("sb_row_regret_matching", x, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  row_map_kernel<ROW_REGRET><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, mask, prefix);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream) {
+  int rc = row_args_ok("sb_row_ln_l2", x, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  row_map_kernel<ROW_LN_L2><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, nullptr, -1);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_row_argmax(const float* x, int32_t* out, int rows, int cols, void* stream) {
+  int rc = row_args_ok("sb_row_argmax", x, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  row_argmax_kernel<<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_convert(const float* x, void* out, size_t n, int out_dtype, void* stream) {
+  if (n == 0) return SB_OK;
+  if (!x || !out) return sb_fail(SB_ERR_BAD_ARG, "sb_convert: null pointer");
+  if (out_dtype != SB_BF16 && out_dtype != SB_F16 && out_dtype != SB_TF32 && out_dtype != SB_F32)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_convert: unknown output dtype %d", out_dtype);
+  convert_kernel<<<grid_for((long long)n, 256), 256, 0, (cudaStream_t)stream>>>(x, out, n, out_dtype);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,11 @@
+"""spiral_b200: B200 (sm_100a) dense-matmul / policy-MLP path behind the reference's call surface.
+
+A thin ctypes host over libspiral_b200.so (hand-written CUDA: tcgen05 MMAs with
+TMEM accumulators fed by TMA).  No CPU fallback exists: without the built
+library every operation raises.
+"""
+from ._lib import SpiralError, LIB_PATH  # noqa: F401
+from .device import (DeviceArray, Event, device_count, device_ptr, device_status, set_device,  # noqa: F401
+                     synchronize)
+from .matmul import matmul, matmul_plan, matmul_tf32  # noqa: F401
+from . import primitives  # noqa: F401

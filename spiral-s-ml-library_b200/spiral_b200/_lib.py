@@ -1,0 +1,108 @@
+"""ctypes binding of libspiral_b200.so: the only way the Python host reaches the GPU.
+
+There is no CPU fallback: if the shared library is missing, or a call fails,
+an exception is raised.
+"""
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p, POINTER
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libspiral_b200.so")
+
+SB_OK = 0
+STATUS_NAMES = {
+    0: "SB_OK", -1: "SB_ERR_BAD_ARG", -2: "SB_ERR_MISALIGNED", -3: "SB_ERR_UNSUPPORTED",
+    -4: "SB_ERR_CUDA", -5: "SB_ERR_DEVICE_TIMEOUT", -6: "SB_ERR_TOO_LARGE", -7: "SB_ERR_NO_DEVICE",
+}
+
+# sb_dtype
+F32, TF32, BF16, F16, I32, U8 = 0, 1, 2, 3, 4, 5
+DTYPE_CODES = {"f32": F32, "tf32": TF32, "bf16": BF16, "f16": F16, "i32": I32, "u8": U8}
+
+# epilogue flags
+EPI_NONE, EPI_BIAS, EPI_RELU, EPI_RELU_GRAD = 0, 1, 2, 4
+EPI_MASKED_SOFTMAX, EPI_REGRET_MATCHING, EPI_ARGMAX = 8, 16, 32
+
+
+class SpiralError(RuntimeError):
+    """A libspiral_b200 call returned a negative status."""
+
+    def __init__(self, code, text):
+        self.code = code
+        super().__init__("%s (%d): %s" % (STATUS_NAMES.get(code, "?"), code, text))
+
+
+_P = c_void_p
+_I = c_int
+_F = c_float
+_Z = c_size_t
+_PP = POINTER(c_void_p)
+_IP = POINTER(c_int)
+
+# name -> (restype, argtypes); every symbol include/spiral_b200.h declares.
+SIGNATURES = {
+    "sb_last_error_string": (c_char_p, []),
+    "sb_version": (_I, []),
+    "sb_device_count": (_I, [_IP]),
+    "sb_set_device": (_I, [_I]),
+    "sb_device_sm_count": (_I, [_IP]),
+    "sb_malloc": (_I, [_PP, _Z]),
+    "sb_free": (_I, [_P]),
+    "sb_malloc_host": (_I, [_PP, _Z]),
+    "sb_free_host": (_I, [_P]),
+    "sb_memcpy_h2d": (_I, [_P, _P, _Z, _P]),
+    "sb_memcpy_d2h": (_I, [_P, _P, _Z, _P]),
+    "sb_memcpy_d2d": (_I, [_P, _P, _Z, _P]),
+    "sb_memset": (_I, [_P, _I, _Z, _P]),
+    "sb_stream_create": (_I, [_PP]),
+    "sb_stream_destroy": (_I, [_P]),
+    "sb_stream_sync": (_I, [_P]),
+    "sb_device_sync": (_I, []),
+    "sb_event_create": (_I, [_PP]),
+    "sb_event_destroy": (_I, [_P]),
+    "sb_event_record": (_I, [_P, _P]),
+    "sb_event_elapsed_ms": (_I, [_P, _P, POINTER(c_float)]),
+    "sb_device_status": (_I, [_IP, _I]),
+    "sb_matmul_tf32": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _P]),
+    "sb_matmul_ex": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "sb_matmul_plan": (_I, [_I, _I, _I, _I, _I, _I, _I, _IP]),
+    "sb_relu": (_I, [_P, _P, _Z, _P]),
+    "sb_row_softmax": (_I, [_P, _P, _I, _I, _P, _I, _P]),
+    "sb_row_regret_matching": (_I, [_P, _P, _I, _I, _P, _I, _P]),
+    "sb_row_argmax": (_I, [_P, _P, _I, _I, _P]),
+    "sb_row_ln_l2": (_I, [_P, _P, _I, _I, _P]),
+    "sb_convert": (_I, [_P, _P, _Z, _I, _P]),
+}
+
+_lib = None
+
+
+def load():
+    """Loads the shared library once and attaches the signatures."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "libspiral_b200.so is not built (%s); run spiral-s-ml-library_b200/build.py -- "
+            "there is no CPU fallback" % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(rc):
+    if rc != SB_OK:
+        text = load().sb_last_error_string()
+        raise SpiralError(rc, text.decode("utf-8", "replace") if text else "")
+    return rc
+
+
+def call(name, *args):
+    """Calls an int-returning entry point and raises SpiralError on failure."""
+    return check(getattr(load(), name)(*args))

@@ -1,0 +1,88 @@
+"""GEMM call surface: the reference's ``matmul_tf32 a_trans b_trans alpha a b beta c``.
+
+Reference: ml/matmul/run.spi:21-26 -- M and N come from ``c``'s shape, K from
+``a``'s (swapped when ``a_trans``), every tensor is row-major and ``c`` is
+updated in place: ``c <- alpha * op(a) @ op(b) + beta * c``.
+"""
+import ctypes
+
+from . import _lib
+from .device import device_ptr, dtype_tag, stream_ptr
+
+EPILOGUE_FLAGS = {
+    "bias": _lib.EPI_BIAS, "relu": _lib.EPI_RELU, "relu_grad": _lib.EPI_RELU_GRAD,
+    "masked_softmax": _lib.EPI_MASKED_SOFTMAX, "regret_matching": _lib.EPI_REGRET_MATCHING,
+    "argmax": _lib.EPI_ARGMAX,
+}
+
+
+def _shape2(x, what):
+    shape = tuple(getattr(x, "shape", ()))
+    if len(shape) != 2:
+        raise ValueError("%s must be a 2-D array, got shape %s" % (what, shape))
+    return int(shape[0]), int(shape[1])
+
+
+def _dims(a_trans, b_trans, a, b, c):
+    m, n = _shape2(c, "c")
+    ar, ac = _shape2(a, "a")
+    br, bc = _shape2(b, "b")
+    am, k = (ac, ar) if a_trans else (ar, ac)
+    bk, bn = (bc, br) if b_trans else (br, bc)
+    if am != m or bn != n or bk != k:
+        raise ValueError("shape mismatch: op(a) is %dx%d, op(b) is %dx%d, c is %dx%d" % (am, k, bk, bn, m, n))
+    return m, n, k
+
+
+def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype=None, epilogue=(), bias=None, mask=None,
+           aux_in=None, aux_out=None, stream=None):
+    """``c <- alpha * op(a) @ op(b) + beta * c`` with an optional fused epilogue.
+
+    ``in_dtype``: 'f32' (FFMA, 1e-5 class), 'tf32' (fp32 storage, TF32 multiply),
+    'bf16', 'f16'; by default fp32 storage runs as 'tf32', the reference's own
+    arithmetic.  ``epilogue``: iterable of names from EPILOGUE_FLAGS.
+    """
+    m, n, k = _dims(bool(a_trans), bool(b_trans), a, b, c)
+    storage = dtype_tag(a)
+    if storage != dtype_tag(b):
+        raise TypeError("a and b must share a storage dtype (%s vs %s)" % (storage, dtype_tag(b)))
+    if in_dtype is None:
+        in_dtype = "tf32" if storage in ("f32", "tf32") else storage
+    if (in_dtype in ("f32", "tf32")) != (storage in ("f32", "tf32")) or \
+            (in_dtype in ("bf16", "f16") and in_dtype != storage):
+        raise TypeError("in_dtype %s does not match the storage dtype %s" % (in_dtype, storage))
+    out_dtype = dtype_tag(c)
+    if out_dtype == "tf32":
+        out_dtype = "f32"
+    epi = 0
+    for name in epilogue:
+        epi |= EPILOGUE_FLAGS[name]
+    _lib.call("sb_matmul_ex", int(bool(a_trans)), int(bool(b_trans)), ctypes.c_float(alpha),
+              device_ptr(a), device_ptr(b), ctypes.c_float(beta), device_ptr(c), m, n, k,
+              _lib.DTYPE_CODES[in_dtype], _lib.DTYPE_CODES[out_dtype], epi, device_ptr(bias),
+              device_ptr(mask), device_ptr(aux_in), device_ptr(aux_out), stream_ptr(stream))
+    return c
+
+
+def matmul_tf32(a_trans, b_trans, alpha, a, b, beta, c, stream=None):
+    """Drop-in for the reference's ``matmul_tf32`` (fp32 storage, TF32 multiply, fp32 accumulate)."""
+    m, n, k = _dims(bool(a_trans), bool(b_trans), a, b, c)
+    for x, what in ((a, "a"), (b, "b"), (c, "c")):
+        if dtype_tag(x) not in ("f32", "tf32"):
+            raise TypeError("matmul_tf32: %s must be fp32" % what)
+    _lib.call("sb_matmul_tf32", int(bool(a_trans)), int(bool(b_trans)), ctypes.c_float(alpha),
+              device_ptr(a), device_ptr(b), ctypes.c_float(beta), device_ptr(c), m, n, k,
+              stream_ptr(stream))
+    return c
+
+
+def matmul_plan(a_trans, b_trans, m, n, k, in_dtype="tf32"):
+    """Tile plan of the tensor-core path: dict(block_m, block_n, block_k, stages, grid).
+
+    Counterpart of matmul_config_tf32 (ml/matmul/run.spi:8-19); unlike it, no
+    divisibility of m, n, k by the tile is demanded (ragged edges are zero-filled).
+    """
+    plan = (ctypes.c_int * 5)()
+    _lib.call("sb_matmul_plan", int(bool(a_trans)), int(bool(b_trans)), int(m), int(n), int(k),
+              _lib.DTYPE_CODES[in_dtype], 0, plan)
+    return dict(zip(("block_m", "block_n", "block_k", "stages", "grid"), list(plan)))

@@ -1,0 +1,82 @@
+"""GPU parity of the stand-alone row / elementwise kernels against the oracle and the
+reference's golden outputs.  Tolerance: 2e-6 absolute against the six-decimal golden
+prints, 1e-6 absolute against the fp32 oracle (probabilities in [0, 1])."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import spiral_oracle as so
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "primitives_golden.npz"))
+
+
+def _dev(gpu, a, dtype=None):
+    return gpu.DeviceArray.from_numpy(a, dtype)
+
+
+@pytest.mark.parametrize("sub", ["a", "b"])
+def test_golden_row_ops(gpu, sub):
+    P = gpu.primitives
+    x = GOLD["t2%s_input" % sub]
+    dx = _dev(gpu, x)
+    out = gpu.DeviceArray(x.shape, "f32")
+    np.testing.assert_allclose(P.softmax(dx, out).numpy(), GOLD["t2%s_softmax" % sub], atol=2e-6, rtol=0)
+    np.testing.assert_allclose(P.masked_softmax(4, dx, out).numpy(), GOLD["t2%s_masked_softmax4" % sub], atol=2e-6, rtol=0)
+    np.testing.assert_allclose(P.masked_softmax(11, dx, out).numpy(), GOLD["t2%s_masked_softmax11" % sub], atol=2e-6, rtol=0)
+    np.testing.assert_allclose(P.ln_l2(dx, out).numpy(), GOLD["t2%s_ln_l2" % sub], atol=2e-6, rtol=0)
+    idx = gpu.DeviceArray((x.shape[0],), "i32")
+    np.testing.assert_array_equal(P.argmax(dx, idx).numpy(), so.argmax(x))
+    x3 = GOLD["t3%s_input" % sub]
+    out3 = gpu.DeviceArray(x3.shape, "f32")
+    np.testing.assert_allclose(P.masked_regret_matching(3, _dev(gpu, x3), out3).numpy(),
+                               GOLD["t3%s_masked_regret3" % sub], atol=2e-6, rtol=0)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (7, 3), (33, 10), (256, 128), (5, 1000)])
+def test_row_ops_against_oracle(gpu, rows, cols):
+    P = gpu.primitives
+    g = so.rng(rows * 1000 + cols)
+    x = g.normal(size=(rows, cols)).astype(np.float32) * 3
+    mask = (g.random((rows, cols)) < 0.6).astype(np.uint8)
+    mask[:, 0] = 1
+    dx, dm = _dev(gpu, x), _dev(gpu, mask)
+    out = gpu.DeviceArray(x.shape, "f32")
+    np.testing.assert_allclose(P.softmax(dx, out, mask=dm).numpy(), so.masked_softmax(x, mask), atol=1e-6)
+    np.testing.assert_allclose(P.regret_matching(dx, out, mask=dm).numpy(), so.masked_regret_matching(x, mask), atol=1e-6)
+    np.testing.assert_allclose(P.regret_matching(dx, out).numpy(), so.regret_matching(x), atol=1e-6)
+    neg = -np.abs(x)
+    np.testing.assert_allclose(P.regret_matching(_dev(gpu, neg), out, mask=dm).numpy(),
+                               so.masked_regret_matching(neg, mask), atol=1e-6)
+    np.testing.assert_array_equal(P.relu(dx, out).numpy(), so.relu(x))
+    idx = gpu.DeviceArray((rows,), "i32")
+    np.testing.assert_array_equal(P.argmax(dx, idx).numpy(), so.argmax(x))
+
+
+def test_argmax_ties_take_lowest_index(gpu):
+    x = np.zeros((4, 40), np.float32)
+    x[1, [5, 37]] = 2.0
+    x[2, [33, 34]] = 1.0
+    idx = gpu.DeviceArray((4,), "i32")
+    np.testing.assert_array_equal(gpu.primitives.argmax(_dev(gpu, x), idx).numpy(), [0, 5, 33, 0])
+
+
+def test_in_place_and_empty(gpu):
+    P = gpu.primitives
+    x = so.rng(9).normal(size=(64, 10)).astype(np.float32)
+    dx = _dev(gpu, x)
+    np.testing.assert_allclose(P.softmax(dx).numpy(), so.softmax(x), atol=1e-6)
+    empty = gpu.DeviceArray((0, 10), "f32")
+    P.softmax(empty)
+    P.relu(empty)
+
+
+def test_convert_rounding_matches_host(gpu):
+    from spiral_b200 import dtypes
+    x = (so.rng(10).normal(size=4099) * 10).astype(np.float32)
+    dx = _dev(gpu, x)
+    for tag, rounder in (("bf16", dtypes.round_bf16), ("f16", dtypes.round_f16), ("tf32", dtypes.round_tf32)):
+        out = gpu.DeviceArray(x.shape, tag)
+        got = gpu.primitives.convert(dx, out).numpy()
+        np.testing.assert_array_equal(got, rounder(x))

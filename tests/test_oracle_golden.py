@@ -1,0 +1,115 @@
+"""The NumPy oracle against the reference's own golden console outputs (CPU only).
+
+Fixtures: tests/golden/primitives_golden.npz, extracted by tests/golden/make_golden.py
+from the reference's test_text_outputs/primitives/{test2,test3}/{a,b}.  The
+printed values carry six decimals, hence the 2e-6 absolute tolerance.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import spiral_oracle as so
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "primitives_golden.npz"))
+ATOL = 2e-6
+
+
+@pytest.mark.parametrize("sub", ["a", "b"])
+def test_softmax_matches_reference_output(sub):
+    x = GOLD["t2%s_input" % sub]
+    np.testing.assert_allclose(so.softmax(x), GOLD["t2%s_softmax" % sub], atol=ATOL, rtol=0)
+
+
+@pytest.mark.parametrize("sub", ["a", "b"])
+@pytest.mark.parametrize("size", [4, 11])
+def test_masked_softmax_matches_reference_output(sub, size):
+    x = GOLD["t2%s_input" % sub]
+    got = so.masked_softmax(x, so.prefix_mask(x.shape, size))
+    np.testing.assert_allclose(got, GOLD["t2%s_masked_softmax%d" % (sub, size)], atol=ATOL, rtol=0)
+    assert np.all(got[:, size:] == 0)
+
+
+@pytest.mark.parametrize("sub", ["a", "b"])
+def test_ln_l2_matches_reference_output(sub):
+    x = GOLD["t2%s_input" % sub]
+    np.testing.assert_allclose(so.ln_l2(x), GOLD["t2%s_ln_l2" % sub], atol=ATOL, rtol=0)
+
+
+@pytest.mark.parametrize("sub", ["a", "b"])
+def test_argmax_matches_reference_output(sub):
+    x = GOLD["t2%s_input" % sub]
+    want = GOLD["t2%s_argmax" % sub][: x.shape[0]]
+    # the printed inputs are rounded to 6 decimals; only rows with a clear winner are decisive
+    top2 = np.sort(x, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 2e-6
+    assert clear.sum() >= x.shape[0] - 1
+    np.testing.assert_array_equal(so.argmax(x)[clear], want[clear])
+
+
+@pytest.mark.parametrize("sub", ["a", "b"])
+def test_masked_regret_matching_matches_reference_output(sub):
+    x = GOLD["t3%s_input" % sub]
+    got = so.masked_regret_matching(x, so.prefix_mask(x.shape, 3))
+    np.testing.assert_allclose(got, GOLD["t3%s_masked_regret3" % sub], atol=ATOL, rtol=0)
+
+
+def test_regret_matching_uniform_when_nothing_positive():
+    x = -np.abs(np.random.default_rng(0).normal(size=(5, 7))).astype(np.float32)
+    mask = np.zeros((5, 7), bool)
+    mask[:, [1, 4, 5]] = True
+    got = so.masked_regret_matching(x, mask)
+    np.testing.assert_allclose(got[:, [1, 4, 5]], 1 / 3, rtol=1e-6)
+    assert np.all(got[:, [0, 2, 3, 6]] == 0)
+
+
+def test_max_and_mean_subtraction_agree():
+    x = np.random.default_rng(1).normal(size=(64, 10)).astype(np.float32)
+    mask = np.random.default_rng(2).random((64, 10)) < 0.6
+    mask[:, 0] = True
+    ref = so.masked_softmax(x, mask)
+    xm = np.where(mask, x, -np.inf)
+    e = np.exp(xm - xm.max(axis=1, keepdims=True))
+    alt = e / e.sum(axis=1, keepdims=True)
+    np.testing.assert_allclose(ref, alt, atol=1e-6)
+
+
+def test_matmul_layout_flags():
+    g = np.random.default_rng(3)
+    a = g.normal(size=(5, 7)).astype(np.float32)
+    b = g.normal(size=(7, 3)).astype(np.float32)
+    c = g.normal(size=(5, 3)).astype(np.float32)
+    want = 2 * a.astype(np.float64) @ b.astype(np.float64) + 0.5 * c
+    for at in (False, True):
+        for bt in (False, True):
+            aa = np.ascontiguousarray(a.T) if at else a
+            bb = np.ascontiguousarray(b.T) if bt else b
+            np.testing.assert_allclose(so.matmul(at, bt, 2.0, aa, bb, 0.5, c), want, rtol=1e-6)
+
+
+def test_input_rounding_classes():
+    x = np.float32([1.0 + 2 ** -9, 1.0 + 2 ** -12, 3.14159265])
+    assert so.round_bf16(x)[0] in (np.float32(1.0), np.float32(1.0 + 2 ** -7))
+    assert so.round_tf32(x)[1] == np.float32(1.0)
+    assert abs(so.round_tf32(x)[2] - x[2]) <= 2 ** -10
+    assert so.round_f16(x)[2] == np.float32(np.float16(x[2]))
+
+
+def test_train_step_gradient_matches_finite_difference():
+    sizes = [6, 8, 4]
+    ws, bs = so.mlp_weights(5, sizes)
+    g = so.rng(6)
+    x = g.normal(size=(16, 6)).astype(np.float32)
+    mask = np.ones((16, 4), np.uint8)
+    mask[::2, 3] = 0
+    tgt = so.random_target(7, mask)
+    _, _, loss, grads = so.mlp_train_step(x, ws, bs, mask, tgt, 0.0)
+    eps = 1e-3
+    for (li, i, j) in [(0, 2, 3), (1, 1, 5), (1, 3, 0)]:
+        wp = [w.copy() for w in ws]
+        wp[li][i, j] += eps
+        lp = so.cross_entropy_loss(so.mlp_forward(x, wp, bs, mask), tgt, mask)
+        wm = [w.copy() for w in ws]
+        wm[li][i, j] -= eps
+        lm = so.cross_entropy_loss(so.mlp_forward(x, wm, bs, mask), tgt, mask)
+        assert abs((lp - lm) / (2 * eps) - grads[li][0][i, j]) < 2e-3
