@@ -80,6 +80,16 @@ int sb_event_elapsed_ms(void* start, void* stop, float* ms);  /* syncs on stop *
  * waits: status[0] = first wait site that expired (0 = healthy), status[1] =
  * count of expired waits.  Synchronises the device. */
 int sb_device_status(int* status2, int clear);
+/* Number of kernels this library has launched in this process so far. */
+unsigned long long sb_launch_count(void);
+/* Device-side timing of the tensor-core GEMM launches between begin and end:
+ * a CUDA event pair is recorded around each launch on its own stream (at most
+ * 4096 launches).  end synchronises and returns the launch count, the summed
+ * kernel time and the summed algorithmic flops (2*M*N*K each).  Stands where
+ * the reference times by hand with time.perf_counter around a synchronised
+ * launch (game/leduc/full.spi:21-34). */
+int sb_gemm_profile_begin(void);
+int sb_gemm_profile_end(int* launches, double* total_ms, double* total_flops);
 
 /* ---- GEMM ---------------------------------------------------------------
  * C[M,N] <- alpha * op(A) * op(B) + beta * C, row-major, in place.
@@ -121,6 +131,58 @@ int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream); 
  * SB_F16 -> 16-bit; SB_TF32 -> fp32 with the low 13 mantissa bits cleared,
  * round-to-nearest-even). */
 int sb_convert(const float* x, void* out, size_t n, int out_dtype, void* stream);
+
+/* ---- dense policy network ---------------------------------------------------
+ * A ReLU MLP `sizes[0] -> sizes[1] -> ... -> sizes[n_layers]` with a row head
+ * on the last layer; every layer is y = x W^T (+ b) with W stored [out, in]
+ * (layers.matmul, ml/layers.spi:227-240,467).  All buffers are caller-owned,
+ * like the reference's weight / workspace / adjoint arenas
+ * (ml/layers.spi:6-12,127-172).
+ *
+ * Parameter layout: one flat vector [W0 | b0 | W1 | b1 | ...]; offsets (in
+ * elements) from sb_mlp_param_offsets: offsets[2i] = W_i, offsets[2i+1] = b_i,
+ * offsets[2*n_layers] = total length.  A weight segment holds
+ * round_up(out, 8) rows (padding rows must be zero and stay zero).  `params`
+ * is the fp32 master copy, `w_compute` the same layout in the storage type of
+ * `in_dtype` (SB_TF32: fp32 rounded to TF32; SB_BF16; SB_F16). */
+int sb_mlp_param_offsets(int n_layers, const int* sizes, long long* offsets);
+
+/* Forward pass; replaces graph_run_host / graph_run_device for a dense chain
+ * (ml/layers.spi:339-344, generated block_matmul/block_map/block_row_map
+ * sequence ml/layers.py:4500-4546).  x: [batch, sizes[0]] in the storage type;
+ * activations: host array of n_layers-1 device pointers, activations[i] =
+ * [batch, sizes[i+1]] in the storage type (workspace, overwritten); params may
+ * be NULL (no bias, as in the reference); head: SB_EPI_MASKED_SOFTMAX |
+ * SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX; out: fp32 [batch, sizes[n_layers]];
+ * actions: int32 [batch] when SB_EPI_ARGMAX. */
+int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                   const void* w_compute, const float* params, void* const* activations, int head,
+                   const uint8_t* mask, float* out, int32_t* actions, void* stream);
+
+/* Backward pass of mean cross-entropy over `1/inv_global_batch` rows on a
+ * masked-softmax head, after sb_mlp_forward with SB_EPI_MASKED_SOFTMAX on the
+ * same buffers.  No counterpart in the reference (it trains by CEM / CFR,
+ * ml/cem.spi:99-146).  Writes the flat fp32 gradient vector `grads` (layout of
+ * sb_mlp_param_offsets, padding zeroed) -- the buffer a data-parallel caller
+ * all-reduces -- and adds this shard's share of the loss to *loss (device
+ * float, caller zeroes it; NULL to skip).  scratch: 256-byte aligned, at least
+ * sb_mlp_backward_scratch_bytes. */
+int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int in_dtype, size_t* bytes);
+int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                    const void* x, const void* w_compute, void* const* activations,
+                    const float* probs, const uint8_t* mask, const float* target, float* grads,
+                    int with_bias, void* scratch, size_t scratch_bytes, float* loss, void* stream);
+
+/* params -= lr * grads over n elements, and w_compute (may be NULL) = params
+ * rounded to compute_dtype.  No counterpart in the reference. */
+int sb_sgd_update(float* params, const float* grads, void* w_compute, long long n, float lr,
+                  int compute_dtype, void* stream);
+
+/* Single-GPU training step: forward, backward over this batch, SGD. */
+int sb_mlp_train_step(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                      float* params, void* w_compute, void* const* activations, const uint8_t* mask,
+                      const float* target, float* probs, float* grads, int with_bias, float lr,
+                      void* scratch, size_t scratch_bytes, float* loss, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,7 +8,7 @@
 int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
-                        void* aux_out, cudaStream_t stream);
+                        void* aux_out, cudaStream_t stream, int splits = 1, int* splits_used = nullptr);
 int sb_umma_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, int sms, int* plan5);
 int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStream_t stream);
 int sb_umma_head_max_n();
@@ -44,7 +44,7 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
   if (M < 0 || N < 0 || K < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: negative dimension (M=%d N=%d K=%d)", M, N, K);
   if (in_dtype != SB_F32 && in_dtype != SB_TF32 && in_dtype != SB_BF16 && in_dtype != SB_F16)
     return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: unknown input dtype %d", in_dtype);
-  if (out_dtype != SB_F32 && out_dtype != SB_BF16 && out_dtype != SB_F16)
+  if (out_dtype != SB_F32 && out_dtype != SB_BF16 && out_dtype != SB_F16 && out_dtype != SB_TF32)
     return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: unknown output dtype %d", out_dtype);
   if (epilogue & ~ALL_FLAGS) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: unknown epilogue flag in 0x%x", epilogue);
   if (M == 0 || N == 0) return SB_OK;
@@ -53,6 +53,7 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
   if ((epilogue & SB_EPI_BIAS) && !bias) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_BIAS without a bias pointer");
   if ((epilogue & SB_EPI_RELU_GRAD) && !aux_in) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_RELU_GRAD without aux_in");
   if ((epilogue & SB_EPI_ARGMAX) && !aux_out) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_ARGMAX without aux_out");
+  if (in_dtype == SB_F32 && out_dtype == SB_TF32) out_dtype = SB_F32;
   if ((epilogue & HEAD_FLAGS) && out_dtype != SB_F32)
     return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: row heads write fp32 output only");
   if ((epilogue & HEAD_FLAGS) && (epilogue & SB_EPI_RELU_GRAD))

@@ -45,6 +45,16 @@ enum SbWaitSite : int {
   SB_SITE_DRAIN = 8,
 };
 
+// Launch accounting: every kernel launch of the library goes through
+// SB_COUNT_LAUNCH so that a host can report how many kernels a region issued.
+extern unsigned long long g_sb_launch_count;
+#define SB_COUNT_LAUNCH() (++g_sb_launch_count)
+
+// Optional GEMM profiling: when enabled, the tensor-core GEMM launcher records
+// a CUDA event pair around each launch on the launching stream.
+void sb_prof_before(cudaStream_t s);
+void sb_prof_after(cudaStream_t s, double flops);
+
 static inline int sb_dtype_size(int dt) {
   switch (dt) {
     case SB_F32: case SB_TF32: return 4;

@@ -95,6 +95,7 @@ int sb_sgemm_launch(int a_trans, int b_trans, float alpha, const float* A, const
     sgemm_kernel<false, true><<<grid, F_THREADS, 0, stream>>>(A, B, C, M, N, K, alpha, beta, epi, bias);
   else
     sgemm_kernel<false, false><<<grid, F_THREADS, 0, stream>>>(A, B, C, M, N, K, alpha, beta, epi, bias);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

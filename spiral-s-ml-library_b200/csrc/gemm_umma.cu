@@ -45,6 +45,10 @@ struct UmmaGemmParams {
   int block_k;  // elements of K per stage
   int k_blocks;
   int tiles_m, tiles_n, num_tiles;
+  int splits;          // split-K factor: work item = (split, tile); 1 = no split
+  int kb_per_split;    // k-blocks per split
+  int num_work;        // num_tiles * splits
+  long long split_stride;  // elements between the partial outputs of two splits
   uint32_t idesc;
   uint32_t a_stage_bytes, b_stage_bytes;
   int a_boxes, b_boxes;    // TMA boxes per stage (1 when K-major)
@@ -98,13 +102,22 @@ __device__ __forceinline__ __nv_bfloat16 float_to<__nv_bfloat16>(float v) {
 template <>
 __device__ __forceinline__ __half float_to<__half>(float v) { return __float2half_rn(v); }
 
+__device__ __forceinline__ float round_tf32_rn(float v) {
+  uint32_t u = __float_as_uint(v);
+  if ((u & 0x7f800000u) == 0x7f800000u) return v;
+  u += 0x0fffu + ((u >> 13) & 1u);
+  return __uint_as_float(u & 0xffffe000u);
+}
+
 // One thread finishes `w` (16 or 32) consecutive columns of its output row.
-template <typename OutT>
+// ROUND_TF32: fp32 output rounded to 10 mantissa bits (nearest even), so that a
+// following TF32 GEMM reads exactly the value stored.
+template <typename OutT, bool ROUND_TF32>
 __device__ __forceinline__ void finish_chunk(const UmmaGemmParams& p, float* v, int w, long long row,
-                                             int col0) {
+                                             int col0, long long c_off) {
   const int valid = min(w, p.N - col0);
   if (valid <= 0) return;
-  OutT* crow = reinterpret_cast<OutT*>(p.C) + row * p.ldc + col0;
+  OutT* crow = reinterpret_cast<OutT*>(p.C) + c_off + row * p.ldc + col0;
   const OutT* arow = reinterpret_cast<const OutT*>(p.aux_in) + row * p.ldc + col0;
   constexpr int VEC = 16 / sizeof(OutT);
   const bool vec_ok = (valid == w) && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
@@ -149,6 +162,7 @@ __device__ __forceinline__ void finish_chunk(const UmmaGemmParams& p, float* v, 
         if (has_bias) x += (j0 + t < valid) ? __ldg(p.bias + col0 + j0 + t) : 0.f;
         if (relu) x = fmaxf(x, 0.f);
         if (relu_grad) x = act[t] > 0.f ? x : 0.f;
+        if (ROUND_TF32) x = round_tf32_rn(x);
         outv[t] = float_to<OutT>(x);
       }
       if (vec_ok) {
@@ -291,12 +305,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x) {
+        const int split = work / p.num_tiles;
         int m_blk, n_blk;
-        tile_coords(p, tile, m_blk, n_blk);
+        tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
         const int m0 = m_blk * UG_BLOCK_M;
         const int n0 = n_blk * p.block_n;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int kb_begin = split * p.kb_per_split;
+        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, SB_SITE_PRODUCER_EMPTY)) {
             ok = false;
             break;
@@ -338,14 +355,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       //           types, 512 (4 rows) for the 32-byte-chunk swizzle of TF32.
       const uint32_t a_lbo = p.a_mn ? p.mn_box_bytes : 16u;
       const uint32_t b_lbo = p.b_mn ? p.mn_box_bytes : 16u;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x) {
+        const int split = work / p.num_tiles;
+        const int kb_begin = split * p.kb_per_split;
+        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
         if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, abortp, SB_SITE_MMA_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, SB_SITE_MMA_FULL)) {
             ok = false;
             break;
@@ -357,7 +377,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t b_desc = umma_smem_desc(b_src, b_lbo, p.b_sbo, p.b_layout);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+            const uint32_t accumulate = (kb > kb_begin || ks > 0) ? 1u : 0u;
             const uint64_t ad = a_desc + (uint64_t)(ks * p.a_kstep);
             const uint64_t bd = b_desc + (uint64_t)(ks * p.b_kstep);
             if (p.kind_tf32)
@@ -383,9 +403,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool head = (p.epi & EPI_HEAD_MASK) != 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    for (int work = blockIdx.x; work < p.num_work; work += gridDim.x) {
+      const int split = work / p.num_tiles;
+      const long long c_off = (long long)split * p.split_stride;
       int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
       if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
       tc_fence_after_sync();
       const long long row = (long long)m_blk * UG_BLOCK_M + quad * 32 + lane;
@@ -405,9 +427,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int col0 = n_blk * p.block_n + c0;
           if (row_ok) {
             float* v = reinterpret_cast<float*>(raw);
-            if (p.out_dtype == SB_F32) finish_chunk<float>(p, v, w, row, col0);
-            else if (p.out_dtype == SB_BF16) finish_chunk<__nv_bfloat16>(p, v, w, row, col0);
-            else finish_chunk<__half>(p, v, w, row, col0);
+            if (p.out_dtype == SB_F32) finish_chunk<float, false>(p, v, w, row, col0, c_off);
+            else if (p.out_dtype == SB_TF32) finish_chunk<float, true>(p, v, w, row, col0, c_off);
+            else if (p.out_dtype == SB_BF16) finish_chunk<__nv_bfloat16, false>(p, v, w, row, col0, c_off);
+            else finish_chunk<__half, false>(p, v, w, row, col0, c_off);
           }
         }
       }
@@ -531,6 +554,10 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms) {
   p.block_n = best_bn;
   p.tiles_n = (p.N + p.block_n - 1) / p.block_n;
   p.num_tiles = p.tiles_m * p.tiles_n;
+  p.splits = 1;
+  p.kb_per_split = p.k_blocks;
+  p.num_work = p.num_tiles;
+  p.split_stride = 0;
   p.acc_stride = next_pow2(p.block_n);
   p.tmem_cols = next_pow2(2 * p.acc_stride);
   p.a_stage_bytes = UG_BLOCK_M * 128u;
@@ -567,7 +594,7 @@ __global__ void scale_rows_kernel(void* C, long long total, float beta, int out_
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long step = (long long)gridDim.x * blockDim.x;
   for (; i < total; i += step) {
-    if (out_dtype == SB_F32) {
+    if (out_dtype == SB_F32 || out_dtype == SB_TF32) {
       float* c = reinterpret_cast<float*>(C);
       c[i] = beta == 0.f ? 0.f : beta * c[i];
     } else if (out_dtype == SB_BF16) {
@@ -587,7 +614,7 @@ __global__ void scale_rows_kernel(void* C, long long total, float beta, int out_
 int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
-                        void* aux_out, cudaStream_t stream) {
+                        void* aux_out, cudaStream_t stream, int splits, int* splits_used) {
   const int es = sb_dtype_size(in_dtype);
   UmmaGemmParams p;
   memset(&p, 0, sizeof(p));
@@ -627,8 +654,21 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
                                  UG_SMEM_LIMIT - 1024));
     attr_set[dev] = true;
   }
-  const int grid = min(p.num_tiles, cached_sm_count());
+  if (splits > 1) {
+    // Split-K: each split writes its own [M,N] partial at C + split * M * N.
+    int kbps = (p.k_blocks + splits - 1) / splits;
+    if (kbps < 1) kbps = 1;
+    p.kb_per_split = kbps;
+    p.splits = (p.k_blocks + kbps - 1) / kbps;   // every split owns at least one k-block
+    p.num_work = p.num_tiles * p.splits;
+    p.split_stride = (long long)M * N;
+  }
+  if (splits_used) *splits_used = p.splits;
+  const int grid = min(p.num_work, cached_sm_count());
+  sb_prof_before(stream);
   umma_gemm_kernel<<<grid, UG_THREADS, smem, stream>>>(ta, tb, p);
+  sb_prof_after(stream, 2.0 * M * N * K);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -653,6 +693,7 @@ int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStr
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   scale_rows_kernel<<<(int)blocks, 256, 0, stream>>>(C, total, beta, out_dtype);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

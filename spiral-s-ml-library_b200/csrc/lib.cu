@@ -6,3 +6,4 @@
 #include "gemm_fp32.cu"
 #include "gemm_umma.cu"
 #include "api.cu"
+#include "mlp.cu"

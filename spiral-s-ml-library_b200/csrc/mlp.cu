@@ -1,0 +1,366 @@
+// Dense policy-network path: forward chain, backward (cross-entropy on a masked
+// softmax head), split-K weight gradients and the fused SGD update.
+//
+// Forward replaces the per-node device functions the reference's graph
+// interpreter emits (BlockMatmul -> BlockMap relu -> BlockRowMap head,
+// ml/layers.spi:181-252, one global-memory pass per node): here every layer is
+// one tensor-core GEMM whose epilogue applies bias, ReLU, the storage rounding
+// of the next layer's input and, on the last layer, the row head.
+//
+// The reference has no backward pass, loss or optimiser (its training is CEM /
+// tabular CFR, ml/cem.spi:99-146); dgrad (NN), wgrad (TN) and SGD below follow
+// the benchmark's training configurations and are pinned by the NumPy oracle.
+//
+// Memory model (caller-owned, as in ml/layers.spi:127-172): a flat fp32 master
+// parameter buffer [W0 | b0 | W1 | b1 | ...] with 64-element aligned segments,
+// a compute copy of the same layout in the storage type of the arithmetic class,
+// a flat fp32 gradient buffer of the same layout (the unit of the data-parallel
+// all-reduce), per-layer activation buffers and one scratch buffer.
+#include "common.cuh"
+
+int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
+                        float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
+                        int epi, const float* bias, const uint8_t* mask, const void* aux_in,
+                        void* aux_out, cudaStream_t stream, int splits, int* splits_used);
+int sb_umma_head_max_n();
+
+namespace {
+
+constexpr int MLP_MAX_LAYERS = 16;
+constexpr long long SEG_ALIGN = 64;  // elements; 256 B in fp32, 128 B in 16-bit storage
+
+long long align_up(long long x, long long a) { return (x + a - 1) / a * a; }
+
+int storage_dtype(int in_dtype) { return in_dtype == SB_TF32 ? SB_TF32 : in_dtype; }
+
+int check_layout(const char* who, int n_layers, const int* sizes, int batch, int in_dtype) {
+  if (n_layers < 1 || n_layers > MLP_MAX_LAYERS) return sb_fail(SB_ERR_BAD_ARG, "%s: n_layers must be in [1, %d]", who, MLP_MAX_LAYERS);
+  if (!sizes) return sb_fail(SB_ERR_BAD_ARG, "%s: sizes is null", who);
+  for (int i = 0; i <= n_layers; ++i)
+    if (sizes[i] < 1) return sb_fail(SB_ERR_BAD_ARG, "%s: sizes[%d] = %d", who, i, sizes[i]);
+  if (batch < 0) return sb_fail(SB_ERR_BAD_ARG, "%s: negative batch", who);
+  if (in_dtype != SB_TF32 && in_dtype != SB_BF16 && in_dtype != SB_F16)
+    return sb_fail(SB_ERR_UNSUPPORTED, "%s: arithmetic class must be SB_TF32, SB_BF16 or SB_F16", who);
+  return SB_OK;
+}
+
+// Rows of a weight segment: the fan-out padded to a multiple of 8 so that the
+// transposed uses of dY (wgrad A operand, dgrad inner dimension) have 16-byte
+// row pitches.  Padding rows stay zero: their gradients are zero.
+int padded_out(int fan_out) { return (fan_out + 7) / 8 * 8; }
+
+void param_offsets(int n_layers, const int* sizes, long long* off) {
+  long long cur = 0;
+  for (int i = 0; i < n_layers; ++i) {
+    off[2 * i] = cur;
+    cur = align_up(cur + (long long)padded_out(sizes[i + 1]) * sizes[i], SEG_ALIGN);
+    off[2 * i + 1] = cur;
+    cur = align_up(cur + sizes[i + 1], SEG_ALIGN);
+  }
+  off[2 * n_layers] = cur;
+}
+
+// d logits of cross-entropy(masked softmax): (p * sum(t) - t) / global_batch on
+// legal entries, 0 elsewhere; also accumulates the loss.  One thread per row.
+template <typename DyT, bool ROUND_TF32>
+__global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __restrict__ target,
+                               const uint8_t* __restrict__ mask, DyT* __restrict__ dy, int rows, int n,
+                               int ld, float inv_batch, float* __restrict__ loss) {
+  float local = 0.f;
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const float* pr = probs + r * n;
+    const float* tr = target + r * n;
+    const uint8_t* mr = mask ? mask + r * n : nullptr;
+    float tsum = 0.f;
+    for (int j = 0; j < n; ++j)
+      if (!mr || mr[j]) tsum += tr[j];
+    for (int j = 0; j < ld; ++j) {
+      const bool lg = j < n && (!mr || mr[j]);
+      float g = 0.f;
+      if (lg) {
+        const float pj = pr[j], tj = tr[j];
+        g = (pj * tsum - tj) * inv_batch;
+        local -= tj * __logf(fmaxf(pj, 1e-38f));
+      }
+      if (ROUND_TF32) {
+        uint32_t u = __float_as_uint(g);
+        u += 0x0fffu + ((u >> 13) & 1u);
+        g = __uint_as_float(u & 0xffffe000u);
+      }
+      if (sizeof(DyT) == 4) reinterpret_cast<float*>(dy)[r * ld + j] = g;
+      else if (sizeof(DyT) == 2) dy[r * ld + j] = (DyT)g;
+    }
+  }
+  if (loss) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if ((threadIdx.x & 31) == 0 && local != 0.f) atomicAdd(loss, local * inv_batch);
+  }
+}
+
+// Column sums of dY [rows, n] -> db[n] (bias gradient).  Each block owns a slab
+// of rows and a 32-column strip; partial sums are combined with atomics into a
+// zeroed output, so db is summed in a run-dependent order (fp32, few terms).
+template <typename DyT>
+__global__ void colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int n,
+                              int rows_per_block) {
+  __shared__ float part[8][33];
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  float s = 0.f;
+  if (col < n)
+    for (int r = r0 + (threadIdx.x >> 5); r < r1; r += 8) s += (float)dy[(long long)r * n + col];
+  part[threadIdx.x >> 5][threadIdx.x & 31] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += part[w][threadIdx.x];
+    if (col < n && t != 0.f) atomicAdd(db + col, t);
+  }
+}
+
+// grads[i] = sum over splits of partial[s][i]; deterministic order.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                     long long n, int splits) {
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partial[(long long)k * n + i];
+    out[i] = s;
+  }
+}
+
+// params -= lr * grads ; compute copy = params rounded to the storage type.
+__global__ void sgd_kernel(float* __restrict__ params, const float* __restrict__ grads,
+                           void* __restrict__ compute, long long n, float lr, int dt) {
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const float w = params[i] - lr * grads[i];
+    params[i] = w;
+    if (!compute) continue;
+    if (dt == SB_BF16) reinterpret_cast<__nv_bfloat16*>(compute)[i] = __float2bfloat16_rn(w);
+    else if (dt == SB_F16) reinterpret_cast<__half*>(compute)[i] = __float2half_rn(w);
+    else if (dt == SB_TF32) {
+      uint32_t u = __float_as_uint(w);
+      if ((u & 0x7f800000u) != 0x7f800000u) { u += 0x0fffu + ((u >> 13) & 1u); u &= 0xffffe000u; }
+      reinterpret_cast<float*>(compute)[i] = __uint_as_float(u);
+    } else reinterpret_cast<float*>(compute)[i] = w;
+  }
+}
+
+int blocks_for(long long n, int per_block, int cap = 148 * 8) {
+  long long b = (n + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  return (int)(b > cap ? cap : b);
+}
+
+// Split factor of a wgrad GEMM [out, in] with inner dimension = batch.
+int wgrad_splits(int out, int in, int batch, int in_dtype) {
+  const int es = sb_dtype_size(in_dtype);
+  const int block_k = 128 / es;
+  const int k_blocks = (batch + block_k - 1) / block_k;
+  const int tiles = ((out + 127) / 128) * ((in + 255) / 256);
+  int s = 148 / (tiles > 0 ? tiles : 1);
+  if (s < 1) s = 1;
+  const int max_by_k = k_blocks / 8 > 0 ? k_blocks / 8 : 1;  // keep >= 8 k-blocks per split
+  if (s > max_by_k) s = max_by_k;
+  if (s > 128) s = 128;
+  return s;
+}
+
+size_t backward_scratch_bytes(int n_layers, const int* sizes, int batch, int in_dtype) {
+  const int es = sb_dtype_size(in_dtype);
+  int max_w = 0;
+  long long max_partial = 0;
+  for (int i = 0; i < n_layers; ++i) {
+    const int op = padded_out(sizes[i + 1]);
+    if (op > max_w) max_w = op;
+    const long long p = (long long)wgrad_splits(op, sizes[i], batch, in_dtype) * op * sizes[i];
+    if (p > max_partial) max_partial = p;
+  }
+  const size_t dy = (size_t)align_up((long long)batch * max_w * es, 256);
+  return 2 * dy + (size_t)max_partial * 4 + 256;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sb_mlp_param_offsets(int n_layers, const int* sizes, long long* offsets) {
+  if (!offsets) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_param_offsets: null output");
+  int rc = check_layout("sb_mlp_param_offsets", n_layers, sizes, 0, SB_BF16);
+  if (rc != SB_OK) return rc;
+  param_offsets(n_layers, sizes, offsets);
+  return SB_OK;
+}
+
+int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                   const void* w_compute, const float* params, void* const* activations, int head,
+                   const uint8_t* mask, float* out, int32_t* actions, void* stream) {
+  int rc = check_layout("sb_mlp_forward", n_layers, sizes, batch, in_dtype);
+  if (rc != SB_OK) return rc;
+  if (batch == 0) return SB_OK;
+  if (!x || !w_compute || !out) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward: null pointer");
+  if (n_layers > 1 && !activations) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward: activations is null");
+  if (head & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX))
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward: head may hold only row-head flags");
+  if ((head & SB_EPI_ARGMAX) && !actions) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward: SB_EPI_ARGMAX without an actions buffer");
+  long long off[2 * MLP_MAX_LAYERS + 1];
+  param_offsets(n_layers, sizes, off);
+  const int es = sb_dtype_size(in_dtype);
+  const int st = storage_dtype(in_dtype);
+  const void* h = x;
+  for (int i = 0; i < n_layers; ++i) {
+    const bool last = i == n_layers - 1;
+    const void* w = reinterpret_cast<const char*>(w_compute) + off[2 * i] * es;
+    const float* b = params ? params + off[2 * i + 1] : nullptr;
+    int epi = b ? SB_EPI_BIAS : 0;
+    void* dst;
+    int odt;
+    if (last) {
+      epi |= head;
+      dst = out;
+      odt = SB_F32;
+    } else {
+      if (!activations[i]) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward: activations[%d] is null", i);
+      epi |= SB_EPI_RELU;
+      dst = activations[i];
+      odt = st;
+    }
+    rc = sb_matmul_ex(0, 1, 1.0f, h, w, 0.0f, dst, batch, sizes[i + 1], sizes[i], in_dtype, odt, epi, b,
+                      last ? mask : nullptr, nullptr, last ? actions : nullptr, stream);
+    if (rc != SB_OK) return rc;
+    h = dst;
+  }
+  return SB_OK;
+}
+
+int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int in_dtype, size_t* bytes) {
+  if (!bytes) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward_scratch_bytes: null output");
+  int rc = check_layout("sb_mlp_backward_scratch_bytes", n_layers, sizes, batch, in_dtype);
+  if (rc != SB_OK) return rc;
+  *bytes = backward_scratch_bytes(n_layers, sizes, batch, in_dtype);
+  return SB_OK;
+}
+
+int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                    const void* x, const void* w_compute, void* const* activations,
+                    const float* probs, const uint8_t* mask, const float* target, float* grads,
+                    int with_bias, void* scratch, size_t scratch_bytes, float* loss, void* stream) {
+  int rc = check_layout("sb_mlp_backward", n_layers, sizes, batch, in_dtype);
+  if (rc != SB_OK) return rc;
+  if (!grads) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: grads is null");
+  long long off[2 * MLP_MAX_LAYERS + 1];
+  param_offsets(n_layers, sizes, off);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (batch == 0) {
+    SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+    return SB_OK;
+  }
+  if (!x || !w_compute || !probs || !target || !scratch)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: null pointer");
+  if (n_layers > 1 && !activations) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: activations is null");
+  for (int i = 1; i < n_layers; ++i)
+    if (sizes[i] % 8 != 0)
+      return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_backward: hidden width %d is not a multiple of 8", sizes[i]);
+  const size_t need = backward_scratch_bytes(n_layers, sizes, batch, in_dtype);
+  if (scratch_bytes < need)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: scratch of %zu bytes, %zu needed", scratch_bytes, need);
+  if (reinterpret_cast<uintptr_t>(scratch) & 255) return sb_fail(SB_ERR_MISALIGNED, "sb_mlp_backward: scratch must be 256-byte aligned");
+  const int es = sb_dtype_size(in_dtype);
+  const int st = storage_dtype(in_dtype);
+  int max_w = 0;
+  for (int i = 0; i < n_layers; ++i) max_w = max(max_w, padded_out(sizes[i + 1]));
+  const size_t dy_bytes = (size_t)align_up((long long)batch * max_w * es, 256);
+  char* sc = reinterpret_cast<char*>(scratch);
+  void* dy_cur = sc;
+  void* dy_next = sc + dy_bytes;
+  float* partial = reinterpret_cast<float*>(sc + 2 * dy_bytes);
+
+  // Bias gradients are accumulated with atomics into zeroed memory; weight
+  // gradients are overwritten.  Zero the whole buffer (padding included) so that
+  // the all-reduce and the SGD update can treat it as one flat vector.
+  SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+
+  const int n_out = sizes[n_layers];
+  const int ld_out = padded_out(n_out);
+  {
+    const int blocks = blocks_for(batch, 256);
+    if (in_dtype == SB_BF16)
+      ce_grad_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(probs, target, mask, (__nv_bfloat16*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
+    else if (in_dtype == SB_F16)
+      ce_grad_kernel<__half, false><<<blocks, 256, 0, s>>>(probs, target, mask, (__half*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
+    else
+      ce_grad_kernel<float, true><<<blocks, 256, 0, s>>>(probs, target, mask, (float*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
+    SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  }
+
+  for (int i = n_layers - 1; i >= 0; --i) {
+    const int fan_out = padded_out(sizes[i + 1]), fan_in = sizes[i];
+    const void* h_in = i == 0 ? x : activations[i - 1];
+    if (with_bias) {
+      const int rows_per_block = 2048;
+      dim3 grid((fan_out + 31) / 32, (batch + rows_per_block - 1) / rows_per_block);
+      float* db = grads + off[2 * i + 1];
+      if (in_dtype == SB_BF16) colsum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy_cur, db, batch, fan_out, rows_per_block);
+      else if (in_dtype == SB_F16) colsum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)dy_cur, db, batch, fan_out, rows_per_block);
+      else colsum_kernel<float><<<grid, 256, 0, s>>>((const float*)dy_cur, db, batch, fan_out, rows_per_block);
+      SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+    }
+    // wgrad (TN): dW[out, in] = dY^T [out, B] * H_in [B, in]
+    float* dw = grads + off[2 * i];
+    const int want = wgrad_splits(fan_out, fan_in, batch, in_dtype);
+    int used = 1;
+    rc = sb_umma_gemm_launch(1, 0, 1.0f, dy_cur, h_in, 0.0f, want > 1 ? (void*)partial : (void*)dw, fan_out,
+                             fan_in, batch, in_dtype, SB_F32, 0, nullptr, nullptr, nullptr, nullptr, s, want, &used);
+    if (rc != SB_OK) return rc;
+    if (want > 1) {
+      const long long n = (long long)fan_out * fan_in;
+      splitk_reduce_kernel<<<blocks_for(n, 256), 256, 0, s>>>(partial, dw, n, used);
+      SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+    }
+    // dgrad (NN): dH[B, in] = dY [B, out] * W [out, in], gated by ReLU'(H_in)
+    if (i > 0) {
+      const void* w = reinterpret_cast<const char*>(w_compute) + off[2 * i] * es;
+      rc = sb_umma_gemm_launch(0, 0, 1.0f, dy_cur, w, 0.0f, dy_next, batch, fan_in, fan_out, in_dtype, st,
+                               SB_EPI_RELU_GRAD, nullptr, nullptr, h_in, nullptr, s, 1, nullptr);
+      if (rc != SB_OK) return rc;
+      void* t = dy_cur; dy_cur = dy_next; dy_next = t;
+    }
+  }
+  return SB_OK;
+}
+
+int sb_sgd_update(float* params, const float* grads, void* w_compute, long long n, float lr,
+                  int compute_dtype, void* stream) {
+  if (n < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_sgd_update: negative length");
+  if (n == 0) return SB_OK;
+  if (!params || !grads) return sb_fail(SB_ERR_BAD_ARG, "sb_sgd_update: null pointer");
+  sgd_kernel<<<blocks_for(n, 256), 256, 0, (cudaStream_t)stream>>>(params, grads, w_compute, n, lr, compute_dtype);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_mlp_train_step(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                      float* params, void* w_compute, void* const* activations, const uint8_t* mask,
+                      const float* target, float* probs, float* grads, int with_bias, float lr,
+                      void* scratch, size_t scratch_bytes, float* loss, void* stream) {
+  int rc = sb_mlp_forward(n_layers, sizes, batch, in_dtype, x, w_compute, with_bias ? params : nullptr,
+                          activations, SB_EPI_MASKED_SOFTMAX, mask, probs, nullptr, stream);
+  if (rc != SB_OK) return rc;
+  rc = sb_mlp_backward(n_layers, sizes, batch, batch > 0 ? 1.0f / (float)batch : 0.f, in_dtype, x, w_compute,
+                       activations, probs, mask, target, grads, with_bias, scratch, scratch_bytes, loss, stream);
+  if (rc != SB_OK) return rc;
+  long long off[2 * MLP_MAX_LAYERS + 1];
+  param_offsets(n_layers, sizes, off);
+  return sb_sgd_update(params, grads, w_compute, off[2 * n_layers], lr, storage_dtype(in_dtype), stream);
+}
+
+}  // extern "C"

@@ -170,6 +170,7 @@ int sb_relu(const float* x, float* out, size_t n, void* stream) {
   if (n == 0) return SB_OK;
   if (!x || !out) return sb_fail(SB_ERR_BAD_ARG, "sb_relu: null pointer");
   relu_kernel<<<grid_for((long long)(n / 4 + 1), 256), 256, 0, (cudaStream_t)stream>>>(x, out, n);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -186,6 +187,7 @@ int sb_row_softmax(const float* x, float* out, int rows, int cols, const uint8_t
   int rc = row_args_ok("sb_row_softmax", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   row_map_kernel<ROW_SOFTMAX><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, mask, prefix);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -195,6 +197,7 @@ int sb_row_regret_matching(const float* x, float* out, int rows, int cols, const
   int rc = row_args_ok("sb_row_regret_matching", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   row_map_kernel<ROW_REGRET><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, mask, prefix);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -203,6 +206,7 @@ int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream) {
   int rc = row_args_ok("sb_row_ln_l2", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   row_map_kernel<ROW_LN_L2><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, nullptr, -1);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -211,6 +215,7 @@ int sb_row_argmax(const float* x, int32_t* out, int rows, int cols, void* stream
   int rc = row_args_ok("sb_row_argmax", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   row_argmax_kernel<<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -221,6 +226,7 @@ int sb_convert(const float* x, void* out, size_t n, int out_dtype, void* stream)
   if (out_dtype != SB_BF16 && out_dtype != SB_F16 && out_dtype != SB_TF32 && out_dtype != SB_F32)
     return sb_fail(SB_ERR_BAD_ARG, "sb_convert: unknown output dtype %d", out_dtype);
   convert_kernel<<<grid_for((long long)n, 256), 256, 0, (cudaStream_t)stream>>>(x, out, n, out_dtype);
+  SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

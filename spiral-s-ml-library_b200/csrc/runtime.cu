@@ -9,6 +9,29 @@
 
 static thread_local char t_error[512] = "";
 
+unsigned long long g_sb_launch_count = 0;
+
+namespace {
+constexpr int PROF_MAX = 4096;
+bool g_prof_on = false;
+int g_prof_n = 0;
+cudaEvent_t g_prof_ev[2 * PROF_MAX];
+bool g_prof_ev_made = false;
+double g_prof_flops[PROF_MAX];
+}  // namespace
+
+void sb_prof_before(cudaStream_t s) {
+  if (!g_prof_on || g_prof_n >= PROF_MAX) return;
+  cudaEventRecord(g_prof_ev[2 * g_prof_n], s);
+}
+
+void sb_prof_after(cudaStream_t s, double flops) {
+  if (!g_prof_on || g_prof_n >= PROF_MAX) return;
+  cudaEventRecord(g_prof_ev[2 * g_prof_n + 1], s);
+  g_prof_flops[g_prof_n] = flops;
+  ++g_prof_n;
+}
+
 void sb_set_error(const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -165,6 +188,35 @@ int sb_event_elapsed_ms(void* start, void* stop, float* ms) {
   if (!start || !stop || !ms) return sb_fail(SB_ERR_BAD_ARG, "sb_event_elapsed_ms: null argument");
   SB_CUDA(cudaEventSynchronize((cudaEvent_t)stop));
   SB_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+  return SB_OK;
+}
+
+unsigned long long sb_launch_count(void) { return g_sb_launch_count; }
+
+int sb_gemm_profile_begin(void) {
+  if (!g_prof_ev_made) {
+    for (int i = 0; i < 2 * PROF_MAX; ++i) SB_CUDA(cudaEventCreate(&g_prof_ev[i]));
+    g_prof_ev_made = true;
+  }
+  g_prof_n = 0;
+  g_prof_on = true;
+  return SB_OK;
+}
+
+int sb_gemm_profile_end(int* launches, double* total_ms, double* total_flops) {
+  g_prof_on = false;
+  double ms = 0.0, fl = 0.0;
+  for (int i = 0; i < g_prof_n; ++i) {
+    SB_CUDA(cudaEventSynchronize(g_prof_ev[2 * i + 1]));
+    float t = 0.f;
+    SB_CUDA(cudaEventElapsedTime(&t, g_prof_ev[2 * i], g_prof_ev[2 * i + 1]));
+    ms += t;
+    fl += g_prof_flops[i];
+  }
+  if (launches) *launches = g_prof_n;
+  if (total_ms) *total_ms = ms;
+  if (total_flops) *total_flops = fl;
+  g_prof_n = 0;
   return SB_OK;
 }
 

@@ -64,6 +64,9 @@ SIGNATURES = {
     "sb_event_record": (_I, [_P, _P]),
     "sb_event_elapsed_ms": (_I, [_P, _P, POINTER(c_float)]),
     "sb_device_status": (_I, [_IP, _I]),
+    "sb_launch_count": (ctypes.c_ulonglong, []),
+    "sb_gemm_profile_begin": (_I, []),
+    "sb_gemm_profile_end": (_I, [_IP, POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "sb_matmul_tf32": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _P]),
     "sb_matmul_ex": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "sb_matmul_plan": (_I, [_I, _I, _I, _I, _I, _I, _I, _IP]),
@@ -73,6 +76,12 @@ SIGNATURES = {
     "sb_row_argmax": (_I, [_P, _P, _I, _I, _P]),
     "sb_row_ln_l2": (_I, [_P, _P, _I, _I, _P]),
     "sb_convert": (_I, [_P, _P, _Z, _I, _P]),
+    "sb_mlp_param_offsets": (_I, [_I, _IP, POINTER(ctypes.c_longlong)]),
+    "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _I, _P, _P, _P, _P]),
+    "sb_mlp_backward_scratch_bytes": (_I, [_I, _IP, _I, _I, POINTER(c_size_t)]),
+    "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),
+    "sb_sgd_update": (_I, [_P, _P, _P, ctypes.c_longlong, _F, _I, _P]),
+    "sb_mlp_train_step": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _P, _P, _P, _P, _I, _F, _P, _Z, _P, _P]),
 }
 
 _lib = None

@@ -196,3 +196,25 @@ class Event:
                 self.ptr = None
         except Exception:
             pass
+
+
+def launch_count():
+    """Kernels launched by the library in this process so far."""
+    return int(_lib.load().sb_launch_count())
+
+
+class GemmProfile:
+    """Context manager: CUDA-event timing of every tensor-core GEMM launch inside the block."""
+
+    def __enter__(self):
+        _lib.call("sb_gemm_profile_begin")
+        self.launches, self.ms, self.flops = 0, 0.0, 0.0
+        return self
+
+    def __exit__(self, *exc):
+        n = ctypes.c_int(0)
+        ms = ctypes.c_double(0)
+        fl = ctypes.c_double(0)
+        _lib.call("sb_gemm_profile_end", ctypes.byref(n), ctypes.byref(ms), ctypes.byref(fl))
+        self.launches, self.ms, self.flops = n.value, ms.value, fl.value
+        return False

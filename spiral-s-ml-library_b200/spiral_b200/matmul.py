@@ -51,9 +51,7 @@ def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype=None, epilogue=(), b
     if (in_dtype in ("f32", "tf32")) != (storage in ("f32", "tf32")) or \
             (in_dtype in ("bf16", "f16") and in_dtype != storage):
         raise TypeError("in_dtype %s does not match the storage dtype %s" % (in_dtype, storage))
-    out_dtype = dtype_tag(c)
-    if out_dtype == "tf32":
-        out_dtype = "f32"
+    out_dtype = dtype_tag(c)   # a 'tf32'-tagged output is fp32 storage rounded to TF32
     epi = 0
     for name in epilogue:
         epi |= EPILOGUE_FLAGS[name]

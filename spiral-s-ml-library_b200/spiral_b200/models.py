@@ -1,0 +1,146 @@
+"""Dense policy network on the GPU: the caller of the GEMM path.
+
+Reference: ml/models.spi:9-76 (run a layer graph per decision) and the model
+graphs game/leduc/model_cem.spi:41-66, game/nl_hu_holdem/model_cem.spi:71-103
+(input -> matmul -> relu ... -> masked head).  ``PolicyMLP`` owns the buffers the
+reference keeps in its weight / workspace / adjoint arenas and drives
+sb_mlp_forward / sb_mlp_backward / sb_sgd_update.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from .device import DeviceArray, device_ptr, stream_ptr
+from . import dtypes
+
+HEAD_FLAGS = {"masked_softmax": _lib.EPI_MASKED_SOFTMAX, "regret_matching": _lib.EPI_REGRET_MATCHING,
+              "argmax": _lib.EPI_ARGMAX}
+
+
+def param_offsets(sizes):
+    """Element offsets [W0, b0, W1, b1, ..., total] of the flat parameter vector."""
+    n = len(sizes) - 1
+    arr = (ctypes.c_int * len(sizes))(*sizes)
+    out = (ctypes.c_longlong * (2 * n + 1))()
+    _lib.call("sb_mlp_param_offsets", n, arr, out)
+    return list(out)
+
+
+class PolicyMLP:
+    """ReLU MLP with a masked row head; weights W_i stored [out, in] like layers.weight."""
+
+    def __init__(self, sizes, batch, in_dtype="bf16", head=("masked_softmax",), with_bias=True,
+                 training=False, grads=None):
+        if in_dtype not in ("tf32", "bf16", "f16"):
+            raise ValueError("in_dtype must be 'tf32', 'bf16' or 'f16'")
+        self.sizes = [int(s) for s in sizes]
+        self.n_layers = len(self.sizes) - 1
+        self.batch = int(batch)
+        self.in_dtype = in_dtype
+        self.storage = in_dtype          # 'tf32' = fp32 storage holding TF32-rounded values
+        self.head = tuple(head)
+        self.head_flags = 0
+        for h in self.head:
+            self.head_flags |= HEAD_FLAGS[h]
+        self.with_bias = bool(with_bias)
+        self.offsets = param_offsets(self.sizes)
+        self.n_params = self.offsets[-1]
+        self._sizes_c = (ctypes.c_int * len(self.sizes))(*self.sizes)
+        self.params = DeviceArray.zeros((self.n_params,), "f32")
+        self.w_compute = DeviceArray.zeros((self.n_params,), self.storage)
+        self.activations = [DeviceArray((self.batch, self.sizes[i + 1]), self.storage)
+                            for i in range(self.n_layers - 1)]
+        self._acts_c = (ctypes.c_void_p * max(1, self.n_layers - 1))(*[a.ptr for a in self.activations])
+        self.probs = DeviceArray((self.batch, self.sizes[-1]), "f32")
+        self.actions = DeviceArray((self.batch,), "i32") if "argmax" in self.head else None
+        self.training = bool(training)
+        self.grads = None
+        self.scratch = None
+        self.loss = None
+        if self.training:
+            self.grads = grads if grads is not None else DeviceArray.zeros((self.n_params,), "f32")
+            nbytes = ctypes.c_size_t(0)
+            _lib.call("sb_mlp_backward_scratch_bytes", self.n_layers, self._sizes_c, self.batch,
+                      _lib.DTYPE_CODES[in_dtype], ctypes.byref(nbytes))
+            self.scratch = DeviceArray((nbytes.value,), "u8")
+            self.loss = DeviceArray.zeros((1,), "f32")
+
+    # -- parameters ----------------------------------------------------------
+    def load_weights(self, weights, biases=None):
+        """Uploads per-layer [out, in] fp32 weights (and biases) into the flat buffers."""
+        flat = np.zeros(self.n_params, np.float32)
+        for i, w in enumerate(weights):
+            w = np.asarray(w, np.float32)
+            if w.shape != (self.sizes[i + 1], self.sizes[i]):
+                raise ValueError("layer %d weight shape %s" % (i, w.shape))
+            o = self.offsets[2 * i]
+            flat[o:o + w.size] = w.ravel()
+            if biases is not None:
+                b = np.asarray(biases[i], np.float32)
+                ob = self.offsets[2 * i + 1]
+                flat[ob:ob + b.size] = b
+        self.params.upload(flat)
+        self.w_compute.upload(flat)       # the upload rounds to the storage type
+        return self
+
+    def get_weights(self):
+        flat = self.params.numpy()
+        ws, bs = [], []
+        for i in range(self.n_layers):
+            o, ob = self.offsets[2 * i], self.offsets[2 * i + 1]
+            n = self.sizes[i + 1] * self.sizes[i]
+            ws.append(flat[o:o + n].reshape(self.sizes[i + 1], self.sizes[i]).copy())
+            bs.append(flat[ob:ob + self.sizes[i + 1]].copy())
+        return ws, bs
+
+    def split_flat(self, flat):
+        """Views of a flat host vector as [(W_i, b_i), ...]."""
+        out = []
+        for i in range(self.n_layers):
+            o, ob = self.offsets[2 * i], self.offsets[2 * i + 1]
+            n = self.sizes[i + 1] * self.sizes[i]
+            out.append((flat[o:o + n].reshape(self.sizes[i + 1], self.sizes[i]), flat[ob:ob + self.sizes[i + 1]]))
+        return out
+
+    # -- execution -----------------------------------------------------------
+    def forward(self, x, mask=None, head_flags=None, stream=None):
+        """probs <- head(MLP(x)); returns the probs DeviceArray (and fills actions for argmax heads)."""
+        flags = self.head_flags if head_flags is None else head_flags
+        _lib.call("sb_mlp_forward", self.n_layers, self._sizes_c, self.batch, _lib.DTYPE_CODES[self.in_dtype],
+                  device_ptr(x), self.w_compute.ptr, self.params.ptr if self.with_bias else None, self._acts_c,
+                  flags, device_ptr(mask), self.probs.ptr, device_ptr(self.actions) if flags & _lib.EPI_ARGMAX else None,
+                  stream_ptr(stream))
+        return self.probs
+
+    def backward(self, x, mask, target, global_batch=None, stream=None):
+        """grads <- d(mean cross-entropy)/d(params) for this shard (after a masked-softmax forward)."""
+        gb = self.batch if global_batch is None else int(global_batch)
+        _lib.call("sb_mlp_backward", self.n_layers, self._sizes_c, self.batch, ctypes.c_float(1.0 / gb),
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr, self._acts_c, self.probs.ptr,
+                  device_ptr(mask), device_ptr(target), device_ptr(self.grads), int(self.with_bias),
+                  self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
+        return self.grads
+
+    def sgd(self, lr, stream=None):
+        _lib.call("sb_sgd_update", self.params.ptr, device_ptr(self.grads), self.w_compute.ptr,
+                  ctypes.c_longlong(self.n_params), ctypes.c_float(lr), _lib.DTYPE_CODES[self.storage],
+                  stream_ptr(stream))
+
+    def train_step(self, x, mask, target, lr, stream=None):
+        """Forward + backward + SGD on one GPU (no gradient exchange)."""
+        _lib.call("sb_mlp_train_step", self.n_layers, self._sizes_c, self.batch, _lib.DTYPE_CODES[self.in_dtype],
+                  device_ptr(x), self.params.ptr, self.w_compute.ptr, self._acts_c, device_ptr(mask),
+                  device_ptr(target), self.probs.ptr, device_ptr(self.grads), int(self.with_bias),
+                  ctypes.c_float(lr), self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
+
+    def flops_per_sample(self, training=False):
+        f = sum(2 * self.sizes[i] * self.sizes[i + 1] for i in range(self.n_layers))
+        if training:
+            f = 3 * f - 2 * self.sizes[0] * self.sizes[1]     # no dgrad into the input
+        return f
+
+
+def to_storage(x, in_dtype):
+    """Host fp32 array -> DeviceArray in the storage type of an arithmetic class."""
+    return DeviceArray.from_numpy(np.asarray(x, np.float32), in_dtype)

@@ -63,12 +63,22 @@ def test_ragged_4000x3000x1000(gpu, at, bt, in_dtype):
     assert so.rel_frobenius(got, so.matmul(at, bt, 1.0, a, b, 0.0, None)) <= TIGHT
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (130, 24, 72), (127, 257, 200), (300, 520, 136), (64, 1000, 8)])
+@pytest.mark.parametrize("m,n,k", [(8, 8, 8), (136, 24, 72), (120, 264, 200), (304, 520, 136), (64, 1000, 8)])
 @pytest.mark.parametrize("at,bt", LAYOUTS[:3])
 def test_small_odd_shapes_bf16(gpu, at, bt, m, n, k):
+    """Every contiguous dimension is a multiple of 8 elements (16-byte row pitch, as the reference
+    also demands, corecuda/base.spi:158); tile tails in M, N and K are exercised."""
     a, b, c = operands(m + n + k, at, bt, m, n, k, "bf16")
     got = run(gpu, at, bt, 1.0, a, b, 0.0, c, "bf16")
     assert so.rel_frobenius(got, so.matmul(at, bt, 1.0, a, b, 0.0, None)) <= TIGHT
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 8), (127, 3, 200), (333, 257, 72)])
+def test_nt_needs_only_k_aligned(gpu, m, n, k):
+    """The dense-layer layout (NT) has K contiguous in both operands: M and N may be anything."""
+    a, b, c = operands(m * n + k, False, True, m, n, k, "bf16")
+    got = run(gpu, False, True, 1.0, a, b, 0.0, c, "bf16")
+    assert so.rel_frobenius(got, so.matmul(False, True, 1.0, a, b, 0.0, None)) <= TIGHT
 
 
 def test_alpha_beta_in_place(gpu):
@@ -131,7 +141,7 @@ def test_relu_grad_epilogue(gpu):
 def test_fused_row_heads(gpu, n, heads):
     m, k = 333, 256
     a, b, c = operands(22 + n, False, True, m, n, k, "tf32")
-    a *= 0.2
+    a = so.round_tf32(a * np.float32(0.2))     # keep the inputs exactly representable in TF32
     mask = (so.rng(23).random((m, n)) < 0.6).astype(np.uint8)
     mask[:, 0] = 1
     idx = gpu.DeviceArray((m,), "i32")

@@ -1,0 +1,118 @@
+"""GPU parity of the dense policy network (forward, backward, SGD) against the oracle.
+
+The oracle rounds weights, inputs and hidden activations at the same points as the
+CUDA path (storage type of the arithmetic class), so forward probabilities agree
+to accumulation order; the benchmark's tolerance for the tf32 / bf16 / fp16 classes
+(2e-3 relative Frobenius error) is asserted on probabilities and on every gradient.
+"""
+import numpy as np
+import pytest
+
+from oracle import spiral_oracle as so
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def build(gpu, sizes, batch, in_dtype, seed, head=("masked_softmax",), training=False, bias_scale=0.0):
+    ws, bs = so.mlp_weights(seed, sizes)
+    if bias_scale:
+        g = so.rng(seed + 100)
+        bs = [(g.normal(size=b.shape) * bias_scale).astype(np.float32) for b in bs]
+    net = gpu.PolicyMLP(sizes, batch, in_dtype=in_dtype, head=head, training=training)
+    net.load_weights(ws, bs)
+    return net, ws, bs
+
+
+@pytest.mark.parametrize("in_dtype", ["tf32", "f16", "bf16"])
+def test_leduc_forward(gpu, in_dtype):
+    """Benchmark configuration 3 shape (32-256-256-256-3, masked softmax then regret matching) at B=2048."""
+    sizes, batch = [32, 256, 256, 256, 3], 2048
+    net, ws, bs = build(gpu, sizes, batch, in_dtype, 3, head=("masked_softmax", "regret_matching", "argmax"))
+    x, mask = so.leduc_inputs(3, batch)
+    probs = net.forward(gpu.to_storage(x, in_dtype), gpu.DeviceArray.from_numpy(mask)).numpy()
+    want = so.mlp_forward(x, ws, bs, mask, in_dtype=in_dtype, act_dtype=in_dtype,
+                          head=("masked_softmax", "regret_matching"))
+    assert so.rel_frobenius(probs, want) <= TOL
+    assert np.all(probs[mask == 0] == 0)
+    np.testing.assert_allclose(probs.sum(1), 1.0, atol=1e-5)
+    actions = net.actions.numpy()
+    np.testing.assert_array_equal(actions, np.argmax(probs, axis=1))
+    top2 = np.sort(want, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 5e-3
+    np.testing.assert_array_equal(actions[clear], so.argmax(want)[clear])
+    # against the un-rounded fp32 network the class tolerance still holds for fp16 / tf32
+    if in_dtype != "bf16":
+        full = so.mlp_forward(x, ws, bs, mask, head=("masked_softmax", "regret_matching"))
+        assert so.rel_frobenius(probs, full) <= TOL
+
+
+def test_holdem_forward_bf16(gpu):
+    """Benchmark configuration 5 shape (512-1024x4-10, 10-way masked softmax) at B=1024."""
+    sizes, batch = [512, 1024, 1024, 1024, 1024, 10], 1024
+    net, ws, bs = build(gpu, sizes, batch, "bf16", 5)
+    x, mask = so.holdem_inputs(5, batch)
+    probs = net.forward(gpu.to_storage(x, "bf16"), gpu.DeviceArray.from_numpy(mask)).numpy()
+    want = so.mlp_forward(x, ws, bs, mask, in_dtype="bf16", act_dtype="bf16")
+    assert so.rel_frobenius(probs, want) <= TOL
+
+
+@pytest.mark.parametrize("in_dtype,sizes,batch", [
+    ("tf32", [32, 256, 256, 256, 3], 1536),
+    ("bf16", [32, 256, 256, 256, 3], 1536),
+    ("bf16", [512, 1024, 1024, 10], 2048),
+])
+def test_backward_gradients(gpu, in_dtype, sizes, batch):
+    net, ws, bs = build(gpu, sizes, batch, in_dtype, 4, training=True, bias_scale=0.05)
+    if sizes[0] == 32:
+        x, mask = so.leduc_inputs(4, batch)
+    else:
+        x, mask = so.holdem_inputs(4, batch, features=sizes[0], actions=sizes[-1])
+    target = so.random_target(44, mask)
+    dx, dm, dt = gpu.to_storage(x, in_dtype), gpu.DeviceArray.from_numpy(mask), gpu.DeviceArray.from_numpy(target)
+    net.forward(dx, dm, head_flags=8)
+    net.backward(dx, dm, dt)
+    got = net.split_flat(net.grads.numpy())
+    _, _, loss, want = so.mlp_train_step(x, [so.round_input(w, in_dtype) for w in ws], bs, mask, target, 0.0,
+                                         in_dtype=in_dtype, act_dtype=in_dtype)
+    assert abs(float(net.loss.numpy()[0]) - loss) <= 2e-3 * abs(loss)
+    for i, ((gw, gb), (ww, wb)) in enumerate(zip(got, want)):
+        assert so.rel_frobenius(gw, ww) <= TOL, "dW of layer %d" % i
+        assert so.rel_frobenius(gb, wb) <= 5e-3, "db of layer %d" % i      # column sums of 16-bit dY
+    # padding of the flat gradient vector stays zero
+    flat = net.grads.numpy().copy()
+    for i in range(net.n_layers):
+        o, ob = net.offsets[2 * i], net.offsets[2 * i + 1]
+        flat[o:o + sizes[i + 1] * sizes[i]] = 0
+        flat[ob:ob + sizes[i + 1]] = 0
+    assert not flat.any()
+
+
+def test_train_step_updates_master_and_compute_weights(gpu):
+    sizes, batch, lr = [32, 256, 256, 256, 3], 4096, 1e-3
+    net, ws, bs = build(gpu, sizes, batch, "bf16", 6, training=True)
+    x, mask = so.leduc_inputs(6, batch)
+    target = so.random_target(66, mask)
+    net.train_step(gpu.to_storage(x, "bf16"), gpu.DeviceArray.from_numpy(mask), gpu.DeviceArray.from_numpy(target), lr)
+    new_w, new_b = net.get_weights()
+    w_ref, b_ref, _, grads = so.mlp_train_step(x, [so.round_bf16(w) for w in ws], bs, mask, target, lr,
+                                               in_dtype="bf16", act_dtype="bf16")
+    for i in range(len(ws)):
+        step_got = ws[i] - new_w[i]          # lr * dW, master weights are fp32
+        step_want = lr * grads[i][0]
+        assert so.rel_frobenius(step_got, step_want) <= 1e-2      # fp32 cancellation in w - w'
+    from spiral_b200 import dtypes
+    flat = net.params.numpy()
+    np.testing.assert_array_equal(net.w_compute.numpy(), dtypes.round_bf16(flat))
+    # a second step still runs on the updated weights and lowers the loss on the same batch
+    l0 = float(net.loss.numpy()[0])
+    net.loss.fill_zero()
+    for _ in range(20):
+        net.loss.fill_zero()
+        net.train_step(gpu.to_storage(x, "bf16"), gpu.DeviceArray.from_numpy(mask), gpu.DeviceArray.from_numpy(target), 0.05)
+    assert float(net.loss.numpy()[0]) < l0
+
+
+def test_empty_batch_is_a_no_op(gpu):
+    net = gpu.PolicyMLP([32, 64, 3], 0, in_dtype="bf16")
+    net.forward(gpu.DeviceArray((0, 32), "bf16"))
