@@ -1,0 +1,453 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-matmul / policy-MLP hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `holdem_train`: one SGD training step (forward, cross-entropy
+backward with dgrad + wgrad GEMMs, gradient all-reduce when N > 1, SGD) of the
+NL-Hold'em-sized policy MLP 512-1024x4-10, bf16 inputs / fp32 accumulate, global
+batch 262144 sharded over the N GPUs (strong scaling), synthetic seeded inputs
+resident in HBM.  One JSON line is printed by rank 0:
+
+  value      samples/s of the whole job, device-timed (CUDA events, max over ranks)
+  e2e        the same step through the public Python API with host buffers: every step
+             copies its inputs from pinned host memory and reads the loss back
+  roofline   the dominant kernel (tcgen05 GEMM): algorithmic flops / CUDA-event time of
+             the GEMM launches, against the measured cuBLAS bf16 peak of this pool
+  cpu_baseline  the NumPy oracle's training step on the host cores (bounded sample)
+  extra      GEMM TFLOP/s of the 4096^3 layout sweep and the other policy workloads
+
+`--impl reference` times the CPU implementation (NumPy, all host threads) of the
+same step on a bounded sample; under torchrun only rank 0 runs it.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "spiral-s-ml-library_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+HOLDEM_SIZES = [512, 1024, 1024, 1024, 1024, 10]
+LEDUC_SIZES = [32, 256, 256, 256, 3]
+WORKLOADS = {
+    # name: (sizes, global batch, in_dtype, training)
+    "holdem_train": (HOLDEM_SIZES, 262144, "bf16", True),
+    "holdem_infer": (HOLDEM_SIZES, 262144, "bf16", False),
+    "leduc_train": (LEDUC_SIZES, 65536, "bf16", True),
+    "leduc_infer": (LEDUC_SIZES, 16384, "f16", False),
+}
+LR = 1e-3
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            if t0 is not None and not (t0 <= ts <= t1 + 0.2):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+class PinnedBuffer:
+    """Page-locked host memory viewed as a NumPy array (source of the end-to-end copies)."""
+
+    def __init__(self, array):
+        import ctypes
+        from spiral_b200 import _lib
+        array = np.ascontiguousarray(array)
+        p = ctypes.c_void_p()
+        _lib.call("sb_malloc_host", ctypes.byref(p), array.nbytes)
+        self.ptr, self.nbytes = p.value, array.nbytes
+        buf = (ctypes.c_char * array.nbytes).from_address(self.ptr)
+        self.array = np.frombuffer(buf, dtype=array.dtype).reshape(array.shape)
+        self.array[...] = array
+
+    def copy_to(self, dev, stream=None):
+        from spiral_b200 import _lib
+        _lib.call("sb_memcpy_h2d", dev.ptr, self.ptr, self.nbytes, stream)
+
+
+def numpy_step(x, ws, bs, mask, target, training):
+    from oracle import spiral_oracle as so
+    if training:
+        so.mlp_train_step(x, ws, bs, mask, target, LR, exact=False)
+    else:
+        so.mlp_forward(x, ws, bs, mask, exact=False)
+
+
+def cpu_reference(workload, steps, warmup, sample_rows):
+    """Times the NumPy restatement (float32 BLAS, all host threads) on `sample_rows` rows per step."""
+    from oracle import spiral_oracle as so
+    sizes, _, _, training = WORKLOADS[workload]
+    ws, bs = so.mlp_weights(5, sizes)
+    if sizes[0] == 32:
+        x, mask = so.leduc_inputs(5, sample_rows)
+    else:
+        x, mask = so.holdem_inputs(5, sample_rows, features=sizes[0], actions=sizes[-1])
+    target = so.random_target(55, mask)
+    for _ in range(warmup):
+        numpy_step(x, ws, bs, mask, target, training)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        numpy_step(x, ws, bs, mask, target, training)
+    dt = (time.perf_counter() - t0) / max(1, steps)
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    return sample_rows / dt, dt * 1e3, cores
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    workload = args.workload
+    sizes, gbatch, in_dtype, training = WORKLOADS[workload]
+    rows = 8192 if sizes[0] == 512 else 65536
+    value, ms, cores = cpu_reference(workload, args.steps, args.warmup, rows)
+    sample = "NumPy float32 %s step on %d rows of the workload per step" % ("training" if training else "forward", rows)
+    line = {
+        "impl": "reference", "metric": "policy_mlp_%s_samples_per_sec" % ("train" if training else "infer"),
+        "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload, "layers": sizes, "global_batch": gbatch, "sample_rows_per_step": rows},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def gemm_sweep(sb, iters=10):
+    """GEMM TFLOP/s at 4096^3 (benchmark configuration 2): layouts NN/NT/TN, bf16 / f16 / tf32 inputs."""
+    out = {}
+    m = n = k = 4096
+    rng = np.random.Generator(np.random.Philox(2))
+    host = rng.standard_normal((4096, 4096), dtype=np.float32)
+    flush = sb.DeviceArray((192 * 1024 * 1024,), "u8")
+    for dt in ("bf16", "f16", "tf32"):
+        a = sb.DeviceArray.from_numpy(host, dt)
+        b = sb.DeviceArray.from_numpy(host.T.copy(), dt)
+        c = sb.DeviceArray((m, n), "f32")
+        for name, (at, bt) in (("NT", (False, True)), ("NN", (False, False)), ("TN", (True, False))):
+            for _ in range(3):
+                sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt)
+            total = 0.0
+            for _ in range(iters):
+                flush.fill_zero()                      # 192 MiB write: evicts the 126 MB L2
+                e0, e1 = sb.Event().record(), None
+                sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt)
+                e1 = sb.Event().record()
+                total += e0.elapsed_ms(e1)
+            out["%s_%s" % (dt, name)] = round(2.0 * m * n * k / (total / iters) / 1e9, 1)
+    return out
+
+
+def run_ours(args, rank, world, local_rank):
+    import spiral_b200 as sb
+    from oracle import spiral_oracle as so   # only for the synthetic input generators and the CPU baseline leg
+
+    workload = args.workload
+    sizes, gbatch, in_dtype, training = WORKLOADS[workload]
+    if args.batch:
+        gbatch = args.batch
+    if gbatch % world:
+        raise SystemExit("global batch %d is not divisible by %d GPUs" % (gbatch, world))
+    batch = gbatch // world
+    sb.set_device(local_rank)
+
+    dist = None
+    torch = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier_sync():
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        sb.synchronize()
+
+    # ---- synthetic inputs of this rank's shard (seeded; stand in for game states) ----------
+    gen_rows = min(batch, 32768)            # generate a block once and tile it: values/shape are what matter
+    if sizes[0] == 32:
+        xh, maskh = so.leduc_inputs(100 + rank, gen_rows)
+    else:
+        xh, maskh = so.holdem_inputs(100 + rank, gen_rows, features=sizes[0], actions=sizes[-1])
+    reps = (batch + gen_rows - 1) // gen_rows
+    xh = np.tile(xh, (reps, 1))[:batch]
+    maskh = np.tile(maskh, (reps, 1))[:batch]
+    targeth = so.random_target(200 + rank, maskh)
+    from spiral_b200 import dtypes
+    if in_dtype == "bf16":
+        x_store = dtypes.f32_to_bf16_bits(xh).reshape(xh.shape)
+    elif in_dtype == "f16":
+        x_store = xh.astype(np.float16)
+    else:
+        x_store = dtypes.round_tf32(xh)
+
+    grads = None
+    if training and world > 1:
+        n_params = sb.param_offsets(sizes)[-1]
+        grads = torch.zeros(n_params, dtype=torch.float32, device="cuda")
+    head = ("masked_softmax",) if training else ("masked_softmax", "regret_matching", "argmax")
+    net = sb.PolicyMLP(sizes, batch, in_dtype=in_dtype, head=head, training=training, grads=grads)
+    ws, bs = so.mlp_weights(5, sizes)        # same seed on every rank: replicated weights
+    net.load_weights(ws, bs)
+
+    x_dev = sb.DeviceArray(xh.shape, in_dtype)
+    mask_dev = sb.DeviceArray(maskh.shape, "u8")
+    target_dev = sb.DeviceArray(targeth.shape, "f32")
+    x_pin, mask_pin, target_pin = PinnedBuffer(x_store), PinnedBuffer(maskh), PinnedBuffer(targeth)
+    x_pin.copy_to(x_dev)
+    mask_pin.copy_to(mask_dev)
+    target_pin.copy_to(target_dev)
+    loss_pin = PinnedBuffer(np.zeros(1, np.float32))
+    sb.synchronize()
+
+    def step():
+        if training:
+            net.loss.fill_zero()
+            net.forward(x_dev, mask_dev)
+            net.backward(x_dev, mask_dev, target_dev, global_batch=gbatch)
+            if dist is not None:
+                dist.all_reduce(grads)
+            net.sgd(LR)
+        else:
+            net.forward(x_dev, mask_dev)
+
+    def step_e2e():
+        from spiral_b200 import _lib
+        x_pin.copy_to(x_dev)
+        mask_pin.copy_to(mask_dev)
+        if training:
+            target_pin.copy_to(target_dev)
+        step()
+        if training:
+            _lib.call("sb_memcpy_d2h", loss_pin.ptr, net.loss.ptr, 4, None)
+        else:
+            _lib.call("sb_memcpy_d2h", act_pin.ptr, net.actions.ptr, act_pin.nbytes, None)
+        _lib.call("sb_stream_sync", None)
+
+    act_pin = None if training else PinnedBuffer(np.zeros(batch, np.int32))
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier_sync()
+        l0 = sb.launch_count()
+        t_wall0 = time.time()
+        e0 = sb.Event().record()
+        for _ in range(steps):
+            fn()
+        e1 = sb.Event().record()
+        ms = e0.elapsed_ms(e1)
+        barrier_sync()
+        t_wall1 = time.time()
+        launches = sb.launch_count() - l0
+        if dist is not None:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches, (t_wall0, t_wall1)
+
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    ms_total, launches, window = timed(step, args.steps, max(3, args.warmup))
+    clocks = sampler.stop(*window) if sampler else None
+    ms_step = ms_total / args.steps
+    value = gbatch / (ms_step * 1e-3)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    ms_e2e, _, _ = timed(step_e2e, e2e_steps, 3)
+    e2e_value = gbatch / (ms_e2e / e2e_steps * 1e-3)
+    h2d = x_pin.nbytes + mask_pin.nbytes + (target_pin.nbytes if training else 0)
+    d2h = 4 if training else act_pin.nbytes
+
+    # ---- dominant kernel: event-timed GEMM launches of two more steps --------------------
+    with sb.GemmProfile() as prof:
+        step()
+        step()
+    sb.synchronize()
+    achieved = prof.flops / (prof.ms * 1e-3) / 1e12 if prof.ms > 0 else 0.0
+    peaks = measured_peaks()
+    peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    status = sb.device_status()
+    if status != (0, 0):
+        raise SystemExit("device-side wait expired during the benchmark: %s" % (status,))
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    extra = {"gemm_kernel_share_of_step": round(prof.ms / 2 / ms_step, 3),
+             "gemm_launches_per_step": prof.launches // 2,
+             "peak_burst_tflops": peaks.get("bf16_tflops"), "peaks_source": peaks["source"],
+             "model_tflops": round(net.flops_per_sample(training) * value / 1e12, 1)}
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        rows = 8192 if sizes[0] == 512 else 65536
+        v, ms_cpu, cores = cpu_reference(workload, 3, 1, rows)
+        cpu = {"value": v, "unit": "samples/s", "cores": cores, "kind": "port",
+               "sample": "NumPy float32 %s step on %d rows, mean of 3" % ("training" if training else "forward", rows)}
+        if not args.no_sweep:
+            extra["gemm_4096_tflops"] = gemm_sweep(sb)
+    line = {
+        "metric": "policy_mlp_%s_samples_per_sec" % ("train" if training else "infer"),
+        "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": in_dtype, "data": "synthetic",
+        "config": {"workload": workload, "layers": sizes, "global_batch": gbatch, "batch_per_gpu": batch,
+                   "parallelism": "dp%d" % world, "lr": LR,
+                   "l2": "inputs (%.0f MB per step) larger than the 126 MB L2" % (h2d / 1e6)},
+        "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel", "achieved": round(achieved, 1), "peak": peak,
+                     "unit": "TFLOP/s", "frac": round(achieved / peak, 4) if peak else None, "traffic": None,
+                     "peak_kind": "%s, sustained cuBLAS bf16" % peaks["source"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(h2d) * world,
+                "d2h_bytes_per_step": int(d2h) * world, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "extra": extra,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+PROFILE_CASES = {
+    # name: (a_trans, b_trans, M, N, K, in_dtype, out_dtype, epilogue)
+    "gemm4096_bf16_nt": (False, True, 4096, 4096, 4096, "bf16", "f32", ()),
+    "gemm4096_bf16_nn": (False, False, 4096, 4096, 4096, "bf16", "f32", ()),
+    "gemm4096_bf16_tn": (True, False, 4096, 4096, 4096, "bf16", "f32", ()),
+    "gemm4096_tf32_nt": (False, True, 4096, 4096, 4096, "tf32", "f32", ()),
+    "holdem_layer_fwd": (False, True, 65536, 1024, 1024, "bf16", "bf16", ("bias", "relu")),
+    "holdem_layer_dgrad": (False, False, 65536, 1024, 1024, "bf16", "bf16", ("relu_grad",)),
+    "holdem_layer_wgrad": (True, False, 1024, 1024, 65536, "bf16", "f32", ()),
+}
+
+
+def run_profile_case(name, iters):
+    """A few launches of one GEMM shape with seeded random operands, for ncu captures (no JSON line)."""
+    import spiral_b200 as sb
+    at, bt, m, n, k, dt, odt, epi = PROFILE_CASES[name]
+    sb.set_device(0)
+    rng = np.random.Generator(np.random.Philox(7))
+    a = sb.DeviceArray.from_numpy(rng.standard_normal((k, m) if at else (m, k), dtype=np.float32), dt)
+    b = sb.DeviceArray.from_numpy(rng.standard_normal((n, k) if bt else (k, n), dtype=np.float32), dt)
+    c = sb.DeviceArray((m, n), odt)
+    bias = sb.DeviceArray.from_numpy(rng.standard_normal(n, dtype=np.float32)) if "bias" in epi else None
+    aux = sb.DeviceArray.from_numpy(rng.standard_normal((m, n), dtype=np.float32), odt) if "relu_grad" in epi else None
+    sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt, epilogue=epi, bias=bias, aux_in=aux)   # first-launch set-up
+    sb.synchronize()
+    e0 = sb.Event().record()
+    for _ in range(iters):
+        sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt, epilogue=epi, bias=bias, aux_in=aux)
+    e1 = sb.Event().record()
+    ms = e0.elapsed_ms(e1) / iters
+    print("profile case %s: %.4f ms per launch, %.1f TFLOP/s, status %s"
+          % (name, ms, 2.0 * m * n * k / ms / 1e9, sb.device_status()), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="holdem_train")
+    ap.add_argument("--batch", type=int, default=0, help="override the global batch (tests only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
+                    help="run a few launches of one GEMM shape (for ncu) and exit")
+    ap.add_argument("--iters", type=int, default=4)
+    args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case, args.iters)
+        return
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus %d needs a torchrun launch with %d ranks" % (args.gpus, args.gpus))
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

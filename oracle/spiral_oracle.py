@@ -167,31 +167,32 @@ def masked_regret_matching(x, mask):
 # ----------------------------------------------------------------------------
 # dense layers and the policy MLP  (ml/layers.spi:227-240, 353-355, 408-420)
 # ----------------------------------------------------------------------------
-def dense(x, w, bias=None, in_dtype="f32"):
+def dense(x, w, bias=None, in_dtype="f32", exact=True):
     """BlockMatmul: y = x @ w.T with w stored [out, in] (NT, alpha=1, beta=0;
     ml/layers.spi:229-235,467).  The reference has no bias; `bias` is the
     benchmark configurations' addition."""
-    y = matmul(False, True, 1.0, x, w, 0.0, None, in_dtype=in_dtype)
+    y = matmul(False, True, 1.0, x, w, 0.0, None, in_dtype=in_dtype, exact=exact)
     if bias is not None:
         y = y + np.asarray(bias, dtype=np.float32)
     return y.astype(np.float32)
 
 
 def mlp_forward(x, weights, biases=None, mask=None, in_dtype="f32", head=("masked_softmax",),
-                act_dtype=None, return_activations=False):
+                act_dtype=None, return_activations=False, exact=True):
     """Hidden layers dense+ReLU, last layer dense + row head.
 
     `act_dtype` rounds every hidden activation to the storage type the CUDA path
     keeps between layers (None = fp32).  Heads apply in the order
     masked_softmax, regret_matching; mask=None means every action is legal.
     Returns probabilities (and optionally the list [x, h1, ..., logits]).
+    exact=False multiplies in float32 BLAS instead of float64 (CPU-baseline timing).
     """
     acts = [np.asarray(x, dtype=np.float32)]
     h = acts[0]
     n_layers = len(weights)
     for i, w in enumerate(weights):
         b = None if biases is None else biases[i]
-        h = dense(h, w, b, in_dtype=in_dtype)
+        h = dense(h, w, b, in_dtype=in_dtype, exact=exact)
         if i < n_layers - 1:
             h = relu(h)
             if act_dtype is not None:
@@ -220,7 +221,8 @@ def cross_entropy_loss(probs, target, mask=None):
     return float(-np.sum(np.where(m, target * lp, 0.0)) / probs.shape[0])
 
 
-def mlp_train_step(x, weights, biases, mask, target, lr, in_dtype="f32", act_dtype=None, global_batch=None):
+def mlp_train_step(x, weights, biases, mask, target, lr, in_dtype="f32", act_dtype=None, global_batch=None,
+                   exact=True):
     """One SGD step on cross-entropy(masked_softmax(logits), target).  Not in the
     reference (no backward pass exists there, ml/layers.spi:10 is CEM scratch).
 
@@ -232,7 +234,7 @@ def mlp_train_step(x, weights, biases, mask, target, lr, in_dtype="f32", act_dty
     the global batch.
     """
     probs, acts = mlp_forward(x, weights, biases, mask, in_dtype=in_dtype, head=("masked_softmax",),
-                              act_dtype=act_dtype, return_activations=True)
+                              act_dtype=act_dtype, return_activations=True, exact=exact)
     bsz = x.shape[0] if global_batch is None else global_batch
     m = np.ones(probs.shape, dtype=bool) if mask is None else np.asarray(mask, dtype=bool)
     tgt = np.where(m, np.asarray(target, dtype=np.float32), np.float32(0))
@@ -243,11 +245,11 @@ def mlp_train_step(x, weights, biases, mask, target, lr, in_dtype="f32", act_dty
     for i in range(len(weights) - 1, -1, -1):
         h_in = acts[i]
         dy_r = round_input(dy, in_dtype) if in_dtype != "f32" else dy
-        dw = matmul(True, False, 1.0, dy_r, h_in, 0.0, None, in_dtype=in_dtype)   # [out,in] = dY.T @ X
+        dw = matmul(True, False, 1.0, dy_r, h_in, 0.0, None, in_dtype=in_dtype, exact=exact)   # [out,in] = dY.T @ X
         db = np.sum(dy, axis=0, dtype=np.float64).astype(np.float32)
         grads[i] = (dw, db)
         if i > 0:
-            dx = matmul(False, False, 1.0, dy_r, weights[i], 0.0, None, in_dtype=in_dtype)  # dY @ W
+            dx = matmul(False, False, 1.0, dy_r, weights[i], 0.0, None, in_dtype=in_dtype, exact=exact)  # dY @ W
             dy = np.where(acts[i] > 0, dx, np.float32(0)).astype(np.float32)
             if act_dtype is not None:
                 dy = round_input(dy, act_dtype)

@@ -33,6 +33,7 @@ constexpr int UG_THREADS = 192;
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
 constexpr int UG_HEAD_MAX_N = 32;  // widest row a fused head keeps in registers
+constexpr int UG_EPI_STAGING = 4 * 2 * 4096;  // 4 epilogue warps x 2 boxes x (32 rows x 128 B)
 
 struct UmmaGemmParams {
   int M, N, K;
@@ -66,6 +67,8 @@ struct UmmaGemmParams {
   const uint8_t* mask;
   const void* aux_in;
   void* aux_out;
+  int tma_store;       // 1: full 32-column chunks leave through shared memory + TMA store
+  uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
 };
 
 __device__ __forceinline__ void tile_coords(const UmmaGemmParams& p, int tile, int& m_blk, int& n_blk) {
@@ -176,6 +179,82 @@ __device__ __forceinline__ void finish_chunk(const UmmaGemmParams& p, float* v, 
   }
 }
 
+// Staged variant for a full 32-column chunk: the warp's 32 rows x 32 columns are
+// written to a swizzled shared-memory box and leave through one TMA store, so
+// global memory sees whole 128-byte (fp32) or 64-byte (16-bit) row segments
+// instead of one 16-byte piece per thread.  `sbuf` is this warp's staging box
+// (two alternate; a box is reused only after the store that read it retired).
+template <typename OutT, bool ROUND_TF32>
+__device__ __forceinline__ void stage_chunk(const UmmaGemmParams& p, const CUtensorMap* tmap_c, float* v,
+                                            long long row, bool row_ok, int row0_warp, int col0,
+                                            long long c_off, uint32_t sbuf, int lane) {
+  constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
+  constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
+  constexpr uint32_t ROW_BYTES = 32 * sizeof(OutT);
+  const bool has_beta = p.beta != 0.0f;
+  const bool has_bias = (p.epi & SB_EPI_BIAS) != 0;
+  const bool relu = (p.epi & SB_EPI_RELU) != 0;
+  const bool relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0;
+  const OutT* crow = reinterpret_cast<const OutT*>(p.C) + c_off + row * p.ldc + col0;
+  const OutT* arow = reinterpret_cast<const OutT*>(p.aux_in) + row * p.ldc + col0;
+  const int valid = min(32, p.N - col0);     // columns of this chunk inside the matrix
+  uint4 packed[PIECES];
+#pragma unroll
+  for (int q = 0; q < PIECES; ++q) {
+    float old[VEC], act[VEC];
+    const bool piece_full = (q + 1) * VEC <= valid;
+    if (has_beta && row_ok) {
+      if (piece_full) {
+        uint4 raw = *reinterpret_cast<const uint4*>(crow + q * VEC);
+        const OutT* e = reinterpret_cast<const OutT*>(&raw);
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) old[t] = load_as_float<OutT>(e + t);
+      } else {
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) old[t] = (q * VEC + t < valid) ? load_as_float<OutT>(crow + q * VEC + t) : 0.f;
+      }
+    }
+    if (relu_grad && row_ok) {
+      if (piece_full) {
+        uint4 raw = *reinterpret_cast<const uint4*>(arow + q * VEC);
+        const OutT* e = reinterpret_cast<const OutT*>(&raw);
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) act[t] = load_as_float<OutT>(e + t);
+      } else {
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) act[t] = (q * VEC + t < valid) ? load_as_float<OutT>(arow + q * VEC + t) : 0.f;
+      }
+    }
+    OutT outv[VEC];
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) {
+      float x = p.alpha * v[q * VEC + t];
+      if (has_beta && row_ok) x += p.beta * old[t];
+      if (has_bias) x += (q * VEC + t < valid) ? __ldg(p.bias + col0 + q * VEC + t) : 0.f;
+      if (relu) x = fmaxf(x, 0.f);
+      if (relu_grad && row_ok) x = act[t] > 0.f ? x : 0.f;
+      if (ROUND_TF32) x = round_tf32_rn(x);
+      outv[t] = float_to<OutT>(x);
+    }
+    packed[q] = *reinterpret_cast<const uint4*>(outv);
+  }
+  // The box about to be overwritten was read by the store issued two chunks ago.
+  if (lane == 0) bulk_wait_group_read<1>();
+  __syncwarp();
+  const uint32_t swz_mask = ROW_BYTES == 128 ? 7u : 3u;
+#pragma unroll
+  for (int q = 0; q < PIECES; ++q) {
+    const uint32_t lin = (uint32_t)lane * ROW_BYTES + (uint32_t)q * 16u;
+    st_shared_v4(sbuf + (lin ^ (((lin >> 7) & swz_mask) << 4)), packed[q]);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tmap_c, sbuf, col0, row0_warp);
+    bulk_commit_group();
+  }
+}
+
 // Row head on a full row (N <= 32) held by one thread; fp32 output.
 // Follows local_masked_softmax / local_masked_regret_matching / local_argmax
 // (ml/primitives.spi:748-780, 705-708); the softmax subtracts the masked
@@ -258,7 +337,8 @@ constexpr int EPI_HEAD_MASK = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | S
 
 __global__ void __launch_bounds__(UG_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, const UmmaGemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const UmmaGemmParams p) {
   extern __shared__ uint8_t ug_smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[UG_MAX_STAGES];
   __shared__ __align__(8) uint64_t bar_empty[UG_MAX_STAGES];
@@ -403,6 +483,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool head = (p.epi & EPI_HEAD_MASK) != 0;
+    const uint32_t sbuf0 = stage_base + p.epi_offset + (uint32_t)(warp - 2) * 8192u;
+    int sbuf_sel = 0;
     for (int work = blockIdx.x; work < p.num_work; work += gridDim.x) {
       const int split = work / p.num_tiles;
       const long long c_off = (long long)split * p.split_stride;
@@ -425,8 +507,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (w == 32) tmem_ld32(t_row + (uint32_t)c0, raw); else tmem_ld16(t_row + (uint32_t)c0, raw);
           tmem_ld_wait();
           const int col0 = n_blk * p.block_n + c0;
-          if (row_ok) {
-            float* v = reinterpret_cast<float*>(raw);
+          float* v = reinterpret_cast<float*>(raw);
+          const int row0_warp = m_blk * UG_BLOCK_M + quad * 32;
+          if (p.tma_store && w == 32 && col0 < p.N) {
+            // Clipped by the tensor map: rows >= M (per split) and columns >= N.
+            if (row0_warp < p.M) {
+              const uint32_t sbuf = sbuf0 + (uint32_t)sbuf_sel * 4096u;
+              const int y = split * p.M + row0_warp;
+              if (p.out_dtype == SB_F32) stage_chunk<float, false>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
+              else if (p.out_dtype == SB_TF32) stage_chunk<float, true>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
+              else if (p.out_dtype == SB_BF16) stage_chunk<__nv_bfloat16, false>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
+              else stage_chunk<__half, false>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
+              sbuf_sel ^= 1;
+            }
+          } else if (row_ok) {
             if (p.out_dtype == SB_F32) finish_chunk<float, false>(p, v, w, row, col0, c_off);
             else if (p.out_dtype == SB_TF32) finish_chunk<float, true>(p, v, w, row, col0, c_off);
             else if (p.out_dtype == SB_BF16) finish_chunk<__nv_bfloat16, false>(p, v, w, row, col0, c_off);
@@ -442,8 +536,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  // Teardown.  After an expired wait, give copies and MMAs still in flight
-  // time to land before shared and tensor memory are released.
+  // Teardown.  Stores still reading the staging boxes must retire first; after
+  // an expired wait, also give copies and MMAs in flight time to land before
+  // shared and tensor memory are released.
+  if (warp >= 2 && lane == 0) bulk_wait_group<0>();
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
@@ -480,9 +576,12 @@ EncodeTiledFn get_encode_tiled() {
 
 // 2-D row-major tensor [rows, cols] -> tensor map with box [box_rows, box_cols],
 // 128-byte swizzle (box_cols * elem size must be 128 bytes), zero fill outside.
-// `chunk32` selects the variant that swizzles 32-byte chunks (MN-major TF32).
+// `swz`: SWZ_128 (16-byte chunks), SWZ_128_CHUNK32 (32-byte chunks, MN-major
+// TF32 operands) or SWZ_64 (64-byte rows, 16-bit output boxes).
+enum TmapSwizzle { SWZ_128 = 0, SWZ_128_CHUNK32 = 1, SWZ_64 = 2 };
+
 int make_tmap_2d(CUtensorMap* map, const void* base, int in_dtype, long long rows, long long cols,
-                 int box_rows, int box_cols, bool chunk32) {
+                 int box_rows, int box_cols, int swz) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return sb_fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const int es = sb_dtype_size(in_dtype);
@@ -495,7 +594,9 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int in_dtype, long long row
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   chunk32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   swz == SWZ_128_CHUNK32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                   : swz == SWZ_64      ? CU_TENSOR_MAP_SWIZZLE_64B
+                                        : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return sb_fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld box=%dx%d)",
@@ -567,11 +668,12 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms) {
   p.a_boxes = p.a_mn ? UG_BLOCK_M / p.mn_box_elems : 1;
   p.b_boxes = p.b_mn ? p.block_n / p.mn_box_elems : 1;
   const int stage_bytes = (int)(p.a_stage_bytes + p.b_stage_bytes);
-  int stages = (UG_SMEM_LIMIT - 2048) / stage_bytes;
+  int stages = (UG_SMEM_LIMIT - 2048 - UG_EPI_STAGING) / stage_bytes;
   if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
   if (stages > p.k_blocks && p.k_blocks >= 2) stages = max(2, p.k_blocks);
   if (stages < 2) stages = 2;
   p.stages = stages;
+  p.epi_offset = (uint32_t)stages * (uint32_t)stage_bytes;
   // Per-MMA descriptor step: K-major advances 32 bytes inside the swizzle
   // atom; MN-major advances (UMMA_K / 8) groups of 8 k-rows (1024 B each).
   const int umma_k = 32 / es;
@@ -587,7 +689,7 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms) {
 }
 
 size_t umma_dyn_smem(const UmmaGemmParams& p) {
-  return (size_t)p.stages * (p.a_stage_bytes + p.b_stage_bytes) + 1024;
+  return (size_t)p.stages * (p.a_stage_bytes + p.b_stage_bytes) + UG_EPI_STAGING + 1024;
 }
 
 __global__ void scale_rows_kernel(void* C, long long total, float beta, int out_dtype) {
@@ -638,22 +740,13 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
 
   CUtensorMap ta, tb;
   int rc;
-  if (!p.a_mn) rc = make_tmap_2d(&ta, A, in_dtype, M, K, UG_BLOCK_M, p.block_k, false);
-  else rc = make_tmap_2d(&ta, A, in_dtype, K, M, p.block_k, p.mn_box_elems, p.a_layout == 1u);
+  if (!p.a_mn) rc = make_tmap_2d(&ta, A, in_dtype, M, K, UG_BLOCK_M, p.block_k, SWZ_128);
+  else rc = make_tmap_2d(&ta, A, in_dtype, K, M, p.block_k, p.mn_box_elems, p.a_layout == 1u ? SWZ_128_CHUNK32 : SWZ_128);
   if (rc != SB_OK) return rc;
-  if (!p.b_mn) rc = make_tmap_2d(&tb, B, in_dtype, N, K, p.block_n, p.block_k, false);
-  else rc = make_tmap_2d(&tb, B, in_dtype, K, N, p.block_k, p.mn_box_elems, p.b_layout == 1u);
+  if (!p.b_mn) rc = make_tmap_2d(&tb, B, in_dtype, N, K, p.block_n, p.block_k, SWZ_128);
+  else rc = make_tmap_2d(&tb, B, in_dtype, K, N, p.block_k, p.mn_box_elems, p.b_layout == 1u ? SWZ_128_CHUNK32 : SWZ_128);
   if (rc != SB_OK) return rc;
 
-  const size_t smem = umma_dyn_smem(p);
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  SB_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 UG_SMEM_LIMIT - 1024));
-    attr_set[dev] = true;
-  }
   if (splits > 1) {
     // Split-K: each split writes its own [M,N] partial at C + split * M * N.
     int kbps = (p.k_blocks + splits - 1) / splits;
@@ -664,9 +757,34 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     p.split_stride = (long long)M * N;
   }
   if (splits_used) *splits_used = p.splits;
+
+  // Output through shared memory + TMA store when C allows it: 16-byte aligned
+  // base and row pitch, no row head, and -- with split-K, where the partials
+  // form one [splits * M, N] tensor -- no 32-row box may straddle two partials.
+  const int es_out = out_dtype == SB_BF16 || out_dtype == SB_F16 ? 2 : 4;
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  p.tma_store = 0;
+  if (!(epi & EPI_HEAD_MASK) && ((long long)N * es_out) % 16 == 0 && N >= 32 &&
+      (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (p.splits == 1 || M % 32 == 0)) {
+    const int cdt = es_out == 4 ? SB_F32 : out_dtype;
+    rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, 32, es_out == 4 ? SWZ_128 : SWZ_64);
+    if (rc != SB_OK) return rc;
+    p.tma_store = 1;
+  }
+
+  const size_t smem = umma_dyn_smem(p);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  SB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 UG_SMEM_LIMIT - 1024));
+    attr_set[dev] = true;
+  }
   const int grid = min(p.num_work, cached_sm_count());
   sb_prof_before(stream);
-  umma_gemm_kernel<<<grid, UG_THREADS, smem, stream>>>(ta, tb, p);
+  umma_gemm_kernel<<<grid, UG_THREADS, smem, stream>>>(ta, tb, tc, p);
   sb_prof_after(stream, 2.0 * M * N * K);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
