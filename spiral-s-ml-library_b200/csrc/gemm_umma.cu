@@ -26,6 +26,9 @@
 // shared memory.
 #include "common.cuh"
 
+#include <stdlib.h>
+#include <string.h>
+
 namespace {
 
 constexpr int UG_BLOCK_M = 128;
@@ -33,7 +36,7 @@ constexpr int UG_THREADS = 192;
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
 constexpr int UG_HEAD_MAX_N = 32;  // widest row a fused head keeps in registers
-constexpr int UG_EPI_STAGING = 4 * 2 * 4096;  // 4 epilogue warps x 2 boxes x (32 rows x 128 B)
+constexpr int UG_EPI_STAGING = 4 * 4096;  // one 32-row x 128-byte box per epilogue warp
 
 struct UmmaGemmParams {
   int M, N, K;
@@ -67,7 +70,8 @@ struct UmmaGemmParams {
   const uint8_t* mask;
   const void* aux_in;
   void* aux_out;
-  int tma_store;       // 1: full 32-column chunks leave through shared memory + TMA store
+  int pair;            // 1: CTA pairs (cta_group::2), 256-row tiles
+  int coalesced;       // 1: 32-column chunks are transposed through shared memory for row-contiguous stores
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
 };
 
@@ -112,146 +116,190 @@ __device__ __forceinline__ float round_tf32_rn(float v) {
   return __uint_as_float(u & 0xffffe000u);
 }
 
-// One thread finishes `w` (16 or 32) consecutive columns of its output row.
-// ROUND_TF32: fp32 output rounded to 10 mantissa bits (nearest even), so that a
-// following TF32 GEMM reads exactly the value stored.
-template <typename OutT, bool ROUND_TF32>
-__device__ __forceinline__ void finish_chunk(const UmmaGemmParams& p, float* v, int w, long long row,
-                                             int col0, long long c_off) {
-  const int valid = min(w, p.N - col0);
-  if (valid <= 0) return;
-  OutT* crow = reinterpret_cast<OutT*>(p.C) + c_off + row * p.ldc + col0;
-  const OutT* arow = reinterpret_cast<const OutT*>(p.aux_in) + row * p.ldc + col0;
-  constexpr int VEC = 16 / sizeof(OutT);
-  const bool vec_ok = (valid == w) && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
-  const bool has_beta = p.beta != 0.0f;
-  const bool has_bias = (p.epi & SB_EPI_BIAS) != 0;
-  const bool relu = (p.epi & SB_EPI_RELU) != 0;
-  const bool relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0;
-  const bool avec_ok = relu_grad && ((reinterpret_cast<uintptr_t>(arow) & 15) == 0) && (valid == w);
+// Coalescing variant for a 32-column chunk.  TMEM hands each thread one output
+// row, so a direct store would touch 32 rows per instruction with 16 bytes
+// each.  Instead the warp's 32 rows x 32 columns go through a swizzled
+// shared-memory box (conflict-free both ways) and are written so that one
+// store instruction covers whole row segments: 4 rows x 128 B (32-bit output)
+// or 8 rows x 64 B (16-bit output).  Old C values (beta) and the activation
+// tile of the ReLU-gradient gate come in through the same box, read with the
+// same coalesced pattern.  `sbuf` is this warp's private 4 KB box.
+template <typename OutT>
+__device__ __forceinline__ uint32_t box_offset(uint32_t row, uint32_t piece) {
+  constexpr uint32_t ROW_BYTES = 32 * sizeof(OutT);
+  constexpr uint32_t PIECES = ROW_BYTES / 16;
+  const uint32_t key = ROW_BYTES == 128 ? (row & 7u) : ((row >> 1) & 3u);
+  return row * ROW_BYTES + (((piece ^ key) & (PIECES - 1)) << 4);
+}
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// Brings the chunk [row0_warp .. +32) x [col0 .. +32) of a row-major matrix
+// (row pitch ld elements; rows valid below row_limit, columns below n; zeros
+// elsewhere) into the box with coalesced loads.  Afterwards lane r finds its
+// own row r at box_offset(r, piece).
+template <typename OutT>
+__device__ __forceinline__ void load_chunk_to_box(const OutT* base, long long ld, long long row0_warp,
+                                                  long long row_limit, int col0, int n, uint32_t sbuf,
+                                                  int lane) {
+  constexpr int VEC = 16 / sizeof(OutT);
+  constexpr int PIECES = 32 / VEC;
+  constexpr int ROWS_PER_INST = 32 / PIECES;
 #pragma unroll
-  for (int j0 = 0; j0 < 32; j0 += VEC) {
-    if (j0 < w) {
-      float old[VEC];
-      float act[VEC];
-      if (has_beta) {
-        if (vec_ok) {
-          uint4 raw = *reinterpret_cast<const uint4*>(crow + j0);
-          const OutT* e = reinterpret_cast<const OutT*>(&raw);
-#pragma unroll
-          for (int t = 0; t < VEC; ++t) old[t] = load_as_float<OutT>(e + t);
-        } else {
-#pragma unroll
-          for (int t = 0; t < VEC; ++t) old[t] = (j0 + t < valid) ? load_as_float<OutT>(crow + j0 + t) : 0.f;
-        }
-      }
-      if (relu_grad) {
-        if (avec_ok) {
-          uint4 raw = *reinterpret_cast<const uint4*>(arow + j0);
-          const OutT* e = reinterpret_cast<const OutT*>(&raw);
-#pragma unroll
-          for (int t = 0; t < VEC; ++t) act[t] = load_as_float<OutT>(e + t);
-        } else {
-#pragma unroll
-          for (int t = 0; t < VEC; ++t) act[t] = (j0 + t < valid) ? load_as_float<OutT>(arow + j0 + t) : 0.f;
-        }
-      }
-      OutT outv[VEC];
-#pragma unroll
-      for (int t = 0; t < VEC; ++t) {
-        float x = p.alpha * v[j0 + t];
-        if (has_beta) x += p.beta * old[t];
-        if (has_bias) x += (j0 + t < valid) ? __ldg(p.bias + col0 + j0 + t) : 0.f;
-        if (relu) x = fmaxf(x, 0.f);
-        if (relu_grad) x = act[t] > 0.f ? x : 0.f;
-        if (ROUND_TF32) x = round_tf32_rn(x);
-        outv[t] = float_to<OutT>(x);
-      }
-      if (vec_ok) {
-        *reinterpret_cast<uint4*>(crow + j0) = *reinterpret_cast<const uint4*>(outv);
+  for (int i = 0; i < PIECES; ++i) {
+    const int r = i * ROWS_PER_INST + lane / PIECES;
+    const int q = lane % PIECES;
+    const long long grow = row0_warp + r;
+    const int gcol = col0 + q * VEC;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (grow < row_limit) {
+      const OutT* src = base + grow * ld + gcol;
+      if (gcol + VEC <= n) {
+        val = *reinterpret_cast<const uint4*>(src);
       } else {
+        OutT tmp[VEC];
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) tmp[t] = (gcol + t < n) ? src[t] : float_to<OutT>(0.f);
+        val = *reinterpret_cast<const uint4*>(tmp);
+      }
+    }
+    st_shared_v4(sbuf + box_offset<OutT>((uint32_t)r, (uint32_t)q), val);
+  }
+  __syncwarp();
+}
+
+// Epilogue arguments held in registers.  The out-of-line epilogue takes them by
+// value: fields read through a reference to the kernel's parameter block would be
+// re-read after every shared-memory asm statement, and with the whole L1 carved
+// out as shared memory each such read costs an L2 round trip.
+struct EpiArgs {
+  void* c;             // output, already offset to this split's partial
+  const void* aux;     // activation tile for the ReLU-gradient gate
+  const float* bias;
+  long long ldc;
+  int M, N;
+  float alpha, beta;
+  bool has_bias, relu, relu_grad, coalesced;
+};
+
+template <typename OutT, bool ROUND_TF32>
+__device__ __forceinline__ void coalesced_chunk(const EpiArgs& e, float* v, float bias_lane, long long row0_warp,
+                                                int col0, uint32_t sbuf, int lane) {
+  constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
+  constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
+  constexpr int ROWS_PER_INST = 32 / PIECES;
+  OutT* cbase = reinterpret_cast<OutT*>(e.c);
+  if (e.beta != 0.0f) {
+    // v <- alpha * acc + beta * C_old, with the old tile read through the box.
+    load_chunk_to_box<OutT>(cbase, e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
+#pragma unroll
+    for (int q = 0; q < PIECES; ++q) {
+      const uint4 raw = ld_shared_v4(sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q));
+      const OutT* o = reinterpret_cast<const OutT*>(&raw);
+#pragma unroll
+      for (int t = 0; t < VEC; ++t) v[q * VEC + t] = e.alpha * v[q * VEC + t] + e.beta * load_as_float<OutT>(o + t);
+    }
+    __syncwarp();
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+  }
+  if (e.has_bias) {
+    // Lane j holds bias[col0 + j]; every lane needs all 32 of them.
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
+  }
+  if (e.relu_grad)
+    load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(e.aux), e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
+#pragma unroll
+  for (int q = 0; q < PIECES; ++q) {
+    const uint32_t mine = sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
+    uint4 araw = make_uint4(0u, 0u, 0u, 0u);
+    if (e.relu_grad) araw = ld_shared_v4(mine);     // this lane's piece of the activation tile
+    const OutT* acte = reinterpret_cast<const OutT*>(&araw);
+    OutT outv[VEC];
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) {
+      float x = v[q * VEC + t];
+      if (e.relu) x = fmaxf(x, 0.f);
+      if (e.relu_grad) x = load_as_float<OutT>(acte + t) > 0.f ? x : 0.f;
+      if (ROUND_TF32) x = round_tf32_rn(x);
+      outv[t] = float_to<OutT>(x);
+    }
+    st_shared_v4(mine, *reinterpret_cast<const uint4*>(outv));   // overwrites only what this lane just read
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < PIECES; ++i) {
+    const int r = i * ROWS_PER_INST + lane / PIECES;
+    const int q = lane % PIECES;
+    const long long grow = row0_warp + r;
+    const int gcol = col0 + q * VEC;
+    if (grow < e.M && gcol < e.N) {
+      const uint4 val = ld_shared_v4(sbuf + box_offset<OutT>((uint32_t)r, (uint32_t)q));
+      OutT* dst = cbase + grow * e.ldc + gcol;
+      if (gcol + VEC <= e.N) {
+        *reinterpret_cast<uint4*>(dst) = val;
+      } else {
+        const OutT* o = reinterpret_cast<const OutT*>(&val);
 #pragma unroll
         for (int t = 0; t < VEC; ++t)
-          if (j0 + t < valid) crow[j0 + t] = outv[t];
+          if (gcol + t < e.N) dst[t] = o[t];
       }
+    }
+  }
+  __syncwarp();
+}
+
+// Per-thread stores of `w` (16 or 32) columns of one row: the fallback when C's
+// row pitch or base is not 16-byte aligned, and the 16-column tail chunk.
+template <typename OutT, bool ROUND_TF32>
+__device__ __forceinline__ void direct_chunk(const EpiArgs& e, float* v, int w, long long row, int col0) {
+  const int valid = min(w, e.N - col0);
+  if (valid <= 0) return;
+  OutT* crow = reinterpret_cast<OutT*>(e.c) + row * e.ldc + col0;
+  const OutT* arow = reinterpret_cast<const OutT*>(e.aux) + row * e.ldc + col0;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {      // static indices keep v[] in registers
+    if (j < valid) {
+      float x = e.alpha * v[j];
+      if (e.beta != 0.0f) x += e.beta * load_as_float<OutT>(crow + j);
+      if (e.has_bias) x += __ldg(e.bias + col0 + j);
+      if (e.relu) x = fmaxf(x, 0.f);
+      if (e.relu_grad) x = load_as_float<OutT>(arow + j) > 0.f ? x : 0.f;
+      if (ROUND_TF32) x = round_tf32_rn(x);
+      crow[j] = float_to<OutT>(x);
     }
   }
 }
 
-// Staged variant for a full 32-column chunk: the warp's 32 rows x 32 columns are
-// written to a swizzled shared-memory box and leave through one TMA store, so
-// global memory sees whole 128-byte (fp32) or 64-byte (16-bit) row segments
-// instead of one 16-byte piece per thread.  `sbuf` is this warp's staging box
-// (two alternate; a box is reused only after the store that read it retired).
+// One warp drains its 32 accumulator rows of a tile: block_n columns in chunks
+// of 32 (a trailing chunk of 16 when block_n % 32 == 16).  Out of line and one
+// instance per output type, so that only one variant's registers are live.
 template <typename OutT, bool ROUND_TF32>
-__device__ __forceinline__ void stage_chunk(const UmmaGemmParams& p, const CUtensorMap* tmap_c, float* v,
-                                            long long row, bool row_ok, int row0_warp, int col0,
-                                            long long c_off, uint32_t sbuf, int lane) {
-  constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
-  constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
-  constexpr uint32_t ROW_BYTES = 32 * sizeof(OutT);
-  const bool has_beta = p.beta != 0.0f;
-  const bool has_bias = (p.epi & SB_EPI_BIAS) != 0;
-  const bool relu = (p.epi & SB_EPI_RELU) != 0;
-  const bool relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0;
-  const OutT* crow = reinterpret_cast<const OutT*>(p.C) + c_off + row * p.ldc + col0;
-  const OutT* arow = reinterpret_cast<const OutT*>(p.aux_in) + row * p.ldc + col0;
-  const int valid = min(32, p.N - col0);     // columns of this chunk inside the matrix
-  uint4 packed[PIECES];
-#pragma unroll
-  for (int q = 0; q < PIECES; ++q) {
-    float old[VEC], act[VEC];
-    const bool piece_full = (q + 1) * VEC <= valid;
-    if (has_beta && row_ok) {
-      if (piece_full) {
-        uint4 raw = *reinterpret_cast<const uint4*>(crow + q * VEC);
-        const OutT* e = reinterpret_cast<const OutT*>(&raw);
-#pragma unroll
-        for (int t = 0; t < VEC; ++t) old[t] = load_as_float<OutT>(e + t);
-      } else {
-#pragma unroll
-        for (int t = 0; t < VEC; ++t) old[t] = (q * VEC + t < valid) ? load_as_float<OutT>(crow + q * VEC + t) : 0.f;
-      }
+__device__ __noinline__ void epilogue_tile(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0,
+                                           uint32_t sbuf, int lane) {
+  const long long row = (long long)row0_warp + lane;
+  const bool row_ok = row < e.M;
+  for (int c0 = 0; c0 < block_n; c0 += 32) {
+    const int w = min(32, block_n - c0);
+    const int col0 = n0 + c0;
+    // The bias load (an L2 round trip) is issued before the TMEM load so that the two overlap.
+    float bias_lane = 0.f;
+    if (e.has_bias && col0 + lane < e.N) bias_lane = __ldg(e.bias + col0 + lane);
+    uint32_t raw[32];
+    if (w == 32) tmem_ld32(t_row + (uint32_t)c0, raw); else tmem_ld16(t_row + (uint32_t)c0, raw);
+    tmem_ld_wait();
+    float* v = reinterpret_cast<float*>(raw);
+    if (e.coalesced && w == 32) {
+      if (row0_warp < e.M && col0 < e.N) coalesced_chunk<OutT, ROUND_TF32>(e, v, bias_lane, row0_warp, col0, sbuf, lane);
+    } else if (row_ok) {
+      direct_chunk<OutT, ROUND_TF32>(e, v, w, row, col0);
     }
-    if (relu_grad && row_ok) {
-      if (piece_full) {
-        uint4 raw = *reinterpret_cast<const uint4*>(arow + q * VEC);
-        const OutT* e = reinterpret_cast<const OutT*>(&raw);
-#pragma unroll
-        for (int t = 0; t < VEC; ++t) act[t] = load_as_float<OutT>(e + t);
-      } else {
-#pragma unroll
-        for (int t = 0; t < VEC; ++t) act[t] = (q * VEC + t < valid) ? load_as_float<OutT>(arow + q * VEC + t) : 0.f;
-      }
-    }
-    OutT outv[VEC];
-#pragma unroll
-    for (int t = 0; t < VEC; ++t) {
-      float x = p.alpha * v[q * VEC + t];
-      if (has_beta && row_ok) x += p.beta * old[t];
-      if (has_bias) x += (q * VEC + t < valid) ? __ldg(p.bias + col0 + q * VEC + t) : 0.f;
-      if (relu) x = fmaxf(x, 0.f);
-      if (relu_grad && row_ok) x = act[t] > 0.f ? x : 0.f;
-      if (ROUND_TF32) x = round_tf32_rn(x);
-      outv[t] = float_to<OutT>(x);
-    }
-    packed[q] = *reinterpret_cast<const uint4*>(outv);
-  }
-  // The box about to be overwritten was read by the store issued two chunks ago.
-  if (lane == 0) bulk_wait_group_read<1>();
-  __syncwarp();
-  const uint32_t swz_mask = ROW_BYTES == 128 ? 7u : 3u;
-#pragma unroll
-  for (int q = 0; q < PIECES; ++q) {
-    const uint32_t lin = (uint32_t)lane * ROW_BYTES + (uint32_t)q * 16u;
-    st_shared_v4(sbuf + (lin ^ (((lin >> 7) & swz_mask) << 4)), packed[q]);
-  }
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) {
-    tma_store_2d(tmap_c, sbuf, col0, row0_warp);
-    bulk_commit_group();
   }
 }
 
@@ -335,10 +383,20 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
 
 constexpr int EPI_HEAD_MASK = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
 
+// PAIR = false: one CTA per 128 x block_n tile (cta_group::1).
+// PAIR = true : a cluster of two CTAs per 256 x block_n tile (cta_group::2).
+//   Each CTA loads its own 128 rows of A and its own half of the B columns
+//   (plain TMA loads whose completion bytes are reported to the leader CTA's
+//   full barrier); the leader CTA (cluster rank 0) issues every MMA with M = 256
+//   and commits to the barriers of both CTAs; each CTA's epilogue drains its own
+//   128 accumulator rows and arrives on the leader's tmem_empty barrier.  Halving
+//   the B bytes each SM stages is what lifts the shared-memory ceiling of the
+//   single-CTA form.
+template <bool PAIR, bool TF32>
 __global__ void __launch_bounds__(UG_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c, const UmmaGemmParams p) {
+                 const __grid_constant__ UmmaGemmParams p) {
   extern __shared__ uint8_t ug_smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[UG_MAX_STAGES];
   __shared__ __align__(8) uint64_t bar_empty[UG_MAX_STAGES];
@@ -350,6 +408,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0u;
+  // Work items are strided over CTAs (single) or over CTA pairs.
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TILE_M = PAIR ? 2 * UG_BLOCK_M : UG_BLOCK_M;
 
   // Stage buffers start on a 1024-byte boundary (one swizzle atom).
   const uint32_t raw_addr = smem_u32(ug_smem_raw);
@@ -363,7 +427,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tmem_full[a]), 1);
-      mbar_init(smem_u32(&bar_tmem_empty[a]), 4);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), PAIR ? 8 : 4);
     }
     abort_flag = 0;
     fence_mbar_init();
@@ -371,59 +435,87 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_slot), (uint32_t)p.tmem_cols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(&tmem_slot), (uint32_t)p.tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&tmem_slot), (uint32_t)p.tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
 
   if (warp == 0) {
     if (lane == 0) {
+      // The issue loop of a single thread: keep it to a handful of instructions
+      // per k-block (addresses advance by adds, nothing is recomputed).
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x) {
+      const int b_cols = PAIR ? p.block_n / 2 : p.block_n;   // half of the B columns per CTA in a pair
+      const uint32_t tx_bytes = PAIR ? 2u * stage_bytes : stage_bytes;
+      const uint32_t full0_local = smem_u32(&bar_full[0]);
+      const uint32_t full0 = PAIR ? map_to_cta(full0_local, 0u) : full0_local;
+      const uint32_t empty0 = smem_u32(&bar_empty[0]);
+      const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0;
+      const int a_boxes = p.a_boxes, b_boxes = p.b_boxes, mn_box_elems = p.mn_box_elems, block_k = p.block_k;
+      const uint32_t mn_box_bytes = p.mn_box_bytes, a_stage_bytes = p.a_stage_bytes;
+      const int stages = p.stages;
+      uint32_t a_dst = stage_base;
+      for (int work = worker; ok && work < p.num_work; work += num_workers) {
         const int split = work / p.num_tiles;
         int m_blk, n_blk;
         tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
-        const int m0 = m_blk * UG_BLOCK_M;
-        const int n0 = n_blk * p.block_n;
+        const int m0 = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M;
+        const int n0 = n_blk * p.block_n + (int)cta_rank * b_cols;
         const int kb_begin = split * p.kb_per_split;
         const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, SB_SITE_PRODUCER_EMPTY)) {
+        int k0 = kb_begin * block_k;
+        for (int kb = kb_begin; kb < kb_end; ++kb, k0 += block_k) {
+          if (!mbar_wait(empty0 + 8u * (uint32_t)stage, phase ^ 1u, abortp, SB_SITE_PRODUCER_EMPTY)) {
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bar_full[stage]);
-          mbar_arrive_expect_tx(full, stage_bytes);
-          const uint32_t a_dst = stage_base + (uint32_t)stage * stage_bytes;
-          const uint32_t b_dst = a_dst + p.a_stage_bytes;
-          const int k0 = kb * p.block_k;
-          if (!p.a_mn) {
-            tma_load_2d(a_dst, &tmap_a, k0, m0, full);
+          // In a pair only the leader arms its full barrier, with the bytes of both CTAs.
+          if (!PAIR || leader) mbar_arrive_expect_tx(full0_local + 8u * (uint32_t)stage, tx_bytes);
+          const uint32_t full = full0 + 8u * (uint32_t)stage;
+          const uint32_t b_dst = a_dst + a_stage_bytes;
+          if (!a_mn) {
+            if (PAIR) tma_load_2d_pair(a_dst, &tmap_a, k0, m0, full);
+            else tma_load_2d(a_dst, &tmap_a, k0, m0, full);
           } else {
-            for (int i = 0; i < p.a_boxes; ++i)
-              tma_load_2d(a_dst + (uint32_t)i * p.mn_box_bytes, &tmap_a, m0 + i * p.mn_box_elems, k0, full);
+            for (int i = 0; i < a_boxes; ++i) {
+              if (PAIR) tma_load_2d_pair(a_dst + (uint32_t)i * mn_box_bytes, &tmap_a, m0 + i * mn_box_elems, k0, full);
+              else tma_load_2d(a_dst + (uint32_t)i * mn_box_bytes, &tmap_a, m0 + i * mn_box_elems, k0, full);
+            }
           }
-          if (!p.b_mn) {
-            tma_load_2d(b_dst, &tmap_b, k0, n0, full);
+          if (!b_mn) {
+            if (PAIR) tma_load_2d_pair(b_dst, &tmap_b, k0, n0, full);
+            else tma_load_2d(b_dst, &tmap_b, k0, n0, full);
           } else {
-            for (int i = 0; i < p.b_boxes; ++i)
-              tma_load_2d(b_dst + (uint32_t)i * p.mn_box_bytes, &tmap_b, n0 + i * p.mn_box_elems, k0, full);
+            for (int i = 0; i < b_boxes; ++i) {
+              if (PAIR) tma_load_2d_pair(b_dst + (uint32_t)i * mn_box_bytes, &tmap_b, n0 + i * mn_box_elems, k0, full);
+              else tma_load_2d(b_dst + (uint32_t)i * mn_box_bytes, &tmap_b, n0 + i * mn_box_elems, k0, full);
+            }
           }
-          if (++stage == p.stages) {
+          a_dst += stage_bytes;
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
+            a_dst = stage_base;
           }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && leader) {
+      // tcgen05.mma issue blocks while the tensor pipe's short queue is full, so
+      // every other instruction of this thread is time the pipe may run dry:
+      // descriptors are kept as (lo, hi) words, the lo word advances by adds.
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -433,9 +525,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // MN-major: LBO = bytes between 128-byte MN segments (one TMA box),
       //           SBO = bytes between k-row groups: 1024 (8 rows) for 16-bit
       //           types, 512 (4 rows) for the 32-byte-chunk swizzle of TF32.
-      const uint32_t a_lbo = p.a_mn ? p.mn_box_bytes : 16u;
-      const uint32_t b_lbo = p.b_mn ? p.mn_box_bytes : 16u;
-      for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x) {
+      const uint64_t a_desc0 = umma_smem_desc(stage_base, p.a_mn ? p.mn_box_bytes : 16u, p.a_sbo, p.a_layout);
+      const uint64_t b_desc0 = umma_smem_desc(stage_base + p.a_stage_bytes, p.b_mn ? p.mn_box_bytes : 16u, p.b_sbo, p.b_layout);
+      const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0;
+      const uint32_t stage_step = stage_bytes >> 4;
+      const uint32_t a_kstep = p.a_kstep, b_kstep = p.b_kstep, idesc = p.idesc;
+      const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
+      const int stages = p.stages;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;
+      for (int work = worker; ok && work < p.num_work; work += num_workers) {
         const int split = work / p.num_tiles;
         const int kb_begin = split * p.kb_per_split;
         const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
@@ -445,34 +544,32 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.acc_stride);
+        uint32_t accumulate = 0u;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, SB_SITE_MMA_FULL)) {
+          if (!mbar_wait(full0 + 8u * (uint32_t)stage, phase, abortp, SB_SITE_MMA_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_src = stage_base + (uint32_t)stage * stage_bytes;
-          const uint32_t b_src = a_src + p.a_stage_bytes;
-          const uint64_t a_desc = umma_smem_desc(a_src, a_lbo, p.a_sbo, p.a_layout);
-          const uint64_t b_desc = umma_smem_desc(b_src, b_lbo, p.b_sbo, p.b_layout);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t accumulate = (kb > kb_begin || ks > 0) ? 1u : 0u;
-            const uint64_t ad = a_desc + (uint64_t)(ks * p.a_kstep);
-            const uint64_t bd = b_desc + (uint64_t)(ks * p.b_kstep);
-            if (p.kind_tf32)
-              umma_tf32(d_tmem, ad, bd, p.idesc, accumulate);
-            else
-              umma_f16(d_tmem, ad, bd, p.idesc, accumulate);
-          }
-          tc_commit(smem_u32(&bar_empty[stage]));
-          if (++stage == p.stages) {
+          umma_issue<PAIR, TF32>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+          umma_issue<PAIR, TF32>(d_tmem, a_lo + a_kstep, a_hi, b_lo + b_kstep, b_hi, idesc, 1u);
+          umma_issue<PAIR, TF32>(d_tmem, a_lo + 2u * a_kstep, a_hi, b_lo + 2u * b_kstep, b_hi, idesc, 1u);
+          umma_issue<PAIR, TF32>(d_tmem, a_lo + 3u * a_kstep, a_hi, b_lo + 3u * b_kstep, b_hi, idesc, 1u);
+          accumulate = 1u;
+          if (PAIR) tc_commit_pair(empty0 + 8u * (uint32_t)stage, (uint16_t)3);
+          else tc_commit(empty0 + 8u * (uint32_t)stage);
+          a_lo += stage_step;
+          b_lo += stage_step;
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
+            a_lo = a_lo0;
+            b_lo = b_lo0;
           }
         }
         if (!ok) break;
-        tc_commit(smem_u32(&bar_tmem_full[acc]));
+        if (PAIR) tc_commit_pair(smem_u32(&bar_tmem_full[acc]), (uint16_t)3);
+        else tc_commit(smem_u32(&bar_tmem_full[acc]));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -483,16 +580,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool head = (p.epi & EPI_HEAD_MASK) != 0;
-    const uint32_t sbuf0 = stage_base + p.epi_offset + (uint32_t)(warp - 2) * 8192u;
-    int sbuf_sel = 0;
-    for (int work = blockIdx.x; work < p.num_work; work += gridDim.x) {
+    const uint32_t sbuf = stage_base + p.epi_offset + (uint32_t)(warp - 2) * 4096u;
+    for (int work = worker; work < p.num_work; work += num_workers) {
       const int split = work / p.num_tiles;
       const long long c_off = (long long)split * p.split_stride;
       int m_blk, n_blk;
       tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
       if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
       tc_fence_after_sync();
-      const long long row = (long long)m_blk * UG_BLOCK_M + quad * 32 + lane;
+      const int row0_warp = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M + quad * 32;
+      const long long row = (long long)row0_warp + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
       if (head) {
@@ -501,56 +598,46 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_wait();
         if (row_ok) finish_head(p, reinterpret_cast<float*>(raw), row);
       } else {
-        for (int c0 = 0; c0 < p.block_n; c0 += 32) {
-          const int w = min(32, p.block_n - c0);
-          uint32_t raw[32];
-          if (w == 32) tmem_ld32(t_row + (uint32_t)c0, raw); else tmem_ld16(t_row + (uint32_t)c0, raw);
-          tmem_ld_wait();
-          const int col0 = n_blk * p.block_n + c0;
-          float* v = reinterpret_cast<float*>(raw);
-          const int row0_warp = m_blk * UG_BLOCK_M + quad * 32;
-          if (p.tma_store && w == 32 && col0 < p.N) {
-            // Clipped by the tensor map: rows >= M (per split) and columns >= N.
-            if (row0_warp < p.M) {
-              const uint32_t sbuf = sbuf0 + (uint32_t)sbuf_sel * 4096u;
-              const int y = split * p.M + row0_warp;
-              if (p.out_dtype == SB_F32) stage_chunk<float, false>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
-              else if (p.out_dtype == SB_TF32) stage_chunk<float, true>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
-              else if (p.out_dtype == SB_BF16) stage_chunk<__nv_bfloat16, false>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
-              else stage_chunk<__half, false>(p, &tmap_c, v, row, row_ok, y, col0, c_off, sbuf, lane);
-              sbuf_sel ^= 1;
-            }
-          } else if (row_ok) {
-            if (p.out_dtype == SB_F32) finish_chunk<float, false>(p, v, w, row, col0, c_off);
-            else if (p.out_dtype == SB_TF32) finish_chunk<float, true>(p, v, w, row, col0, c_off);
-            else if (p.out_dtype == SB_BF16) finish_chunk<__nv_bfloat16, false>(p, v, w, row, col0, c_off);
-            else finish_chunk<__half, false>(p, v, w, row, col0, c_off);
-          }
-        }
+        const int n0 = n_blk * p.block_n;
+        EpiArgs e;
+        e.aux = p.aux_in; e.bias = p.bias; e.ldc = p.ldc; e.M = p.M; e.N = p.N;
+        e.alpha = p.alpha; e.beta = p.beta;
+        e.has_bias = (p.epi & SB_EPI_BIAS) != 0; e.relu = (p.epi & SB_EPI_RELU) != 0;
+        e.relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0; e.coalesced = p.coalesced != 0;
+        if (p.out_dtype == SB_F32 || p.out_dtype == SB_TF32) e.c = reinterpret_cast<float*>(p.C) + c_off;
+        else e.c = reinterpret_cast<uint16_t*>(p.C) + c_off;
+        if (p.out_dtype == SB_F32) epilogue_tile<float, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
+        else if (p.out_dtype == SB_TF32) epilogue_tile<float, true>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
+        else if (p.out_dtype == SB_BF16) epilogue_tile<__nv_bfloat16, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
+        else epilogue_tile<__half, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+      if (lane == 0) {
+        // The MMA issuer (leader CTA) owns the tmem_empty barrier of the pair.
+        if (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_tmem_empty[acc]), 0u));
+        else mbar_arrive(smem_u32(&bar_tmem_empty[acc]));
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
   }
 
-  // Teardown.  Stores still reading the staging boxes must retire first; after
-  // an expired wait, also give copies and MMAs in flight time to land before
-  // shared and tensor memory are released.
-  if (warp >= 2 && lane == 0) bulk_wait_group<0>();
+  // Teardown.  After an expired wait, give copies and MMAs in flight time to
+  // land before shared and tensor memory are released.  In a pair neither CTA
+  // may leave while its peer can still touch its shared memory or barriers.
   __syncwarp();
   tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   if (*abortp != 0) {
     const unsigned long long t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) { }
-    __syncthreads();
   }
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, (uint32_t)p.tmem_cols);
+    else tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
 }
 
@@ -604,6 +691,16 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int in_dtype, long long row
   return SB_OK;
 }
 
+// SB_NO_PAIR=1 in the environment keeps every GEMM on single-CTA tiles.
+bool sb_pair_mode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SB_NO_PAIR");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 int round_up_int(int x, int m) { return (x + m - 1) / m * m; }
 int next_pow2(int x) {
   int p = 32;
@@ -625,26 +722,33 @@ int cached_sm_count() {
 }
 
 // Chooses block_n / stages / grid for a problem; `sms` = SM count to plan for.
-void plan_umma(UmmaGemmParams& p, int in_dtype, int sms) {
+// `allow_pair`: CTA pairs may be used (needs at least two 128-row blocks and a
+// tile at least 64 columns wide; row heads stay on single CTAs).
+void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair) {
   const int es = sb_dtype_size(in_dtype);
   p.block_k = 128 / es;
   p.k_blocks = (p.K + p.block_k - 1) / p.block_k;
-  p.tiles_m = (p.M + UG_BLOCK_M - 1) / UG_BLOCK_M;
   p.mn_box_elems = 128 / es;
   p.mn_box_bytes = (uint32_t)p.block_k * 128u;
-  const int gran = p.b_mn ? p.mn_box_elems : 16;
+  p.pair = (allow_pair && p.M > UG_BLOCK_M && p.N >= 64 && sms >= 2) ? 1 : 0;
+  const int tile_m = p.pair ? 2 * UG_BLOCK_M : UG_BLOCK_M;
+  const int workers = p.pair ? sms / 2 : sms;
+  p.tiles_m = (p.M + tile_m - 1) / tile_m;
+  // Column granularity of a tile: 16 for a K-major B (32 in a pair, 16 per CTA);
+  // an MN-major B needs whole 128-byte boxes per CTA.
+  const int gran = (p.b_mn ? p.mn_box_elems : 16) * (p.pair ? 2 : 1);
   int best_bn = 0;
   if (p.N <= 256) {
     best_bn = round_up_int(p.N, gran);
   } else {
-    // Minimise (waves of tiles over the SMs) x (cost of one tile); tiles
-    // narrower than 192 columns are shared-memory-bandwidth bound for
-    // single-CTA MMAs, so they are not considered for wide problems.
+    // Minimise (waves of tiles over the workers) x (cost of one tile); tiles
+    // narrower than 192 columns stage too many operand bytes per flop, so they
+    // are not considered for wide problems.
     double best_cost = 1e30;
-    for (int bn = 256; bn >= 192; bn -= gran) {
+    for (int bn = 256; bn >= 192; bn -= 16) {
       if (bn % gran) continue;
       const long long tiles = (long long)p.tiles_m * ((p.N + bn - 1) / bn);
-      const long long waves = (tiles + sms - 1) / sms;
+      const long long waves = (tiles + workers - 1) / workers;
       const double cost = (double)waves * (bn + 16);
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
@@ -661,12 +765,13 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms) {
   p.split_stride = 0;
   p.acc_stride = next_pow2(p.block_n);
   p.tmem_cols = next_pow2(2 * p.acc_stride);
+  // Per CTA: 128 rows of A and all (single) or half (pair) of the B columns.
+  const int b_cols = p.pair ? p.block_n / 2 : p.block_n;
   p.a_stage_bytes = UG_BLOCK_M * 128u;
-  p.b_stage_bytes = (uint32_t)p.block_n * 128u;
-  // Keep every stage 1024-byte aligned: block_n * 128 is a multiple of 1024
-  // only when block_n % 8 == 0, which holds (multiples of 16).
+  p.b_stage_bytes = (uint32_t)b_cols * 128u;
+  // Every stage stays 1024-byte aligned: b_cols is a multiple of 16.
   p.a_boxes = p.a_mn ? UG_BLOCK_M / p.mn_box_elems : 1;
-  p.b_boxes = p.b_mn ? p.block_n / p.mn_box_elems : 1;
+  p.b_boxes = p.b_mn ? b_cols / p.mn_box_elems : 1;
   const int stage_bytes = (int)(p.a_stage_bytes + p.b_stage_bytes);
   int stages = (UG_SMEM_LIMIT - 2048 - UG_EPI_STAGING) / stage_bytes;
   if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
@@ -685,7 +790,7 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms) {
   p.b_layout = b32 ? 1u : 2u;
   p.a_sbo = a32 ? 512u : 1024u;
   p.b_sbo = b32 ? 512u : 1024u;
-  p.idesc = sb_umma_idesc(in_dtype, p.a_mn, p.b_mn, UG_BLOCK_M, p.block_n);
+  p.idesc = sb_umma_idesc(in_dtype, p.a_mn, p.b_mn, tile_m, p.block_n);
 }
 
 size_t umma_dyn_smem(const UmmaGemmParams& p) {
@@ -723,7 +828,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_trans ? 1 : 0;   // A stored [K,M]: M contiguous
   p.b_mn = b_trans ? 0 : 1;   // B stored [K,N]: N contiguous
-  plan_umma(p, in_dtype, cached_sm_count());
+  plan_umma(p, in_dtype, cached_sm_count(), !(epi & EPI_HEAD_MASK) && sb_pair_mode_enabled());
   p.alpha = alpha; p.beta = beta;
   p.C = C; p.ldc = N; p.out_dtype = out_dtype;
   p.epi = epi; p.bias = bias; p.mask = mask; p.aux_in = aux_in; p.aux_out = aux_out;
@@ -743,7 +848,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   if (!p.a_mn) rc = make_tmap_2d(&ta, A, in_dtype, M, K, UG_BLOCK_M, p.block_k, SWZ_128);
   else rc = make_tmap_2d(&ta, A, in_dtype, K, M, p.block_k, p.mn_box_elems, p.a_layout == 1u ? SWZ_128_CHUNK32 : SWZ_128);
   if (rc != SB_OK) return rc;
-  if (!p.b_mn) rc = make_tmap_2d(&tb, B, in_dtype, N, K, p.block_n, p.block_k, SWZ_128);
+  if (!p.b_mn) rc = make_tmap_2d(&tb, B, in_dtype, N, K, p.pair ? p.block_n / 2 : p.block_n, p.block_k, SWZ_128);
   else rc = make_tmap_2d(&tb, B, in_dtype, K, N, p.block_k, p.mn_box_elems, p.b_layout == 1u ? SWZ_128_CHUNK32 : SWZ_128);
   if (rc != SB_OK) return rc;
 
@@ -758,33 +863,48 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   }
   if (splits_used) *splits_used = p.splits;
 
-  // Output through shared memory + TMA store when C allows it: 16-byte aligned
-  // base and row pitch, no row head, and -- with split-K, where the partials
-  // form one [splits * M, N] tensor -- no 32-row box may straddle two partials.
+  // Row-contiguous (coalesced) stores need a 16-byte aligned base and row pitch;
+  // anything else falls back to per-thread stores.  Row heads write directly.
   const int es_out = out_dtype == SB_BF16 || out_dtype == SB_F16 ? 2 : 4;
-  CUtensorMap tc;
-  memset(&tc, 0, sizeof(tc));
-  p.tma_store = 0;
-  if (!(epi & EPI_HEAD_MASK) && ((long long)N * es_out) % 16 == 0 && N >= 32 &&
-      (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (p.splits == 1 || M % 32 == 0)) {
-    const int cdt = es_out == 4 ? SB_F32 : out_dtype;
-    rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, 32, es_out == 4 ? SWZ_128 : SWZ_64);
-    if (rc != SB_OK) return rc;
-    p.tma_store = 1;
-  }
+  p.coalesced = (!(epi & EPI_HEAD_MASK) && ((long long)N * es_out) % 16 == 0 &&
+                 (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                 (!aux_in || (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0)) ? 1 : 0;
 
   const size_t smem = umma_dyn_smem(p);
   static bool attr_set[64] = {false};
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 UG_SMEM_LIMIT - 1024));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
     attr_set[dev] = true;
   }
-  const int grid = min(p.num_work, cached_sm_count());
   sb_prof_before(stream);
-  umma_gemm_kernel<<<grid, UG_THREADS, smem, stream>>>(ta, tb, tc, p);
+  if (!p.pair) {
+    const int grid = min(p.num_work, cached_sm_count());
+    if (p.kind_tf32) umma_gemm_kernel<false, true><<<grid, UG_THREADS, smem, stream>>>(ta, tb, p);
+    else umma_gemm_kernel<false, false><<<grid, UG_THREADS, smem, stream>>>(ta, tb, p);
+  } else {
+    // One cluster of two CTAs per worker; the two CTAs of a cluster share a TPC.
+    const int workers = min(p.num_work, cached_sm_count() / 2);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * workers, 1, 1);
+    cfg.blockDim = dim3(UG_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (p.kind_tf32) SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, true>, ta, tb, p));
+    else SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, false>, ta, tb, p));
+  }
   sb_prof_after(stream, 2.0 * M * N * K);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
@@ -797,12 +917,12 @@ int sb_umma_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, in
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_trans ? 1 : 0;
   p.b_mn = b_trans ? 0 : 1;
-  plan_umma(p, in_dtype, sms);
-  plan5[0] = UG_BLOCK_M;
+  plan_umma(p, in_dtype, sms, sb_pair_mode_enabled());
+  plan5[0] = p.pair ? 2 * UG_BLOCK_M : UG_BLOCK_M;
   plan5[1] = p.block_n;
   plan5[2] = p.block_k;
   plan5[3] = p.stages;
-  plan5[4] = min(p.num_tiles, sms);
+  plan5[4] = p.pair ? 2 * min(p.num_tiles, sms / 2) : min(p.num_tiles, sms);
   return SB_OK;
 }
 
