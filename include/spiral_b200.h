@@ -90,6 +90,8 @@ unsigned long long sb_launch_count(void);
  * launch (game/leduc/full.spi:21-34). */
 int sb_gemm_profile_begin(void);
 int sb_gemm_profile_end(int* launches, double* total_ms, double* total_flops);
+/* Time and flops of launch `index` of the profile that sb_gemm_profile_end just closed. */
+int sb_gemm_profile_entry(int index, double* ms, double* flops);
 
 /* ---- GEMM ---------------------------------------------------------------
  * C[M,N] <- alpha * op(A) * op(B) + beta * C, row-major, in place.

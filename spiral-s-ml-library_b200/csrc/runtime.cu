@@ -18,6 +18,8 @@ int g_prof_n = 0;
 cudaEvent_t g_prof_ev[2 * PROF_MAX];
 bool g_prof_ev_made = false;
 double g_prof_flops[PROF_MAX];
+float g_prof_ms[PROF_MAX];
+int g_prof_last_n = 0;
 }  // namespace
 
 void sb_prof_before(cudaStream_t s) {
@@ -210,13 +212,23 @@ int sb_gemm_profile_end(int* launches, double* total_ms, double* total_flops) {
     SB_CUDA(cudaEventSynchronize(g_prof_ev[2 * i + 1]));
     float t = 0.f;
     SB_CUDA(cudaEventElapsedTime(&t, g_prof_ev[2 * i], g_prof_ev[2 * i + 1]));
+    g_prof_ms[i] = t;
     ms += t;
     fl += g_prof_flops[i];
   }
   if (launches) *launches = g_prof_n;
   if (total_ms) *total_ms = ms;
   if (total_flops) *total_flops = fl;
+  g_prof_last_n = g_prof_n;
   g_prof_n = 0;
+  return SB_OK;
+}
+
+int sb_gemm_profile_entry(int index, double* ms, double* flops) {
+  if (index < 0 || index >= g_prof_last_n || !ms || !flops)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_gemm_profile_entry: index %d outside the last profile of %d launches", index, g_prof_last_n);
+  *ms = g_prof_ms[index];
+  *flops = g_prof_flops[index];
   return SB_OK;
 }
 

@@ -67,6 +67,7 @@ SIGNATURES = {
     "sb_launch_count": (ctypes.c_ulonglong, []),
     "sb_gemm_profile_begin": (_I, []),
     "sb_gemm_profile_end": (_I, [_IP, POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
+    "sb_gemm_profile_entry": (_I, [_I, POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "sb_matmul_tf32": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _P]),
     "sb_matmul_ex": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "sb_matmul_plan": (_I, [_I, _I, _I, _I, _I, _I, _I, _IP]),

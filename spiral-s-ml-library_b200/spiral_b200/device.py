@@ -217,4 +217,8 @@ class GemmProfile:
         fl = ctypes.c_double(0)
         _lib.call("sb_gemm_profile_end", ctypes.byref(n), ctypes.byref(ms), ctypes.byref(fl))
         self.launches, self.ms, self.flops = n.value, ms.value, fl.value
+        self.entries = []
+        for i in range(n.value):
+            _lib.call("sb_gemm_profile_entry", i, ctypes.byref(ms), ctypes.byref(fl))
+            self.entries.append((ms.value, fl.value))
         return False
