@@ -40,7 +40,8 @@ typedef enum sb_dtype { SB_F32 = 0, SB_TF32 = 1, SB_BF16 = 2, SB_F16 = 3, SB_I32
  *   v = alpha * acc + beta * C_old ; v += bias[col] ; v = relu(v) ;
  *   v = (aux_in[row,col] > 0) ? v : 0   (RELU_GRAD) ;
  *   row head: masked softmax, then regret matching, then argmax.
- * The row heads need the whole row in one tile: N <= 256. */
+ * Row heads are fused into the GEMM for N <= 32 and run as a second kernel on
+ * C for wider rows. */
 enum {
   SB_EPI_NONE = 0,
   SB_EPI_BIAS = 1,            /* bias: fp32[N] */
@@ -48,7 +49,11 @@ enum {
   SB_EPI_RELU_GRAD = 4,       /* aux_in: activation [M,N] in out_dtype */
   SB_EPI_MASKED_SOFTMAX = 8,  /* ml/primitives.spi:748-759; mask: uint8[M,N] or NULL = all legal */
   SB_EPI_REGRET_MATCHING = 16,/* ml/primitives.spi:761-780, same mask */
-  SB_EPI_ARGMAX = 32          /* ml/primitives.spi:705-708; aux_out: int32[M], lowest index on ties */
+  SB_EPI_ARGMAX = 32,         /* ml/primitives.spi:705-708; aux_out: int32[M], lowest index on ties */
+  /* ReLU sign bits instead of the activation tile (N % 32 == 0): word
+   * [row, c] of a uint32[M, N/32] matrix, bit j = (value[row, 32c + j] > 0). */
+  SB_EPI_RELU_MASK_OUT = 64,  /* with SB_EPI_RELU: also write the sign bits to aux_out */
+  SB_EPI_RELU_GRAD_MASK = 128 /* gate by the sign bits in aux_in (the backward twin of the above) */
 };
 
 /* ---- runtime ------------------------------------------------------------ */
@@ -154,12 +159,17 @@ int sb_mlp_param_offsets(int n_layers, const int* sizes, long long* offsets);
  * sequence ml/layers.py:4500-4546).  x: [batch, sizes[0]] in the storage type;
  * activations: host array of n_layers-1 device pointers, activations[i] =
  * [batch, sizes[i+1]] in the storage type (workspace, overwritten); params may
- * be NULL (no bias, as in the reference); head: SB_EPI_MASKED_SOFTMAX |
+ * be NULL (no bias, as in the reference); relu_bits: NULL, or a host array of
+ * n_layers-1 device pointers, relu_bits[i] = uint32 [batch, sizes[i+1]/32]
+ * receiving the ReLU sign bits of hidden layer i (SB_EPI_RELU_MASK_OUT; used
+ * when the width is a multiple of 32, so that backward need not re-read the
+ * activations to gate its gradients); head: SB_EPI_MASKED_SOFTMAX |
  * SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX; out: fp32 [batch, sizes[n_layers]];
  * actions: int32 [batch] when SB_EPI_ARGMAX. */
 int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
-                   const void* w_compute, const float* params, void* const* activations, int head,
-                   const uint8_t* mask, float* out, int32_t* actions, void* stream);
+                   const void* w_compute, const float* params, void* const* activations,
+                   void* const* relu_bits, int head, const uint8_t* mask, float* out, int32_t* actions,
+                   void* stream);
 
 /* Backward pass of mean cross-entropy over `1/inv_global_batch` rows on a
  * masked-softmax head, after sb_mlp_forward with SB_EPI_MASKED_SOFTMAX on the
@@ -172,8 +182,9 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
 int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int in_dtype, size_t* bytes);
 int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
                     const void* x, const void* w_compute, void* const* activations,
-                    const float* probs, const uint8_t* mask, const float* target, float* grads,
-                    int with_bias, void* scratch, size_t scratch_bytes, float* loss, void* stream);
+                    void* const* relu_bits, const float* probs, const uint8_t* mask, const float* target,
+                    float* grads, int with_bias, void* scratch, size_t scratch_bytes, float* loss,
+                    void* stream);
 
 /* params -= lr * grads over n elements, and w_compute (may be NULL) = params
  * rounded to compute_dtype.  No counterpart in the reference. */
@@ -182,7 +193,8 @@ int sb_sgd_update(float* params, const float* grads, void* w_compute, long long 
 
 /* Single-GPU training step: forward, backward over this batch, SGD. */
 int sb_mlp_train_step(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
-                      float* params, void* w_compute, void* const* activations, const uint8_t* mask,
+                      float* params, void* w_compute, void* const* activations, void* const* relu_bits,
+                      const uint8_t* mask,
                       const float* target, float* probs, float* grads, int with_bias, float lr,
                       void* scratch, size_t scratch_bytes, float* loss, void* stream);
 

@@ -32,11 +32,13 @@
 namespace {
 
 constexpr int UG_BLOCK_M = 128;
-constexpr int UG_THREADS = 192;
+constexpr int UG_EPI_WARPS = 4;      // 4 or 8: one or two warps per TMEM lane quadrant
+constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;   // a warp takes every UG_EPI_STRIDE-th 32-column chunk
+constexpr int UG_THREADS = 64 + 32 * UG_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
 constexpr int UG_HEAD_MAX_N = 32;  // widest row a fused head keeps in registers
-constexpr int UG_EPI_STAGING = 4 * 4096;  // one 32-row x 128-byte box per epilogue warp
+constexpr int UG_EPI_STAGING = UG_EPI_WARPS * 4096;  // one 32-row x 128-byte box per epilogue warp
 
 struct UmmaGemmParams {
   int M, N, K;
@@ -177,18 +179,25 @@ __device__ __forceinline__ void load_chunk_to_box(const OutT* base, long long ld
 // re-read after every shared-memory asm statement, and with the whole L1 carved
 // out as shared memory each such read costs an L2 round trip.
 struct EpiArgs {
-  void* c;             // output, already offset to this split's partial
-  const void* aux;     // activation tile for the ReLU-gradient gate
+  void* c;                  // output, already offset to this split's partial
+  const void* aux;          // activation tile for the ReLU-gradient gate (SB_EPI_RELU_GRAD)
   const float* bias;
+  const uint32_t* gate_in;  // ReLU sign bits, one word per row and 32 columns (SB_EPI_RELU_GRAD_MASK)
+  uint32_t* gate_out;       // where the forward pass records them (SB_EPI_RELU_MASK_OUT)
   long long ldc;
   int M, N;
+  int gate_ld;              // words per row of the sign-bit matrices = N / 32
   float alpha, beta;
   bool has_bias, relu, relu_grad, coalesced;
 };
 
+// Finishes one 32-column chunk.  `bias_lane` = bias[col0 + lane]; `gate` = this
+// row's 32 ReLU sign bits of the chunk (when gating by bits).  Returns the sign
+// bits of the values this row produced (bit j = value j > 0 before the ReLU).
 template <typename OutT, bool ROUND_TF32>
-__device__ __forceinline__ void coalesced_chunk(const EpiArgs& e, float* v, float bias_lane, long long row0_warp,
-                                                int col0, uint32_t sbuf, int lane) {
+__device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, float bias_lane, uint32_t gate,
+                                                    long long row0_warp, int col0, uint32_t sbuf,
+                                                    uint32_t bias_smem, int lane) {
   constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
   constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
   constexpr int ROWS_PER_INST = 32 / PIECES;
@@ -204,14 +213,32 @@ __device__ __forceinline__ void coalesced_chunk(const EpiArgs& e, float* v, floa
       for (int t = 0; t < VEC; ++t) v[q * VEC + t] = e.alpha * v[q * VEC + t] + e.beta * load_as_float<OutT>(o + t);
     }
     __syncwarp();
-  } else {
+  } else if (e.alpha != 1.0f) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
   }
   if (e.has_bias) {
-    // Lane j holds bias[col0 + j]; every lane needs all 32 of them.
+    // Lane j holds bias[col0 + j]; every lane needs all 32: spread them through
+    // 128 bytes of shared memory and read them back as broadcasts.
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(bias_smem + 4u * (uint32_t)lane), "f"(bias_lane) : "memory");
+    __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
+    for (int q = 0; q < 8; ++q) {
+      const uint4 b = ld_shared_v4(bias_smem + 16u * (uint32_t)q);
+      v[4 * q + 0] += __uint_as_float(b.x);
+      v[4 * q + 1] += __uint_as_float(b.y);
+      v[4 * q + 2] += __uint_as_float(b.z);
+      v[4 * q + 3] += __uint_as_float(b.w);
+    }
+  }
+  uint32_t signs = 0u;
+  if (e.gate_out) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) signs |= (v[j] > 0.f ? 1u : 0u) << j;
+  }
+  if (e.gate_in) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = ((gate >> j) & 1u) ? v[j] : 0.f;
   }
   if (e.relu_grad)
     load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(e.aux), e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
@@ -253,14 +280,17 @@ __device__ __forceinline__ void coalesced_chunk(const EpiArgs& e, float* v, floa
     }
   }
   __syncwarp();
+  return signs;
 }
 
 // Per-thread stores of `w` (16 or 32) columns of one row: the fallback when C's
 // row pitch or base is not 16-byte aligned, and the 16-column tail chunk.
 template <typename OutT, bool ROUND_TF32>
-__device__ __forceinline__ void direct_chunk(const EpiArgs& e, float* v, int w, long long row, int col0) {
+__device__ __forceinline__ uint32_t direct_chunk(const EpiArgs& e, float* v, uint32_t gate, int w, long long row,
+                                                 int col0) {
   const int valid = min(w, e.N - col0);
-  if (valid <= 0) return;
+  uint32_t signs = 0u;
+  if (valid <= 0) return signs;
   OutT* crow = reinterpret_cast<OutT*>(e.c) + row * e.ldc + col0;
   const OutT* arow = reinterpret_cast<const OutT*>(e.aux) + row * e.ldc + col0;
 #pragma unroll
@@ -269,38 +299,82 @@ __device__ __forceinline__ void direct_chunk(const EpiArgs& e, float* v, int w, 
       float x = e.alpha * v[j];
       if (e.beta != 0.0f) x += e.beta * load_as_float<OutT>(crow + j);
       if (e.has_bias) x += __ldg(e.bias + col0 + j);
+      signs |= (x > 0.f ? 1u : 0u) << j;
+      if (e.gate_in) x = ((gate >> j) & 1u) ? x : 0.f;
       if (e.relu) x = fmaxf(x, 0.f);
       if (e.relu_grad) x = load_as_float<OutT>(arow + j) > 0.f ? x : 0.f;
       if (ROUND_TF32) x = round_tf32_rn(x);
       crow[j] = float_to<OutT>(x);
     }
   }
+  return signs;
 }
 
-// One warp drains its 32 accumulator rows of a tile: block_n columns in chunks
-// of 32 (a trailing chunk of 16 when block_n % 32 == 16).  Out of line and one
-// instance per output type, so that only one variant's registers are live.
+// One warp drains its share of a tile: its 32 accumulator rows (TMEM lane
+// quadrant) and every UG_EPI_STRIDE-th 32-column chunk starting at `half` (with 8
+// epilogue warps two warps share a quadrant).  The bias values and ReLU sign word of a chunk are requested one
+// chunk ahead (the first before the wait for the accumulator), and the TMEM
+// load of the next chunk is in flight while the current one is finished.  Out
+// of line, one instance per output type.  Returns false when the wait for the
+// accumulator expired.
 template <typename OutT, bool ROUND_TF32>
-__device__ __noinline__ void epilogue_tile(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0,
-                                           uint32_t sbuf, int lane) {
+__device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0,
+                                           uint32_t sbuf, uint32_t bias_smem, int lane, int half,
+                                           uint32_t bar_full, uint32_t parity, volatile int* abortp) {
   const long long row = (long long)row0_warp + lane;
   const bool row_ok = row < e.M;
-  for (int c0 = 0; c0 < block_n; c0 += 32) {
-    const int w = min(32, block_n - c0);
-    const int col0 = n0 + c0;
-    // The bias load (an L2 round trip) is issued before the TMEM load so that the two overlap.
-    float bias_lane = 0.f;
-    if (e.has_bias && col0 + lane < e.N) bias_lane = __ldg(e.bias + col0 + lane);
-    uint32_t raw[32];
-    if (w == 32) tmem_ld32(t_row + (uint32_t)c0, raw); else tmem_ld16(t_row + (uint32_t)c0, raw);
+  const int nchunks = (block_n + 31) >> 5;
+  const int nfull = e.coalesced ? (block_n >> 5) : 0;     // chunks that take the coalesced path
+  const bool rows_live = row0_warp < e.M;
+
+  auto fetch = [&](int c, float& bias_lane, uint32_t& gate) {
+    bias_lane = 0.f;
+    gate = 0u;
+    const int col0 = n0 + c * 32;
+    if (c < nchunks) {
+      if (e.has_bias && col0 + lane < e.N) bias_lane = __ldg(e.bias + col0 + lane);
+      if (e.gate_in && row_ok && col0 < e.N) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
+    }
+  };
+  auto finish = [&](float* v, int c, float bias_lane, uint32_t gate) {
+    const int col0 = n0 + c * 32;
+    if (rows_live && col0 < e.N) {
+      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32>(e, v, bias_lane, gate, row0_warp, col0, sbuf, bias_smem, lane);
+      if (e.gate_out && row_ok) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
+    }
+  };
+
+  int c = half;
+  float bias_cur, bias_nxt;
+  uint32_t gate_cur, gate_nxt;
+  fetch(c, bias_cur, gate_cur);
+  if (!mbar_wait(bar_full, parity, abortp, SB_SITE_EPI_TMEM_FULL)) return false;
+  tc_fence_after_sync();
+
+  uint32_t raw_a[32];
+  for (; c < nfull; c += UG_EPI_STRIDE) {
+    tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
+    fetch(c + UG_EPI_STRIDE, bias_nxt, gate_nxt);    // in flight while this chunk is finished
     tmem_ld_wait();
-    float* v = reinterpret_cast<float*>(raw);
-    if (e.coalesced && w == 32) {
-      if (row0_warp < e.M && col0 < e.N) coalesced_chunk<OutT, ROUND_TF32>(e, v, bias_lane, row0_warp, col0, sbuf, lane);
-    } else if (row_ok) {
-      direct_chunk<OutT, ROUND_TF32>(e, v, w, row, col0);
+    finish(reinterpret_cast<float*>(raw_a), c, bias_cur, gate_cur);
+    bias_cur = bias_nxt;
+    gate_cur = gate_nxt;
+  }
+  // What is left for this warp: a 16-column tail chunk, or every chunk when C
+  // cannot take row-contiguous 16-byte stores.
+  for (; c < nchunks; c += UG_EPI_STRIDE) {
+    const int w = min(32, block_n - c * 32);
+    if (w == 32) tmem_ld32(t_row + (uint32_t)(c * 32), raw_a); else tmem_ld16(t_row + (uint32_t)(c * 32), raw_a);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (row_ok && col0 < e.N) {
+      uint32_t gate = 0u;
+      if (e.gate_in) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
+      const uint32_t signs = direct_chunk<OutT, ROUND_TF32>(e, reinterpret_cast<float*>(raw_a), gate, w, row, col0);
+      if (e.gate_out) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
     }
   }
+  return true;
 }
 
 // Row head on a full row (N <= 32) held by one thread; fp32 output.
@@ -382,6 +456,7 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
 }
 
 constexpr int EPI_HEAD_MASK = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
+constexpr int EPI_GATE_MASK = SB_EPI_RELU_MASK_OUT | SB_EPI_RELU_GRAD_MASK;
 
 // PAIR = false: one CTA per 128 x block_n tile (cta_group::1).
 // PAIR = true : a cluster of two CTAs per 256 x block_n tile (cta_group::2).
@@ -404,6 +479,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) float bias_spread[UG_EPI_WARPS][32];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -427,7 +503,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tmem_full[a]), 1);
-      mbar_init(smem_u32(&bar_tmem_empty[a]), PAIR ? 8 : 4);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), PAIR ? 2 * UG_EPI_WARPS : UG_EPI_WARPS);
     }
     abort_flag = 0;
     fence_mbar_init();
@@ -575,41 +651,55 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   } else {
-    // Epilogue warps 2..5; TMEM lane quadrant = warp index modulo 4.
+    // Epilogue warps.  A warp may only read the TMEM lane quadrant given by its index
+    // modulo 4; with 8 warps the two warps of a quadrant take alternate 32-column chunks.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool head = (p.epi & EPI_HEAD_MASK) != 0;
     const uint32_t sbuf = stage_base + p.epi_offset + (uint32_t)(warp - 2) * 4096u;
+    const uint32_t bias_smem = smem_u32(&bias_spread[warp - 2][0]);
+    EpiArgs e;
+    e.aux = p.aux_in; e.bias = p.bias; e.ldc = p.ldc; e.M = p.M; e.N = p.N;
+    e.alpha = p.alpha; e.beta = p.beta;
+    e.has_bias = (p.epi & SB_EPI_BIAS) != 0; e.relu = (p.epi & SB_EPI_RELU) != 0;
+    e.relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0; e.coalesced = p.coalesced != 0;
+    e.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
+    e.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
+    e.gate_ld = p.N >> 5;
     for (int work = worker; work < p.num_work; work += num_workers) {
       const int split = work / p.num_tiles;
       const long long c_off = (long long)split * p.split_stride;
       int m_blk, n_blk;
       tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
-      if (!mbar_wait(smem_u32(&bar_tmem_full[acc]), acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
-      tc_fence_after_sync();
       const int row0_warp = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M + quad * 32;
-      const long long row = (long long)row0_warp + lane;
-      const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
+      const uint32_t full_bar = smem_u32(&bar_tmem_full[acc]);
       if (head) {
-        uint32_t raw[32];
-        if (p.block_n >= 32) tmem_ld32(t_row, raw); else tmem_ld16(t_row, raw);
-        tmem_ld_wait();
-        if (row_ok) finish_head(p, reinterpret_cast<float*>(raw), row);
+        if (!mbar_wait(full_bar, acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
+        tc_fence_after_sync();
+        if (half == 0) {               // a head row is one chunk: the second warp of the quadrant idles
+          const long long row = (long long)row0_warp + lane;
+          uint32_t raw[32];
+          if (p.block_n >= 32) tmem_ld32(t_row, raw); else tmem_ld16(t_row, raw);
+          tmem_ld_wait();
+          if (row < p.M) finish_head(p, reinterpret_cast<float*>(raw), row);
+        }
       } else {
         const int n0 = n_blk * p.block_n;
-        EpiArgs e;
-        e.aux = p.aux_in; e.bias = p.bias; e.ldc = p.ldc; e.M = p.M; e.N = p.N;
-        e.alpha = p.alpha; e.beta = p.beta;
-        e.has_bias = (p.epi & SB_EPI_BIAS) != 0; e.relu = (p.epi & SB_EPI_RELU) != 0;
-        e.relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0; e.coalesced = p.coalesced != 0;
         if (p.out_dtype == SB_F32 || p.out_dtype == SB_TF32) e.c = reinterpret_cast<float*>(p.C) + c_off;
         else e.c = reinterpret_cast<uint16_t*>(p.C) + c_off;
-        if (p.out_dtype == SB_F32) epilogue_tile<float, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
-        else if (p.out_dtype == SB_TF32) epilogue_tile<float, true>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
-        else if (p.out_dtype == SB_BF16) epilogue_tile<__nv_bfloat16, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
-        else epilogue_tile<__half, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, lane);
+        bool ok;
+        if (p.out_dtype == SB_F32)
+          ok = epilogue_tile<float, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
+        else if (p.out_dtype == SB_TF32)
+          ok = epilogue_tile<float, true>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
+        else if (p.out_dtype == SB_BF16)
+          ok = epilogue_tile<__nv_bfloat16, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
+        else
+          ok = epilogue_tile<__half, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
+        if (!ok) break;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -724,7 +814,7 @@ int cached_sm_count() {
 // Chooses block_n / stages / grid for a problem; `sms` = SM count to plan for.
 // `allow_pair`: CTA pairs may be used (needs at least two 128-row blocks and a
 // tile at least 64 columns wide; row heads stay on single CTAs).
-void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair) {
+void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair, bool chunks32 = false) {
   const int es = sb_dtype_size(in_dtype);
   p.block_k = 128 / es;
   p.k_blocks = (p.K + p.block_k - 1) / p.block_k;
@@ -736,7 +826,8 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair) {
   p.tiles_m = (p.M + tile_m - 1) / tile_m;
   // Column granularity of a tile: 16 for a K-major B (32 in a pair, 16 per CTA);
   // an MN-major B needs whole 128-byte boxes per CTA.
-  const int gran = (p.b_mn ? p.mn_box_elems : 16) * (p.pair ? 2 : 1);
+  int gran = (p.b_mn ? p.mn_box_elems : 16) * (p.pair ? 2 : 1);
+  if (chunks32 && gran < 32) gran = 32;   // the ReLU sign words cover whole 32-column chunks
   int best_bn = 0;
   if (p.N <= 256) {
     best_bn = round_up_int(p.N, gran);
@@ -828,7 +919,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_trans ? 1 : 0;   // A stored [K,M]: M contiguous
   p.b_mn = b_trans ? 0 : 1;   // B stored [K,N]: N contiguous
-  plan_umma(p, in_dtype, cached_sm_count(), !(epi & EPI_HEAD_MASK) && sb_pair_mode_enabled());
+  plan_umma(p, in_dtype, cached_sm_count(), !(epi & EPI_HEAD_MASK) && sb_pair_mode_enabled(), (epi & EPI_GATE_MASK) != 0);
   p.alpha = alpha; p.beta = beta;
   p.C = C; p.ldc = N; p.out_dtype = out_dtype;
   p.epi = epi; p.bias = bias; p.mask = mask; p.aux_in = aux_in; p.aux_out = aux_out;
@@ -868,17 +959,17 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   const int es_out = out_dtype == SB_BF16 || out_dtype == SB_F16 ? 2 : 4;
   p.coalesced = (!(epi & EPI_HEAD_MASK) && ((long long)N * es_out) % 16 == 0 &&
                  (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
-                 (!aux_in || (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0)) ? 1 : 0;
+                 (!(epi & SB_EPI_RELU_GRAD) || (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0)) ? 1 : 0;
 
   const size_t smem = umma_dyn_smem(p);
   static bool attr_set[64] = {false};
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
-    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
-    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
-    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 1024));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     attr_set[dev] = true;
   }
   sb_prof_before(stream);

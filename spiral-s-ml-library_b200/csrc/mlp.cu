@@ -198,8 +198,9 @@ int sb_mlp_param_offsets(int n_layers, const int* sizes, long long* offsets) {
 }
 
 int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
-                   const void* w_compute, const float* params, void* const* activations, int head,
-                   const uint8_t* mask, float* out, int32_t* actions, void* stream) {
+                   const void* w_compute, const float* params, void* const* activations,
+                   void* const* relu_bits, int head, const uint8_t* mask, float* out, int32_t* actions,
+                   void* stream) {
   int rc = check_layout("sb_mlp_forward", n_layers, sizes, batch, in_dtype);
   if (rc != SB_OK) return rc;
   if (batch == 0) return SB_OK;
@@ -229,9 +230,11 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
       epi |= SB_EPI_RELU;
       dst = activations[i];
       odt = st;
+      if (relu_bits && relu_bits[i] && sizes[i + 1] % 32 == 0) epi |= SB_EPI_RELU_MASK_OUT;
     }
+    void* aux_out = last ? (void*)actions : ((epi & SB_EPI_RELU_MASK_OUT) ? relu_bits[i] : nullptr);
     rc = sb_matmul_ex(0, 1, 1.0f, h, w, 0.0f, dst, batch, sizes[i + 1], sizes[i], in_dtype, odt, epi, b,
-                      last ? mask : nullptr, nullptr, last ? actions : nullptr, stream);
+                      last ? mask : nullptr, nullptr, aux_out, stream);
     if (rc != SB_OK) return rc;
     h = dst;
   }
@@ -248,8 +251,9 @@ int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int
 
 int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
                     const void* x, const void* w_compute, void* const* activations,
-                    const float* probs, const uint8_t* mask, const float* target, float* grads,
-                    int with_bias, void* scratch, size_t scratch_bytes, float* loss, void* stream) {
+                    void* const* relu_bits, const float* probs, const uint8_t* mask, const float* target,
+                    float* grads, int with_bias, void* scratch, size_t scratch_bytes, float* loss,
+                    void* stream) {
   int rc = check_layout("sb_mlp_backward", n_layers, sizes, batch, in_dtype);
   if (rc != SB_OK) return rc;
   if (!grads) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: grads is null");
@@ -328,8 +332,12 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
     // dgrad (NN): dH[B, in] = dY [B, out] * W [out, in], gated by ReLU'(H_in)
     if (i > 0) {
       const void* w = reinterpret_cast<const char*>(w_compute) + off[2 * i] * es;
+      // The gate is ReLU'(H_in): read from the sign bits the forward pass recorded
+      // when they exist (4 bytes per row and 32 columns), else from H_in itself.
+      const bool bits = relu_bits && relu_bits[i - 1] && fan_in % 32 == 0;
       rc = sb_umma_gemm_launch(0, 0, 1.0f, dy_cur, w, 0.0f, dy_next, batch, fan_in, fan_out, in_dtype, st,
-                               SB_EPI_RELU_GRAD, nullptr, nullptr, h_in, nullptr, s, 1, nullptr);
+                               bits ? SB_EPI_RELU_GRAD_MASK : SB_EPI_RELU_GRAD, nullptr, nullptr,
+                               bits ? (const void*)relu_bits[i - 1] : h_in, nullptr, s, 1, nullptr);
       if (rc != SB_OK) return rc;
       void* t = dy_cur; dy_cur = dy_next; dy_next = t;
     }
@@ -349,14 +357,16 @@ int sb_sgd_update(float* params, const float* grads, void* w_compute, long long 
 }
 
 int sb_mlp_train_step(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
-                      float* params, void* w_compute, void* const* activations, const uint8_t* mask,
+                      float* params, void* w_compute, void* const* activations, void* const* relu_bits,
+                      const uint8_t* mask,
                       const float* target, float* probs, float* grads, int with_bias, float lr,
                       void* scratch, size_t scratch_bytes, float* loss, void* stream) {
   int rc = sb_mlp_forward(n_layers, sizes, batch, in_dtype, x, w_compute, with_bias ? params : nullptr,
-                          activations, SB_EPI_MASKED_SOFTMAX, mask, probs, nullptr, stream);
+                          activations, relu_bits, SB_EPI_MASKED_SOFTMAX, mask, probs, nullptr, stream);
   if (rc != SB_OK) return rc;
   rc = sb_mlp_backward(n_layers, sizes, batch, batch > 0 ? 1.0f / (float)batch : 0.f, in_dtype, x, w_compute,
-                       activations, probs, mask, target, grads, with_bias, scratch, scratch_bytes, loss, stream);
+                       activations, relu_bits, probs, mask, target, grads, with_bias, scratch, scratch_bytes, loss,
+                       stream);
   if (rc != SB_OK) return rc;
   long long off[2 * MLP_MAX_LAYERS + 1];
   param_offsets(n_layers, sizes, off);

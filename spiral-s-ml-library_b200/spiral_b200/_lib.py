@@ -23,6 +23,7 @@ DTYPE_CODES = {"f32": F32, "tf32": TF32, "bf16": BF16, "f16": F16, "i32": I32, "
 # epilogue flags
 EPI_NONE, EPI_BIAS, EPI_RELU, EPI_RELU_GRAD = 0, 1, 2, 4
 EPI_MASKED_SOFTMAX, EPI_REGRET_MATCHING, EPI_ARGMAX = 8, 16, 32
+EPI_RELU_MASK_OUT, EPI_RELU_GRAD_MASK = 64, 128
 
 
 class SpiralError(RuntimeError):
@@ -78,11 +79,11 @@ SIGNATURES = {
     "sb_row_ln_l2": (_I, [_P, _P, _I, _I, _P]),
     "sb_convert": (_I, [_P, _P, _Z, _I, _P]),
     "sb_mlp_param_offsets": (_I, [_I, _IP, POINTER(ctypes.c_longlong)]),
-    "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _I, _P, _P, _P, _P]),
+    "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),
     "sb_mlp_backward_scratch_bytes": (_I, [_I, _IP, _I, _I, POINTER(c_size_t)]),
-    "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),
+    "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),
     "sb_sgd_update": (_I, [_P, _P, _P, ctypes.c_longlong, _F, _I, _P]),
-    "sb_mlp_train_step": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _P, _P, _P, _P, _I, _F, _P, _Z, _P, _P]),
+    "sb_mlp_train_step": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _F, _P, _Z, _P, _P]),
 }
 
 _lib = None

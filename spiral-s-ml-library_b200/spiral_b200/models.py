@@ -55,6 +55,14 @@ class PolicyMLP:
         self.probs = DeviceArray((self.batch, self.sizes[-1]), "f32")
         self.actions = DeviceArray((self.batch,), "i32") if "argmax" in self.head else None
         self.training = bool(training)
+        # ReLU sign bits of every hidden layer (uint32 [batch, width / 32]): recorded by the
+        # forward pass when training so that backward gates by bits instead of re-reading H.
+        self.relu_bits = []
+        self._bits_c = None
+        if self.training and all(w % 32 == 0 for w in self.sizes[1:-1]) and self.n_layers > 1:
+            self.relu_bits = [DeviceArray((self.batch, self.sizes[i + 1] // 32), "i32")
+                              for i in range(self.n_layers - 1)]
+            self._bits_c = (ctypes.c_void_p * (self.n_layers - 1))(*[b.ptr for b in self.relu_bits])
         self.grads = None
         self.scratch = None
         self.loss = None
@@ -109,7 +117,7 @@ class PolicyMLP:
         flags = self.head_flags if head_flags is None else head_flags
         _lib.call("sb_mlp_forward", self.n_layers, self._sizes_c, self.batch, _lib.DTYPE_CODES[self.in_dtype],
                   device_ptr(x), self.w_compute.ptr, self.params.ptr if self.with_bias else None, self._acts_c,
-                  flags, device_ptr(mask), self.probs.ptr, device_ptr(self.actions) if flags & _lib.EPI_ARGMAX else None,
+                  self._bits_c, flags, device_ptr(mask), self.probs.ptr, device_ptr(self.actions) if flags & _lib.EPI_ARGMAX else None,
                   stream_ptr(stream))
         return self.probs
 
@@ -117,7 +125,8 @@ class PolicyMLP:
         """grads <- d(mean cross-entropy)/d(params) for this shard (after a masked-softmax forward)."""
         gb = self.batch if global_batch is None else int(global_batch)
         _lib.call("sb_mlp_backward", self.n_layers, self._sizes_c, self.batch, ctypes.c_float(1.0 / gb),
-                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr, self._acts_c, self.probs.ptr,
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr, self._acts_c, self._bits_c,
+                  self.probs.ptr,
                   device_ptr(mask), device_ptr(target), device_ptr(self.grads), int(self.with_bias),
                   self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
         return self.grads
@@ -130,7 +139,7 @@ class PolicyMLP:
     def train_step(self, x, mask, target, lr, stream=None):
         """Forward + backward + SGD on one GPU (no gradient exchange)."""
         _lib.call("sb_mlp_train_step", self.n_layers, self._sizes_c, self.batch, _lib.DTYPE_CODES[self.in_dtype],
-                  device_ptr(x), self.params.ptr, self.w_compute.ptr, self._acts_c, device_ptr(mask),
+                  device_ptr(x), self.params.ptr, self.w_compute.ptr, self._acts_c, self._bits_c, device_ptr(mask),
                   device_ptr(target), self.probs.ptr, device_ptr(self.grads), int(self.with_bias),
                   ctypes.c_float(lr), self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
 

@@ -136,6 +136,28 @@ def test_relu_grad_epilogue(gpu):
     assert np.all(got[act <= 0] == 0)
 
 
+def test_relu_sign_bits_forward_and_backward_gate(gpu):
+    """SB_EPI_RELU_MASK_OUT records bit j of word [row, c] = (value[row, 32c+j] > 0); gating a second
+    GEMM by those bits equals gating by the activation tile itself."""
+    m, n, k = 300, 320, 128
+    a, b, c = operands(31, False, True, m, n, k, "bf16")
+    bits = gpu.DeviceArray.zeros((m, n // 32), "i32")
+    act = run(gpu, False, True, 1.0, a, b, 0.0, c, "bf16", out_dtype="bf16", epilogue=("relu", "relu_mask_out"),
+              aux_out=bits)
+    pre = so.matmul(False, True, 1.0, a, b, 0.0, None)
+    want_bits = np.packbits((pre > 0).reshape(m, n // 32, 32), axis=-1, bitorder="little").view(np.uint32).reshape(m, n // 32)
+    got_bits = bits.numpy().view(np.uint32)
+    decided = np.abs(pre) > 1e-3                       # leave out values within rounding of zero
+    diff = np.unpackbits((got_bits ^ want_bits).view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n)
+    assert not (diff.astype(bool) & decided).any()
+    np.testing.assert_array_equal(act > 0, np.unpackbits(got_bits.view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n).astype(bool))
+    a2, b2, c2 = operands(32, False, False, m, n, 64, "bf16")
+    by_bits = run(gpu, False, False, 1.0, a2, b2, 0.0, c2, "bf16", out_dtype="bf16", epilogue=("relu_grad_mask",), aux_in=bits)
+    by_tile = run(gpu, False, False, 1.0, a2, b2, 0.0, c2, "bf16", out_dtype="bf16", epilogue=("relu_grad",),
+                  aux_in=gpu.DeviceArray.from_numpy(act, "bf16"))
+    np.testing.assert_array_equal(by_bits, by_tile)
+
+
 @pytest.mark.parametrize("n", [3, 10, 16, 17, 32, 40])
 @pytest.mark.parametrize("heads", [("masked_softmax",), ("regret_matching",), ("masked_softmax", "regret_matching")])
 def test_fused_row_heads(gpu, n, heads):
