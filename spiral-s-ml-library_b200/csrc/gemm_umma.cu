@@ -32,7 +32,7 @@
 namespace {
 
 constexpr int UG_BLOCK_M = 128;
-constexpr int UG_EPI_WARPS = 4;      // 4 or 8: one or two warps per TMEM lane quadrant
+constexpr int UG_EPI_WARPS = 8;      // 4 or 8: one or two warps per TMEM lane quadrant
 constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;   // a warp takes every UG_EPI_STRIDE-th 32-column chunk
 constexpr int UG_THREADS = 64 + 32 * UG_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr int UG_MAX_STAGES = 8;
@@ -194,7 +194,10 @@ struct EpiArgs {
 // Finishes one 32-column chunk.  `bias_lane` = bias[col0 + lane]; `gate` = this
 // row's 32 ReLU sign bits of the chunk (when gating by bits).  Returns the sign
 // bits of the values this row produced (bit j = value j > 0 before the ReLU).
-template <typename OutT, bool ROUND_TF32>
+// GENERAL = false leaves out the two rarely used features that read a second
+// tile (beta != 0 and the activation-tile gate), which keeps the common variants
+// inside the register budget of a 10-warp CTA.
+template <typename OutT, bool ROUND_TF32, bool GENERAL>
 __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, float bias_lane, uint32_t gate,
                                                     long long row0_warp, int col0, uint32_t sbuf,
                                                     uint32_t bias_smem, int lane) {
@@ -202,7 +205,7 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
   constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
   constexpr int ROWS_PER_INST = 32 / PIECES;
   OutT* cbase = reinterpret_cast<OutT*>(e.c);
-  if (e.beta != 0.0f) {
+  if (GENERAL && e.beta != 0.0f) {
     // v <- alpha * acc + beta * C_old, with the old tile read through the box.
     load_chunk_to_box<OutT>(cbase, e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
 #pragma unroll
@@ -240,27 +243,30 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = ((gate >> j) & 1u) ? v[j] : 0.f;
   }
-  if (e.relu_grad)
+  const bool tile_gate = GENERAL && e.relu_grad;
+  if (tile_gate)
     load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(e.aux), e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
 #pragma unroll
   for (int q = 0; q < PIECES; ++q) {
     const uint32_t mine = sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
     uint4 araw = make_uint4(0u, 0u, 0u, 0u);
-    if (e.relu_grad) araw = ld_shared_v4(mine);     // this lane's piece of the activation tile
+    if (tile_gate) araw = ld_shared_v4(mine);     // this lane's piece of the activation tile
     const OutT* acte = reinterpret_cast<const OutT*>(&araw);
     OutT outv[VEC];
 #pragma unroll
     for (int t = 0; t < VEC; ++t) {
       float x = v[q * VEC + t];
       if (e.relu) x = fmaxf(x, 0.f);
-      if (e.relu_grad) x = load_as_float<OutT>(acte + t) > 0.f ? x : 0.f;
+      if (tile_gate) x = load_as_float<OutT>(acte + t) > 0.f ? x : 0.f;
       if (ROUND_TF32) x = round_tf32_rn(x);
       outv[t] = float_to<OutT>(x);
     }
     st_shared_v4(mine, *reinterpret_cast<const uint4*>(outv));   // overwrites only what this lane just read
   }
   __syncwarp();
-#pragma unroll
+  // Not fully unrolled: eight independent 64-bit store addresses at once would
+  // push the 32-bit-output variant past its register budget.
+#pragma unroll 2
   for (int i = 0; i < PIECES; ++i) {
     const int r = i * ROWS_PER_INST + lane / PIECES;
     const int q = lane % PIECES;
@@ -310,6 +316,29 @@ __device__ __forceinline__ uint32_t direct_chunk(const EpiArgs& e, float* v, uin
   return signs;
 }
 
+// Chunks that cannot take the coalesced path, from chunk `c` on: per-thread stores.
+// A function of its own so that its registers do not add to the fast path's.
+template <typename OutT, bool ROUND_TF32>
+__device__ __noinline__ void epilogue_rest(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0, int lane,
+                                           int c) {
+  const long long row = (long long)row0_warp + lane;
+  const bool row_ok = row < e.M;
+  const int nchunks = (block_n + 31) >> 5;
+  for (; c < nchunks; c += UG_EPI_STRIDE) {
+    uint32_t raw[32];
+    const int w = min(32, block_n - c * 32);
+    if (w == 32) tmem_ld32(t_row + (uint32_t)(c * 32), raw); else tmem_ld16(t_row + (uint32_t)(c * 32), raw);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (row_ok && col0 < e.N) {
+      uint32_t gate = 0u;
+      if (e.gate_in) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
+      const uint32_t signs = direct_chunk<OutT, ROUND_TF32>(e, reinterpret_cast<float*>(raw), gate, w, row, col0);
+      if (e.gate_out) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
+    }
+  }
+}
+
 // One warp drains its share of a tile: its 32 accumulator rows (TMEM lane
 // quadrant) and every UG_EPI_STRIDE-th 32-column chunk starting at `half` (with 8
 // epilogue warps two warps share a quadrant).  The bias values and ReLU sign word of a chunk are requested one
@@ -317,7 +346,7 @@ __device__ __forceinline__ uint32_t direct_chunk(const EpiArgs& e, float* v, uin
 // load of the next chunk is in flight while the current one is finished.  Out
 // of line, one instance per output type.  Returns false when the wait for the
 // accumulator expired.
-template <typename OutT, bool ROUND_TF32>
+template <typename OutT, bool ROUND_TF32, bool GENERAL>
 __device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0,
                                            uint32_t sbuf, uint32_t bias_smem, int lane, int half,
                                            uint32_t bar_full, uint32_t parity, volatile int* abortp) {
@@ -339,7 +368,7 @@ __device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_
   auto finish = [&](float* v, int c, float bias_lane, uint32_t gate) {
     const int col0 = n0 + c * 32;
     if (rows_live && col0 < e.N) {
-      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32>(e, v, bias_lane, gate, row0_warp, col0, sbuf, bias_smem, lane);
+      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, GENERAL>(e, v, bias_lane, gate, row0_warp, col0, sbuf, bias_smem, lane);
       if (e.gate_out && row_ok) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
     }
   };
@@ -362,34 +391,34 @@ __device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_
   }
   // What is left for this warp: a 16-column tail chunk, or every chunk when C
   // cannot take row-contiguous 16-byte stores.
-  for (; c < nchunks; c += UG_EPI_STRIDE) {
-    const int w = min(32, block_n - c * 32);
-    if (w == 32) tmem_ld32(t_row + (uint32_t)(c * 32), raw_a); else tmem_ld16(t_row + (uint32_t)(c * 32), raw_a);
-    tmem_ld_wait();
-    const int col0 = n0 + c * 32;
-    if (row_ok && col0 < e.N) {
-      uint32_t gate = 0u;
-      if (e.gate_in) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
-      const uint32_t signs = direct_chunk<OutT, ROUND_TF32>(e, reinterpret_cast<float*>(raw_a), gate, w, row, col0);
-      if (e.gate_out) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
-    }
-  }
+  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32>(e, t_row, block_n, row0_warp, n0, lane, c);
   return true;
 }
+
+struct HeadArgs {
+  void* C;
+  const float* bias;
+  const uint8_t* mask;
+  void* aux_out;
+  long long ldc;
+  int N, epi;
+  float alpha, beta;
+};
 
 // Row head on a full row (N <= 32) held by one thread; fp32 output.
 // Follows local_masked_softmax / local_masked_regret_matching / local_argmax
 // (ml/primitives.spi:748-780, 705-708); the softmax subtracts the masked
 // maximum, which equals the reference's masked-mean form exactly in exact
 // arithmetic and cannot overflow.
-__device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, long long row) {
+template <int UG_HEAD_W>
+__device__ __forceinline__ void finish_head(const HeadArgs& p, float* v, long long row) {
   const int n = p.N;
   float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc;
   const uint8_t* mrow = p.mask ? p.mask + row * (long long)n : nullptr;
   const bool has_beta = p.beta != 0.0f;
   uint32_t legal = 0;
 #pragma unroll
-  for (int j = 0; j < UG_HEAD_MAX_N; ++j) {
+  for (int j = 0; j < UG_HEAD_W; ++j) {
     if (j < n) {
       float x = p.alpha * v[j];
       if (has_beta) x += p.beta * crow[j];
@@ -403,11 +432,11 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
   if (p.epi & SB_EPI_MASKED_SOFTMAX) {
     float mx = -3.402823466e38f;
 #pragma unroll
-    for (int j = 0; j < UG_HEAD_MAX_N; ++j)
+    for (int j = 0; j < UG_HEAD_W; ++j)
       if (j < n && ((legal >> j) & 1u)) mx = fmaxf(mx, v[j]);
     float s = 0.f;
 #pragma unroll
-    for (int j = 0; j < UG_HEAD_MAX_N; ++j) {
+    for (int j = 0; j < UG_HEAD_W; ++j) {
       if (j < n) {
         float e = ((legal >> j) & 1u) ? __expf(v[j] - mx) : 0.f;
         v[j] = e;
@@ -416,13 +445,13 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
     }
     const float inv = s > 0.f ? 1.f / s : 0.f;
 #pragma unroll
-    for (int j = 0; j < UG_HEAD_MAX_N; ++j)
+    for (int j = 0; j < UG_HEAD_W; ++j)
       if (j < n) v[j] *= inv;
   }
   if (p.epi & SB_EPI_REGRET_MATCHING) {
     float s = 0.f;
 #pragma unroll
-    for (int j = 0; j < UG_HEAD_MAX_N; ++j) {
+    for (int j = 0; j < UG_HEAD_W; ++j) {
       if (j < n) {
         float q = ((legal >> j) & 1u) ? fmaxf(v[j], 0.f) : 0.f;
         v[j] = q;
@@ -431,7 +460,7 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
     }
     const float inv_len = count > 0 ? 1.f / (float)count : 0.f;
 #pragma unroll
-    for (int j = 0; j < UG_HEAD_MAX_N; ++j) {
+    for (int j = 0; j < UG_HEAD_W; ++j) {
       if (j < n) {
         const bool lg = (legal >> j) & 1u;
         v[j] = !lg ? 0.f : (s != 0.f ? v[j] / s : inv_len);
@@ -439,13 +468,13 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
     }
   }
 #pragma unroll
-  for (int j = 0; j < UG_HEAD_MAX_N; ++j)
+  for (int j = 0; j < UG_HEAD_W; ++j)
     if (j < n) crow[j] = v[j];
   if (p.epi & SB_EPI_ARGMAX) {
     int best = 0;
     float bv = v[0];
 #pragma unroll
-    for (int j = 1; j < UG_HEAD_MAX_N; ++j) {
+    for (int j = 1; j < UG_HEAD_W; ++j) {
       if (j < n && v[j] > bv) {
         bv = v[j];
         best = j;
@@ -453,6 +482,16 @@ __device__ __forceinline__ void finish_head(const UmmaGemmParams& p, float* v, l
     }
     reinterpret_cast<int32_t*>(p.aux_out)[row] = best;
   }
+}
+
+// One warp finishes the head rows of its TMEM lane quadrant; out of line for the
+// same reason as epilogue_tile.
+template <int W>
+__device__ __noinline__ void epilogue_head(HeadArgs h, uint32_t t_row, long long row, int M) {
+  uint32_t raw[W];
+  if (W == 32) tmem_ld32(t_row, raw); else tmem_ld16(t_row, raw);
+  tmem_ld_wait();
+  if (row < M) finish_head<W>(h, reinterpret_cast<float*>(raw), row);
 }
 
 constexpr int EPI_HEAD_MASK = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
@@ -668,6 +707,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     e.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
     e.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
     e.gate_ld = p.N >> 5;
+    const bool general = p.beta != 0.0f || e.relu_grad;
     for (int work = worker; work < p.num_work; work += num_workers) {
       const int split = work / p.num_tiles;
       const long long c_off = (long long)split * p.split_stride;
@@ -680,25 +720,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!mbar_wait(full_bar, acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
         tc_fence_after_sync();
         if (half == 0) {               // a head row is one chunk: the second warp of the quadrant idles
-          const long long row = (long long)row0_warp + lane;
-          uint32_t raw[32];
-          if (p.block_n >= 32) tmem_ld32(t_row, raw); else tmem_ld16(t_row, raw);
-          tmem_ld_wait();
-          if (row < p.M) finish_head(p, reinterpret_cast<float*>(raw), row);
+          HeadArgs h;
+          h.C = p.C; h.bias = p.bias; h.mask = p.mask; h.aux_out = p.aux_out; h.ldc = p.ldc;
+          h.N = p.N; h.epi = p.epi; h.alpha = p.alpha; h.beta = p.beta;
+          if (p.block_n >= 32) epilogue_head<32>(h, t_row, (long long)row0_warp + lane, p.M);
+          else epilogue_head<16>(h, t_row, (long long)row0_warp + lane, p.M);
         }
       } else {
         const int n0 = n_blk * p.block_n;
         if (p.out_dtype == SB_F32 || p.out_dtype == SB_TF32) e.c = reinterpret_cast<float*>(p.C) + c_off;
         else e.c = reinterpret_cast<uint16_t*>(p.C) + c_off;
         bool ok;
-        if (p.out_dtype == SB_F32)
-          ok = epilogue_tile<float, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
-        else if (p.out_dtype == SB_TF32)
-          ok = epilogue_tile<float, true>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
-        else if (p.out_dtype == SB_BF16)
-          ok = epilogue_tile<__nv_bfloat16, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
-        else
-          ok = epilogue_tile<__half, false>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp);
+#define SB_EPI_CALL(T, R, G) \
+  epilogue_tile<T, R, G>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp)
+        if (general) {
+          if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, true);
+          else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, true);
+          else if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, true);
+          else ok = SB_EPI_CALL(__half, false, true);
+        } else {
+          if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, false);
+          else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, false);
+          else if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, false);
+          else ok = SB_EPI_CALL(__half, false, false);
+        }
+#undef SB_EPI_CALL
         if (!ok) break;
       }
       tc_fence_before_sync();
