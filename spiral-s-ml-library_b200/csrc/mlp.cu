@@ -99,25 +99,45 @@ __global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __r
   }
 }
 
-// Column sums of dY [rows, n] -> db[n] (bias gradient).  Each block owns a slab
-// of rows and a 32-column strip; partial sums are combined with atomics into a
-// zeroed output, so db is summed in a run-dependent order (fp32, few terms).
+// Column sums of dY [rows, n] -> db[n] (bias gradient).  A block owns a slab of
+// rows and a strip of 32 * VEC columns; each thread reads 16-byte pieces (VEC
+// elements) so that a warp covers 512 contiguous bytes of a row, the 8 warps
+// take alternate rows, and the block's partial sums are combined with atomics
+// into a zeroed output (fp32, run-dependent order over a few hundred terms).
 template <typename DyT>
-__global__ void colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int n,
-                              int rows_per_block) {
-  __shared__ float part[8][33];
-  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+__global__ void __launch_bounds__(256)
+colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int n, int rows_per_block) {
+  constexpr int VEC = 16 / sizeof(DyT);
+  __shared__ float part[8][32 * VEC + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col0 = (blockIdx.x * 32 + lane) * VEC;
   const int r0 = blockIdx.y * rows_per_block;
   const int r1 = min(rows, r0 + rows_per_block);
-  float s = 0.f;
-  if (col < n)
-    for (int r = r0 + (threadIdx.x >> 5); r < r1; r += 8) s += (float)dy[(long long)r * n + col];
-  part[threadIdx.x >> 5][threadIdx.x & 31] = s;
+  float s[VEC];
+#pragma unroll
+  for (int t = 0; t < VEC; ++t) s[t] = 0.f;
+  const bool vec_ok = (n % VEC == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0) && col0 + VEC <= n;
+  if (vec_ok) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(dy + (long long)r * n + col0);
+      const DyT* e = reinterpret_cast<const DyT*>(&raw);
+#pragma unroll
+      for (int t = 0; t < VEC; ++t) s[t] += (float)e[t];
+    }
+  } else {
+    for (int r = r0 + warp; r < r1; r += 8)
+#pragma unroll
+      for (int t = 0; t < VEC; ++t)
+        if (col0 + t < n) s[t] += (float)dy[(long long)r * n + col0 + t];
+  }
+#pragma unroll
+  for (int t = 0; t < VEC; ++t) part[warp][lane * VEC + t] = s[t];
   __syncthreads();
-  if (threadIdx.x < 32) {
+  for (int j = threadIdx.x; j < 32 * VEC; j += 256) {
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) t += part[w][threadIdx.x];
+    for (int w = 0; w < 8; ++w) t += part[w][j];
+    const int col = blockIdx.x * 32 * VEC + j;
     if (col < n && t != 0.f) atomicAdd(db + col, t);
   }
 }
@@ -307,8 +327,13 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
     const int fan_out = padded_out(sizes[i + 1]), fan_in = sizes[i];
     const void* h_in = i == 0 ? x : activations[i - 1];
     if (with_bias) {
-      const int rows_per_block = 2048;
-      dim3 grid((fan_out + 31) / 32, (batch + rows_per_block - 1) / rows_per_block);
+      // Enough blocks to fill the GPU a few times over, each with a long row slab.
+      const int strip = 32 * (16 / es);
+      const int strips = (fan_out + strip - 1) / strip;
+      int slabs = (148 * 4 + strips - 1) / strips;
+      int rows_per_block = (batch + slabs - 1) / slabs;
+      if (rows_per_block < 64) rows_per_block = 64;
+      dim3 grid(strips, (batch + rows_per_block - 1) / rows_per_block);
       float* db = grads + off[2 * i + 1];
       if (in_dtype == SB_BF16) colsum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy_cur, db, batch, fan_out, rows_per_block);
       else if (in_dtype == SB_F16) colsum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)dy_cur, db, batch, fan_out, rows_per_block);
