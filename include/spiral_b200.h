@@ -171,6 +171,25 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
                    void* const* relu_bits, int head, const uint8_t* mask, float* out, int32_t* actions,
                    void* stream);
 
+/* The same forward pass for callers that cannot allocate device memory (a host
+ * that owns no allocator, a plugin in a context where allocation is forbidden,
+ * code inside a stream capture): the hidden activations live in a fixed array
+ * inside the library image instead of caller memory.  It has no counterpart in
+ * the reference.  Limit: the 256-byte aligned hidden activations,
+ * sum over hidden layers of batch * sizes[i+1] * element size, must fit in
+ * SB_STATIC_WORKSPACE_BYTES (32 MiB, held by every GPU that loads the library
+ * until the process exits); larger requests return SB_ERR_TOO_LARGE.  It calls
+ * no cudaMalloc / cudaFree.  The first call on a device looks up the array's
+ * device address and sets kernel attributes; make that call before starting any
+ * stream capture.  All calls share the one array and it keeps the last call's
+ * contents (every byte used is rewritten before it is read, so nothing needs
+ * clearing): two calls that overlap on the GPU -- different streams, or
+ * different host threads -- race on it. */
+#define SB_STATIC_WORKSPACE_BYTES (32u * 1024u * 1024u)
+int sb_mlp_forward_static(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                          const void* w_compute, const float* params, int head, const uint8_t* mask,
+                          float* out, int32_t* actions, void* stream);
+
 /* Backward pass of mean cross-entropy over `1/inv_global_batch` rows on a
  * masked-softmax head, after sb_mlp_forward with SB_EPI_MASKED_SOFTMAX on the
  * same buffers.  No counterpart in the reference (it trains by CEM / CFR,

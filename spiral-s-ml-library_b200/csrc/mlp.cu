@@ -261,6 +261,72 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
   return SB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Forward pass for hosts that cannot allocate device memory.
+//
+// Some callers of this library have no way to obtain the hidden-activation
+// workspace that sb_mlp_forward wants: a per-decision game loop that only
+// holds the reference's three arenas, a plugin running inside someone else's
+// CUDA context with allocation forbidden, or code between cudaStreamBeginCapture
+// and EndCapture, where cudaMalloc is illegal.  For them the hidden activations
+// live in the fixed array below, which is part of the library image: every GPU
+// that loads the library holds these SB_STATIC_WORKSPACE_BYTES until the
+// process exits.
+//
+// In host code the name `g_static_workspace` is only a host-side stand-in for
+// the symbol, not a device address; the real address is looked up once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels get.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_workspace[SB_STATIC_WORKSPACE_BYTES];
+
+namespace {
+unsigned char* g_static_workspace_addr[64] = {nullptr};
+
+// Device address of the static workspace on the current device (looked up on
+// the first call per device, with that device current).
+int static_workspace_address(unsigned char** out) {
+  int dev = 0;
+  SB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_static: device index %d out of range", dev);
+  if (!g_static_workspace_addr[dev]) {
+    void* p = nullptr;
+    SB_CUDA(cudaGetSymbolAddress(&p, g_static_workspace));
+    if (!p) return sb_fail(SB_ERR_CUDA, "sb_mlp_forward_static: cudaGetSymbolAddress returned a null address");
+    g_static_workspace_addr[dev] = reinterpret_cast<unsigned char*>(p);
+  }
+  *out = g_static_workspace_addr[dev];
+  return SB_OK;
+}
+}  // namespace
+
+int sb_mlp_forward_static(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                          const void* w_compute, const float* params, int head, const uint8_t* mask,
+                          float* out, int32_t* actions, void* stream) {
+  int rc = check_layout("sb_mlp_forward_static", n_layers, sizes, batch, in_dtype);
+  if (rc != SB_OK) return rc;
+  // Carve one 256-byte aligned slab per hidden layer out of the fixed array.
+  const int es = sb_dtype_size(in_dtype);
+  void* acts[MLP_MAX_LAYERS];
+  size_t offset = 0;
+  size_t offsets[MLP_MAX_LAYERS];
+  for (int i = 0; i + 1 < n_layers; ++i) {
+    offsets[i] = offset;
+    offset += (size_t)align_up((long long)batch * sizes[i + 1] * es, 256);
+  }
+  if (offset > (size_t)SB_STATIC_WORKSPACE_BYTES)
+    return sb_fail(SB_ERR_TOO_LARGE,
+                   "sb_mlp_forward_static: hidden activations need %zu bytes, the built-in workspace holds %zu; "
+                   "use sb_mlp_forward with caller memory for this batch", offset, (size_t)SB_STATIC_WORKSPACE_BYTES);
+  unsigned char* base = nullptr;
+  rc = static_workspace_address(&base);
+  if (rc != SB_OK) return rc;
+  for (int i = 0; i + 1 < n_layers; ++i) acts[i] = base + offsets[i];
+  // Every slab is completely overwritten by its layer before the next layer
+  // reads it, so nothing left behind by an earlier call needs clearing.
+  return sb_mlp_forward(n_layers, sizes, batch, in_dtype, x, w_compute, params, n_layers > 1 ? acts : nullptr,
+                        nullptr, head, mask, out, actions, stream);
+}
+
 int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int in_dtype, size_t* bytes) {
   if (!bytes) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward_scratch_bytes: null output");
   int rc = check_layout("sb_mlp_backward_scratch_bytes", n_layers, sizes, batch, in_dtype);

@@ -121,6 +121,22 @@ class PolicyMLP:
                   stream_ptr(stream))
         return self.probs
 
+    def forward_no_alloc(self, x, out, mask=None, actions=None, head_flags=None, stream=None):
+        """Forward pass whose hidden activations use the library's built-in 32 MiB workspace.
+
+        For callers that may not allocate device memory (no allocator of their own, a context where
+        allocation is forbidden, inside a stream capture).  `out` (fp32 [batch, actions]) and
+        `actions` (int32 [batch], for argmax heads) are caller buffers.  Raises SpiralError
+        (SB_ERR_TOO_LARGE) when batch x hidden widths does not fit.  Calls share the one workspace:
+        do not overlap two of them on the GPU.
+        """
+        flags = self.head_flags if head_flags is None else head_flags
+        _lib.call("sb_mlp_forward_static", self.n_layers, self._sizes_c, self.batch,
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr,
+                  self.params.ptr if self.with_bias else None, flags, device_ptr(mask), device_ptr(out),
+                  device_ptr(actions) if flags & _lib.EPI_ARGMAX else None, stream_ptr(stream))
+        return out
+
     def backward(self, x, mask, target, global_batch=None, stream=None):
         """grads <- d(mean cross-entropy)/d(params) for this shard (after a masked-softmax forward)."""
         gb = self.batch if global_batch is None else int(global_batch)
