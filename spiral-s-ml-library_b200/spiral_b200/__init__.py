@@ -10,3 +10,5 @@ from .device import (DeviceArray, Event, GemmProfile, launch_count, device_count
 from .matmul import matmul, matmul_plan, matmul_tf32  # noqa: F401
 from . import primitives  # noqa: F401
 from .models import PolicyMLP, param_offsets, to_storage  # noqa: F401
+from . import layers  # noqa: F401
+from .parallel import DataParallel, shard_rows, bucket_ranges  # noqa: F401

@@ -95,7 +95,7 @@ class DeviceArray:
         return self
 
     def fill_zero(self, stream=None):
-        _lib.call("sb_memset", self.ptr, 0, self.nbytes, stream)
+        _lib.call("sb_memset", self.ptr, 0, self.nbytes, stream_ptr(stream))
         return self
 
     # -- readback ----------------------------------------------------------

@@ -1,0 +1,218 @@
+"""Layer-graph builder with the reference's names, run on the fused GEMM path.
+
+Mirrors the dense subset of ml/layers.spi: graph builders ``input``, ``matmul``,
+``relu``, ``softmax``, ``masked_softmax``, ``regret_matching``,
+``masked_regret_matching``, ``argmax``, ``ln_l2`` (:347-420, 467, 482-484), the
+arena planner ``create_model`` (:127-172, 486-490), ``pass_init`` (:307, weights
+N(0, 0.1) as weight_init :460-463), ``key_extract`` (:321-325) and
+``graph_run_host`` (:339-344).
+
+Differences by design: the reference emits one device function per node and a
+global-memory pass for every activation and head; here ``graph_run_host`` fuses
+``matmul -> relu`` and ``matmul -> head`` chains into one GEMM launch each, and
+only nodes that cannot be fused run as stand-alone kernels.  Tensors are 3-D in
+the reference (blocks, rows, features); the leading dimensions are the batch.
+"""
+import numpy as np
+
+from . import _lib
+from . import primitives
+from .device import DeviceArray, stream_ptr
+from .matmul import matmul as _matmul
+
+WEIGHT_ID, WORKSPACE_ID, WEIGHT_ADJOINT_ID = 0, 1, 2     # ml/layers.spi:6-12
+CONSTANT_SEED = 12344321                                 # corecuda/cupy.spi:6
+_ALIGN = 256                                             # bytes; the reference aligns to 16 (partitionm.spi:3-4)
+
+
+class Node:
+    """One graph node; ``dims`` is the shape of its output tensor."""
+
+    def __init__(self, op, src=None, dims=None, **attrs):
+        self.op, self.src, self.dims, self.attrs = op, src, tuple(dims), attrs
+        self.offset = None        # byte offset of the output in the workspace arena
+        self.weight_offset = None
+
+    @property
+    def rows(self):
+        return int(np.prod(self.dims[:-1]))
+
+    @property
+    def cols(self):
+        return int(self.dims[-1])
+
+
+def input(key, dims):
+    """A keyed workspace tensor the caller fills (layers.input, ml/layers.spi:482-484)."""
+    return Node("input", None, dims, key=key)
+
+
+def matmul(in_out, x):
+    """Dense layer y = x W^T with W stored [out, in]; ``in_out`` = (in, out) as in ``matmul (b,a) x``
+    (ml/layers.spi:467: BlockMatmul(x, weight (a,b)))."""
+    fan_in, fan_out = int(in_out[0]), int(in_out[1])
+    if x.cols != fan_in:
+        raise ValueError("matmul: input has %d features, the layer expects %d" % (x.cols, fan_in))
+    return Node("matmul", x, x.dims[:-1] + (fan_out,), fan_in=fan_in, fan_out=fan_out)
+
+
+def relu(x):
+    return Node("relu", x, x.dims)
+
+
+def softmax(x):
+    return Node("softmax", x, x.dims, size=-1)
+
+
+def masked_softmax(size, x):
+    """Legal iff column index < size (ml/layers.spi:408-414)."""
+    return Node("softmax", x, x.dims, size=int(size))
+
+
+def regret_matching(x):
+    return Node("regret_matching", x, x.dims, size=-1)
+
+
+def masked_regret_matching(size, x):
+    return Node("regret_matching", x, x.dims, size=int(size))
+
+
+def ln_l2(x):
+    return Node("ln_l2", x, x.dims)
+
+
+def argmax(x):
+    """Index of the row maximum; the output keeps a trailing dimension of 1 (one int32 per row)."""
+    return Node("argmax", x, x.dims[:-1] + (1,))
+
+
+class Model:
+    """Planned graph + its three arenas (weights, workspace, weight adjoint), ml/layers.spi:486-502."""
+
+    def __init__(self, graph, in_dtype):
+        self.graph, self.in_dtype = graph, in_dtype
+        self.nodes = []
+        n = graph
+        while n is not None:
+            self.nodes.append(n)
+            n = n.src
+        self.nodes.reverse()
+        if self.nodes[0].op != "input":
+            raise ValueError("a graph must start at an input node")
+        sizes = [0, 0, 0]
+        for n in self.nodes:                      # pass_calculate_partitions, ml/layers.spi:127-172
+            if n.op == "matmul":
+                n.weight_offset = sizes[WEIGHT_ID]
+                sizes[WEIGHT_ID] += _round_up(n.attrs["fan_in"] * n.attrs["fan_out"] * 4, _ALIGN)
+            n.offset = sizes[WORKSPACE_ID]
+            sizes[WORKSPACE_ID] += _round_up(n.rows * (n.cols if n.op != "argmax" else 1) * 4, _ALIGN)
+        self.partition_bytes = tuple(sizes)
+        self.arenas = None
+
+    def allocate(self):
+        if self.arenas is None:
+            self.arenas = [DeviceArray.zeros((max(b, 16),), "u8") for b in self.partition_bytes]
+        return self
+
+    def tensor(self, node):
+        """Typed view of a node's output inside the workspace arena."""
+        if node.op == "argmax":
+            return self.arenas[WORKSPACE_ID].view((node.rows,), "i32", node.offset)
+        return self.arenas[WORKSPACE_ID].view((node.rows, node.cols), "f32", node.offset)
+
+    def weight(self, node):
+        return self.arenas[WEIGHT_ID].view((node.attrs["fan_out"], node.attrs["fan_in"]), "f32", node.weight_offset)
+
+
+def _round_up(x, a):
+    return (x + a - 1) // a * a
+
+
+def create_model(graph, in_dtype="tf32", allocate=True):
+    """Plans the arenas of ``graph`` (and allocates them).  ``in_dtype``: 'tf32' (the reference's
+    arithmetic, default) or 'f32' (FFMA)."""
+    if in_dtype not in ("tf32", "f32"):
+        raise ValueError("layer graphs store fp32; in_dtype must be 'tf32' or 'f32'")
+    model = Model(graph, in_dtype)
+    return model.allocate() if allocate else model
+
+
+def model_to_model_ptrs(model):
+    """(weights, workspace, weight_adjoint) device pointers, the kernel arguments of ml/layers.py:4500."""
+    return tuple(a.ptr for a in model.arenas)
+
+
+def pass_init(model, seed=CONSTANT_SEED, std=0.1):
+    """Initialises every weight tensor N(0, std^2) (weight_init, ml/layers.spi:460-463)."""
+    gen = np.random.Generator(np.random.Philox(seed))
+    for n in model.nodes:
+        if n.op == "matmul":
+            w = gen.normal(0.0, std, size=(n.attrs["fan_out"], n.attrs["fan_in"])).astype(np.float32)
+            model.weight(n).upload(w)
+    return model
+
+
+def get_weights(model):
+    return [model.weight(n).numpy() for n in model.nodes if n.op == "matmul"]
+
+
+def key_extract(model, key):
+    """The workspace tensor registered under ``key`` (ml/layers.spi:321-325)."""
+    for n in model.nodes:
+        if n.op == "input" and n.attrs["key"] == key:
+            return model.tensor(n)
+    raise KeyError(key)
+
+
+def graph_run_host(model, stream=None):
+    """Runs the graph (ml/layers.spi:339-344) and returns the output tensor of the last node."""
+    nodes = model.nodes
+    i = 1
+    while i < len(nodes):
+        n = nodes[i]
+        src = model.tensor(n.src)
+        if n.op == "matmul":
+            epilogue, last, j, mask_dev = [], n, i + 1, None
+            if j < len(nodes) and nodes[j].op == "relu":
+                epilogue.append("relu")
+                last, j = nodes[j], j + 1
+            elif model.in_dtype == "tf32":
+                # softmax and regret matching fuse (in that order) when they share one prefix mask
+                k, size, mask_needed = j, None, False
+                while k < len(nodes) and nodes[k].op in ("softmax", "regret_matching"):
+                    want = "masked_softmax" if nodes[k].op == "softmax" else "regret_matching"
+                    if want in epilogue or (want == "masked_softmax" and "regret_matching" in epilogue):
+                        break
+                    if size is not None and nodes[k].attrs["size"] != size:
+                        break
+                    size = nodes[k].attrs["size"]
+                    epilogue.append(want)
+                    last, k = nodes[k], k + 1
+                j = k
+                mask_needed = size is not None and size >= 0
+                if mask_needed:
+                    m = np.zeros((n.rows, n.cols), np.uint8)
+                    m[:, :size] = 1
+                    mask_dev = DeviceArray.from_numpy(m)
+            out = model.tensor(last)
+            _matmul(False, True, 1.0, src, model.weight(n), 0.0, out, in_dtype=model.in_dtype,
+                    epilogue=tuple(epilogue), mask=mask_dev, stream=stream)
+            if mask_dev is not None:
+                _lib.call("sb_stream_sync", stream_ptr(stream))      # the mask buffer is released on return
+            i = j
+            continue
+        out = model.tensor(n)
+        if n.op == "relu":
+            primitives.relu(src, out, stream=stream)
+        elif n.op == "softmax":
+            primitives.softmax(src, out, prefix=n.attrs["size"], stream=stream)
+        elif n.op == "regret_matching":
+            primitives.regret_matching(src, out, prefix=n.attrs["size"], stream=stream)
+        elif n.op == "ln_l2":
+            primitives.ln_l2(src, out, stream=stream)
+        elif n.op == "argmax":
+            primitives.argmax(src, out, stream=stream)
+        else:
+            raise ValueError("unknown node %r" % n.op)
+        i += 1
+    return model.tensor(nodes[-1])

@@ -116,3 +116,33 @@ def test_train_step_updates_master_and_compute_weights(gpu):
 def test_empty_batch_is_a_no_op(gpu):
     net = gpu.PolicyMLP([32, 64, 3], 0, in_dtype="bf16")
     net.forward(gpu.DeviceArray((0, 32), "bf16"))
+
+
+def test_layer_graph_runs_fused_and_matches_oracle(gpu):
+    """The reference's builder names (ml/layers.spi:347-420) on the fused path: a 3-layer net with
+    ReLU and a prefix-masked softmax head, weights N(0, 0.1) from pass_init."""
+    L = gpu.layers
+    g = L.masked_softmax(3, L.matmul((64, 8), L.relu(L.matmul((64, 64), L.relu(L.matmul((32, 64),
+                         L.input("input", (2, 256, 32))))))))
+    model = L.pass_init(L.create_model(g))
+    x = so.round_tf32(so.rng(8).normal(size=(512, 32)).astype(np.float32))
+    L.key_extract(model, "input").upload(x)
+    out = L.graph_run_host(model).numpy()
+    ws = [so.round_tf32(w) for w in L.get_weights(model)]
+    h = x
+    for w in ws[:-1]:
+        h = so.relu(so.matmul(False, True, 1.0, h, w, 0.0, None, in_dtype="tf32"))
+    want = so.masked_softmax(so.matmul(False, True, 1.0, h, ws[-1], 0.0, None, in_dtype="tf32"),
+                             so.prefix_mask((512, 8), 3))
+    assert so.rel_frobenius(out, want) <= TOL
+    assert np.all(out[:, 3:] == 0)
+    # unfused nodes: ln_l2 and argmax after a plain matmul
+    g2 = L.argmax(L.ln_l2(L.matmul((32, 16), L.input("input", (1, 128, 32)))))
+    m2 = L.pass_init(L.create_model(g2))
+    L.key_extract(m2, "input").upload(x[:128])
+    idx = L.graph_run_host(m2).numpy()
+    w2 = so.round_tf32(L.get_weights(m2)[0])
+    ref = so.ln_l2(so.matmul(False, True, 1.0, x[:128], w2, 0.0, None, in_dtype="tf32"))
+    top2 = np.sort(ref, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 1e-4 * np.abs(top2[:, 1])
+    np.testing.assert_array_equal(idx[clear], so.argmax(ref)[clear])
