@@ -81,6 +81,7 @@ int sb_event_create(void** event);
 int sb_event_destroy(void* event);
 int sb_event_record(void* event, void* stream);
 int sb_event_elapsed_ms(void* start, void* stop, float* ms);  /* syncs on stop */
+int sb_stream_wait_event(void* stream, void* event);        /* later work on stream waits for event */
 /* Reads (and optionally clears) the device status word written by bounded
  * waits: status[0] = first wait site that expired (0 = healthy), status[1] =
  * count of expired waits.  Synchronises the device. */

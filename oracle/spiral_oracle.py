@@ -10,9 +10,11 @@ L2 row normalisation, argmax) are pinned against the reference's own golden
 console outputs (tests/golden/primitives_golden.npz, extracted from
 test_text_outputs/primitives/ by tests/golden/make_golden.py).  The GEMM has no
 stored vectors in the reference (its self-test compares against cp.matmul on
-unsaved random inputs, ml/matmul/run.spi:41,54-58): GEMM PARITY IS UNPINNED by
-reference data and rests on the definition C = alpha*op(A)*op(B) + beta*C
-evaluated in float64.  Cross-entropy, dgrad, wgrad and SGD have no reference
+unsaved random inputs, ml/matmul/run.spi:41,54-58); it is pinned instead against
+the reference's own kernel, recompiled for sm_100a by oracle/build_ref.py and run
+on the same inputs (tests/test_gpu_e_reference_kernel.py), at the one shape that
+kernel is generated for.  Elsewhere the oracle is the definition
+C = alpha*op(A)*op(B) + beta*C evaluated in float64.  Cross-entropy, dgrad, wgrad and SGD have no reference
 implementation at all; they are defined here.
 """
 import numpy as np

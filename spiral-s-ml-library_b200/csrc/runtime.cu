@@ -186,6 +186,12 @@ int sb_event_record(void* event, void* stream) {
   return SB_OK;
 }
 
+int sb_stream_wait_event(void* stream, void* event) {
+  if (!event) return sb_fail(SB_ERR_BAD_ARG, "sb_stream_wait_event: null event");
+  SB_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+  return SB_OK;
+}
+
 int sb_event_elapsed_ms(void* start, void* stop, float* ms) {
   if (!start || !stop || !ms) return sb_fail(SB_ERR_BAD_ARG, "sb_event_elapsed_ms: null argument");
   SB_CUDA(cudaEventSynchronize((cudaEvent_t)stop));

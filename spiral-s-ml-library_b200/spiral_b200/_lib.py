@@ -63,6 +63,7 @@ SIGNATURES = {
     "sb_event_create": (_I, [_PP]),
     "sb_event_destroy": (_I, [_P]),
     "sb_event_record": (_I, [_P, _P]),
+    "sb_stream_wait_event": (_I, [_P, _P]),
     "sb_event_elapsed_ms": (_I, [_P, _P, POINTER(c_float)]),
     "sb_device_status": (_I, [_IP, _I]),
     "sb_launch_count": (ctypes.c_ulonglong, []),

@@ -172,6 +172,34 @@ def stream_ptr(stream):
     raise TypeError("cannot take a stream handle from %r" % type(stream))
 
 
+class Stream:
+    """A non-blocking CUDA stream (does not synchronise with the legacy default stream)."""
+
+    def __init__(self):
+        p = ctypes.c_void_p()
+        _lib.call("sb_stream_create", ctypes.byref(p))
+        self.ptr = p.value
+
+    def wait_event(self, event):
+        _lib.call("sb_stream_wait_event", self.ptr, event.ptr)
+
+    def synchronize(self):
+        _lib.call("sb_stream_sync", self.ptr)
+
+    def __del__(self):
+        try:
+            if self.ptr:
+                _lib.load().sb_stream_destroy(self.ptr)
+                self.ptr = None
+        except Exception:
+            pass
+
+
+def wait_event(stream, event):
+    """Work submitted to `stream` (None = default stream) after this call waits for `event`."""
+    _lib.call("sb_stream_wait_event", stream_ptr(stream), event.ptr)
+
+
 class Event:
     """CUDA event for device-side timing on the launching stream."""
 
