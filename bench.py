@@ -321,12 +321,16 @@ def run_ours(args, rank, world, local_rank):
     loss_pin = PinnedBuffer(np.zeros(1, np.float32))
     sb.synchronize()
 
+    # narrow nets run inference as one persistent fused kernel
+    fused = (not training) and max(sizes[1:-1]) <= 256 and in_dtype in ("f16", "bf16") and not args.layerwise
     dp = sb.DataParallel(net, gbatch, all_reduce=(lambda g: dist.all_reduce(g)) if dist is not None else None,
                          world_size=world, rank=rank)
 
     def step():
         if training:
             dp.train_step(x_dev, mask_dev, target_dev, LR)
+        elif fused:
+            net.forward_fused(x_dev, mask_dev)
         else:
             dp.infer(x_dev, mask_dev)
 
@@ -362,6 +366,8 @@ def run_ours(args, rank, world, local_rank):
         xs, ms, ts = sets[cur]
         if training:
             dp.train_step(xs, ms, ts, LR)
+        elif fused:
+            net.forward_fused(xs, ms)
         else:
             dp.infer(xs, ms)
         free[cur].record()
@@ -505,6 +511,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the global batch (tests only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--layerwise", action="store_true", help="narrow-net inference through one GEMM per layer")
     ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
                     help="run a few launches of one GEMM shape (for ncu) and exit")
     ap.add_argument("--iters", type=int, default=4)

@@ -172,6 +172,16 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
                    void* const* relu_bits, int head, const uint8_t* mask, float* out, int32_t* actions,
                    void* stream);
 
+/* The same forward pass as ONE persistent kernel for narrow nets (the Leduc-sized
+ * policy MLP): hidden activations stay in shared memory / TMEM, so no activations
+ * buffer is needed.  Replaces the same reference chain (ml/layers.py:4500-4546).
+ * Limits: in_dtype SB_F16 or SB_BF16; sizes[0] in 8..256 and a multiple of 8;
+ * hidden widths multiples of 64 up to 256; sizes[n_layers] <= 32; n_layers <= 8;
+ * otherwise SB_ERR_UNSUPPORTED (use sb_mlp_forward). */
+int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                         const void* w_compute, const float* params, int head, const uint8_t* mask,
+                         float* out, int32_t* actions, void* stream);
+
 /* The same forward pass for callers that cannot allocate device memory (a host
  * that owns no allocator, a plugin in a context where allocation is forbidden,
  * code inside a stream capture): the hidden activations live in a fixed array

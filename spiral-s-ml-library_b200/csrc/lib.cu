@@ -7,3 +7,4 @@
 #include "gemm_umma.cu"
 #include "api.cu"
 #include "mlp.cu"
+#include "mlp_fused.cu"

@@ -121,6 +121,17 @@ class PolicyMLP:
                   stream_ptr(stream))
         return self.probs
 
+    def forward_fused(self, x, mask=None, head_flags=None, stream=None):
+        """Forward pass as one persistent kernel (narrow nets: 16-bit class, hidden widths multiples of
+        64 up to 256, at most 32 outputs); hidden activations never reach global memory.  Raises
+        SpiralError (SB_ERR_UNSUPPORTED) for shapes outside those limits."""
+        flags = self.head_flags if head_flags is None else head_flags
+        _lib.call("sb_mlp_forward_fused", self.n_layers, self._sizes_c, self.batch,
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr,
+                  self.params.ptr if self.with_bias else None, flags, device_ptr(mask), self.probs.ptr,
+                  device_ptr(self.actions) if flags & _lib.EPI_ARGMAX else None, stream_ptr(stream))
+        return self.probs
+
     def forward_no_alloc(self, x, out, mask=None, actions=None, head_flags=None, stream=None):
         """Forward pass whose hidden activations use the library's built-in 32 MiB workspace.
 

@@ -146,3 +146,44 @@ def test_layer_graph_runs_fused_and_matches_oracle(gpu):
     top2 = np.sort(ref, axis=1)[:, -2:]
     clear = (top2[:, 1] - top2[:, 0]) > 1e-4 * np.abs(top2[:, 1])
     np.testing.assert_array_equal(idx[clear], so.argmax(ref)[clear])
+
+
+@pytest.mark.parametrize("in_dtype,batch", [("f16", 1000), ("bf16", 16384), ("f16", 25600)])
+def test_fused_persistent_forward_matches_layerwise_and_oracle(gpu, in_dtype, batch):
+    """One persistent kernel for the Leduc-sized net: ragged last tile (1000), the benchmark batch
+    (16384 = 128 tiles) and more tiles than SMs (25600 = 200 tiles)."""
+    sizes = [32, 256, 256, 256, 3]
+    net, ws, bs = build(gpu, sizes, batch, in_dtype, 3, head=("masked_softmax", "regret_matching", "argmax"),
+                        bias_scale=0.1)
+    x, mask = so.leduc_inputs(9, batch)
+    dx, dm = gpu.to_storage(x, in_dtype), gpu.DeviceArray.from_numpy(mask)
+    layerwise = net.forward(dx, dm).numpy().copy()
+    actions_layerwise = net.actions.numpy().copy()
+    net.probs.fill_zero()
+    net.actions.fill_zero()
+    fused = net.forward_fused(dx, dm).numpy()
+    assert so.rel_frobenius(fused, layerwise) <= 1e-5        # same rounding points, same arithmetic
+    want = so.mlp_forward(x, ws, bs, mask, in_dtype=in_dtype, act_dtype=in_dtype,
+                          head=("masked_softmax", "regret_matching"))
+    assert so.rel_frobenius(fused, want) <= TOL
+    actions = net.actions.numpy()
+    np.testing.assert_array_equal(actions, np.argmax(fused, axis=1))
+    agree = actions == actions_layerwise
+    assert agree.mean() > 0.999
+
+
+def test_fused_forward_other_shapes_and_limits(gpu):
+    from spiral_b200 import SpiralError
+    sizes, batch = [64, 128, 64, 10], 777
+    net, ws, bs = build(gpu, sizes, batch, "bf16", 12)
+    g = so.rng(12)
+    x = g.random((batch, 64), dtype=np.float32)
+    mask = (g.random((batch, 10)) < 0.6).astype(np.uint8)
+    mask[:, 0] = 1
+    got = net.forward_fused(gpu.to_storage(x, "bf16"), gpu.DeviceArray.from_numpy(mask)).numpy()
+    want = so.mlp_forward(x, ws, bs, mask, in_dtype="bf16", act_dtype="bf16")
+    assert so.rel_frobenius(got, want) <= TOL
+    wide = gpu.PolicyMLP([512, 1024, 10], 128, in_dtype="bf16")
+    with pytest.raises(SpiralError) as err:
+        wide.forward_fused(gpu.DeviceArray((128, 512), "bf16"))
+    assert err.value.code == -3
