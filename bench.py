@@ -433,6 +433,15 @@ def run_ours(args, rank, world, local_rank):
              "gemm_launches_per_step": prof.launches // 2,
              "peak_burst_tflops": peaks.get("bf16_tflops"), "peaks_source": peaks["source"],
              "model_tflops": round(net.flops_per_sample(training) * value / 1e12, 1)}
+    if not training:
+        # North-star view of the small-MLP case: algorithmic bytes of one forward pass (inputs, mask,
+        # probabilities, actions, weights once) over the step time, against the measured HBM copy rate.
+        n_params = sb.param_offsets(sizes)[-1]
+        alg_bytes = (x_pin.nbytes + mask_pin.nbytes + batch * sizes[-1] * 4 + batch * 4) * world + n_params * 2
+        hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+        gbs = alg_bytes / (ms_step * 1e-3) / 1e9
+        extra["hbm_view"] = {"algorithmic_bytes": int(alg_bytes), "achieved_gbs": round(gbs, 1), "peak_gbs": hbm_peak,
+                             "frac": round(gbs / hbm_peak / world, 4)}
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         rows = 8192 if sizes[0] == 512 else 65536
@@ -452,7 +461,8 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": workload, "layers": sizes, "global_batch": gbatch, "batch_per_gpu": batch,
                    "parallelism": "dp%d" % world, "lr": LR,
                    "l2": "inputs (%.0f MB per step) larger than the 126 MB L2" % (h2d / 1e6)},
-        "roofline": {"bound": "tensor", "kernel": "umma_gemm_kernel", "achieved": round(achieved, 1), "peak": peak,
+        "roofline": {"bound": "tensor", "kernel": "mlp_fused_kernel" if fused else "umma_gemm_kernel",
+                     "achieved": round(achieved, 1), "peak": peak,
                      "unit": "TFLOP/s", "frac": round(achieved / peak, 4) if peak else None, "traffic": None,
                      "peak_kind": "%s, sustained cuBLAS bf16" % peaks["source"]},
         "cpu_baseline": cpu,

@@ -61,6 +61,9 @@ struct UmmaGemmParams {
   int mn_box_elems;        // MN extent of one MN-major box (128 bytes)
   uint32_t mn_box_bytes;   // bytes of one MN-major box = block_k * 128
   uint32_t a_kstep, b_kstep;  // descriptor start-address step per MMA, in 16-byte units
+  int subs;                   // 128-byte K sub-blocks per stage (1 or 2): 4 * subs MMAs per barrier round
+  uint32_t a_sub_step, b_sub_step;  // descriptor step between the two sub-blocks, in 16-byte units
+  uint32_t a_sub_bytes, b_sub_bytes;  // bytes of one K-major sub-block (rows * 128)
   uint32_t a_sbo, b_sbo;      // stride byte offset of the smem descriptors
   uint32_t a_layout, b_layout;  // descriptor layout type (2 = SW128, 1 = SW128 with 32-byte chunks)
   float alpha, beta;
@@ -579,6 +582,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0;
       const int a_boxes = p.a_boxes, b_boxes = p.b_boxes, mn_box_elems = p.mn_box_elems, block_k = p.block_k;
       const uint32_t mn_box_bytes = p.mn_box_bytes, a_stage_bytes = p.a_stage_bytes;
+      const int subs = p.subs;
+      const uint32_t a_sub_bytes = p.a_sub_bytes, b_sub_bytes = p.b_sub_bytes;
       const int stages = p.stages;
       uint32_t a_dst = stage_base;
       for (int work = worker; ok && work < p.num_work; work += num_workers) {
@@ -600,8 +605,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t full = full0 + 8u * (uint32_t)stage;
           const uint32_t b_dst = a_dst + a_stage_bytes;
           if (!a_mn) {
-            if (PAIR) tma_load_2d_pair(a_dst, &tmap_a, k0, m0, full);
-            else tma_load_2d(a_dst, &tmap_a, k0, m0, full);
+            for (int s = 0; s < subs; ++s) {
+              if (PAIR) tma_load_2d_pair(a_dst + (uint32_t)s * a_sub_bytes, &tmap_a, k0 + s * mn_box_elems, m0, full);
+              else tma_load_2d(a_dst + (uint32_t)s * a_sub_bytes, &tmap_a, k0 + s * mn_box_elems, m0, full);
+            }
           } else {
             for (int i = 0; i < a_boxes; ++i) {
               if (PAIR) tma_load_2d_pair(a_dst + (uint32_t)i * mn_box_bytes, &tmap_a, m0 + i * mn_box_elems, k0, full);
@@ -609,8 +616,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
           if (!b_mn) {
-            if (PAIR) tma_load_2d_pair(b_dst, &tmap_b, k0, n0, full);
-            else tma_load_2d(b_dst, &tmap_b, k0, n0, full);
+            for (int s = 0; s < subs; ++s) {
+              if (PAIR) tma_load_2d_pair(b_dst + (uint32_t)s * b_sub_bytes, &tmap_b, k0 + s * mn_box_elems, n0, full);
+              else tma_load_2d(b_dst + (uint32_t)s * b_sub_bytes, &tmap_b, k0 + s * mn_box_elems, n0, full);
+            }
           } else {
             for (int i = 0; i < b_boxes; ++i) {
               if (PAIR) tma_load_2d_pair(b_dst + (uint32_t)i * mn_box_bytes, &tmap_b, n0 + i * mn_box_elems, k0, full);
@@ -646,6 +655,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0;
       const uint32_t stage_step = stage_bytes >> 4;
       const uint32_t a_kstep = p.a_kstep, b_kstep = p.b_kstep, idesc = p.idesc;
+      const uint32_t a_sub_step = p.a_sub_step, b_sub_step = p.b_sub_step;
+      const bool two_subs = p.subs == 2;
       const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
       const int stages = p.stages;
       uint32_t a_lo = a_lo0, b_lo = b_lo0;
@@ -670,6 +681,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           umma_issue<PAIR, TF32>(d_tmem, a_lo + a_kstep, a_hi, b_lo + b_kstep, b_hi, idesc, 1u);
           umma_issue<PAIR, TF32>(d_tmem, a_lo + 2u * a_kstep, a_hi, b_lo + 2u * b_kstep, b_hi, idesc, 1u);
           umma_issue<PAIR, TF32>(d_tmem, a_lo + 3u * a_kstep, a_hi, b_lo + 3u * b_kstep, b_hi, idesc, 1u);
+          if (two_subs) {
+            const uint32_t a2 = a_lo + a_sub_step, b2 = b_lo + b_sub_step;
+            umma_issue<PAIR, TF32>(d_tmem, a2, a_hi, b2, b_hi, idesc, 1u);
+            umma_issue<PAIR, TF32>(d_tmem, a2 + a_kstep, a_hi, b2 + b_kstep, b_hi, idesc, 1u);
+            umma_issue<PAIR, TF32>(d_tmem, a2 + 2u * a_kstep, a_hi, b2 + 2u * b_kstep, b_hi, idesc, 1u);
+            umma_issue<PAIR, TF32>(d_tmem, a2 + 3u * a_kstep, a_hi, b2 + 3u * b_kstep, b_hi, idesc, 1u);
+          }
           accumulate = 1u;
           if (PAIR) tc_commit_pair(empty0 + 8u * (uint32_t)stage, (uint16_t)3);
           else tc_commit(empty0 + 8u * (uint32_t)stage);
@@ -862,10 +880,7 @@ int cached_sm_count() {
 // tile at least 64 columns wide; row heads stay on single CTAs).
 void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair, bool chunks32 = false) {
   const int es = sb_dtype_size(in_dtype);
-  p.block_k = 128 / es;
-  p.k_blocks = (p.K + p.block_k - 1) / p.block_k;
   p.mn_box_elems = 128 / es;
-  p.mn_box_bytes = (uint32_t)p.block_k * 128u;
   p.pair = (allow_pair && p.M > UG_BLOCK_M && p.N >= 64 && sms >= 2) ? 1 : 0;
   const int tile_m = p.pair ? 2 * UG_BLOCK_M : UG_BLOCK_M;
   const int workers = p.pair ? sms / 2 : sms;
@@ -904,13 +919,27 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair, bool c
   p.tmem_cols = next_pow2(2 * p.acc_stride);
   // Per CTA: 128 rows of A and all (single) or half (pair) of the B columns.
   const int b_cols = p.pair ? p.block_n / 2 : p.block_n;
-  p.a_stage_bytes = UG_BLOCK_M * 128u;
-  p.b_stage_bytes = (uint32_t)b_cols * 128u;
+  // A stage holds one or two 128-byte sub-blocks of K.  Two halve the barrier
+  // rounds per flop (the issue thread's fixed cost per round is what keeps the
+  // tensor pipe from running back to back); they are used when at least three
+  // such stages still fit and K is long enough to fill them.
+  const int sub_bytes = (UG_BLOCK_M + b_cols) * 128;
+  const int budget = UG_SMEM_LIMIT - 2048 - UG_EPI_STAGING;
+  const int sub_k = 128 / es;
+  p.subs = (budget / (2 * sub_bytes) >= 3 && p.K >= 6 * sub_k) ? 2 : 1;
+  p.block_k = p.subs * sub_k;
+  p.k_blocks = (p.K + p.block_k - 1) / p.block_k;
+  p.kb_per_split = p.k_blocks;
+  p.mn_box_bytes = (uint32_t)p.block_k * 128u;
+  p.a_sub_bytes = UG_BLOCK_M * 128u;
+  p.b_sub_bytes = (uint32_t)b_cols * 128u;
+  p.a_stage_bytes = (uint32_t)p.subs * p.a_sub_bytes;
+  p.b_stage_bytes = (uint32_t)p.subs * p.b_sub_bytes;
   // Every stage stays 1024-byte aligned: b_cols is a multiple of 16.
   p.a_boxes = p.a_mn ? UG_BLOCK_M / p.mn_box_elems : 1;
   p.b_boxes = p.b_mn ? b_cols / p.mn_box_elems : 1;
   const int stage_bytes = (int)(p.a_stage_bytes + p.b_stage_bytes);
-  int stages = (UG_SMEM_LIMIT - 2048 - UG_EPI_STAGING) / stage_bytes;
+  int stages = budget / stage_bytes;
   if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
   if (stages > p.k_blocks && p.k_blocks >= 2) stages = max(2, p.k_blocks);
   if (stages < 2) stages = 2;
@@ -921,6 +950,10 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair, bool c
   const int umma_k = 32 / es;
   p.a_kstep = p.a_mn ? (uint32_t)((umma_k / 8) * 1024 / 16) : 2u;
   p.b_kstep = p.b_mn ? (uint32_t)((umma_k / 8) * 1024 / 16) : 2u;
+  // Second sub-block: MN-major tiles simply continue along K (4 more k-steps);
+  // K-major tiles start a new [rows x 128 B] slab.
+  p.a_sub_step = p.a_mn ? 4u * p.a_kstep : p.a_sub_bytes / 16u;
+  p.b_sub_step = p.b_mn ? 4u * p.b_kstep : p.b_sub_bytes / 16u;
   p.kind_tf32 = (in_dtype == SB_TF32) ? 1 : 0;
   const bool a32 = p.a_mn && es == 4, b32 = p.b_mn && es == 4;
   p.a_layout = a32 ? 1u : 2u;
@@ -982,10 +1015,10 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
 
   CUtensorMap ta, tb;
   int rc;
-  if (!p.a_mn) rc = make_tmap_2d(&ta, A, in_dtype, M, K, UG_BLOCK_M, p.block_k, SWZ_128);
+  if (!p.a_mn) rc = make_tmap_2d(&ta, A, in_dtype, M, K, UG_BLOCK_M, p.mn_box_elems, SWZ_128);
   else rc = make_tmap_2d(&ta, A, in_dtype, K, M, p.block_k, p.mn_box_elems, p.a_layout == 1u ? SWZ_128_CHUNK32 : SWZ_128);
   if (rc != SB_OK) return rc;
-  if (!p.b_mn) rc = make_tmap_2d(&tb, B, in_dtype, N, K, p.pair ? p.block_n / 2 : p.block_n, p.block_k, SWZ_128);
+  if (!p.b_mn) rc = make_tmap_2d(&tb, B, in_dtype, N, K, p.pair ? p.block_n / 2 : p.block_n, p.mn_box_elems, SWZ_128);
   else rc = make_tmap_2d(&tb, B, in_dtype, K, N, p.block_k, p.mn_box_elems, p.b_layout == 1u ? SWZ_128_CHUNK32 : SWZ_128);
   if (rc != SB_OK) return rc;
 

@@ -424,7 +424,11 @@ extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, i
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  double flops = 0.0;
+  for (int l = 0; l < n_layers; ++l) flops += 2.0 * batch * (double)sizes[l] * sizes[l + 1];
+  sb_prof_before((cudaStream_t)stream);
   mlp_fused_kernel<<<grid, FM_THREADS, smem, (cudaStream_t)stream>>>(maps, p);
+  sb_prof_after((cudaStream_t)stream, flops);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
