@@ -77,6 +77,7 @@ struct UmmaGemmParams {
   void* aux_out;
   int pair;            // 1: CTA pairs (cta_group::2), 256-row tiles
   int coalesced;       // 1: 32-column chunks are transposed through shared memory for row-contiguous stores
+  int tma_store;       // 1: and the finished boxes are written by TMA stores
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
 };
 
@@ -192,6 +193,8 @@ struct EpiArgs {
   int gate_ld;              // words per row of the sign-bit matrices = N / 32
   float alpha, beta;
   bool has_bias, relu, relu_grad, coalesced;
+  const CUtensorMap* tma_c; // non-null: finished boxes leave through TMA stores (32 x 32 element boxes over C)
+  int tma_row0;             // row offset of this split's partial inside the tensor map
 };
 
 // Finishes one 32-column chunk.  `bias_lane` = bias[col0 + lane]; `gate` = this
@@ -249,6 +252,11 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
   const bool tile_gate = GENERAL && e.relu_grad;
   if (tile_gate)
     load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(e.aux), e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
+  if (!GENERAL && e.tma_c) {
+    // The store that last read this box must have finished reading it.
+    if (lane == 0) bulk_wait_group_read<0>();
+    __syncwarp();
+  }
 #pragma unroll
   for (int q = 0; q < PIECES; ++q) {
     const uint32_t mine = sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
@@ -265,6 +273,17 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
       outv[t] = float_to<OutT>(x);
     }
     st_shared_v4(mine, *reinterpret_cast<const uint4*>(outv));   // overwrites only what this lane just read
+  }
+  if (!GENERAL && e.tma_c) {
+    // The box already has the layout of a swizzled TMA box: one asynchronous bulk store writes
+    // it (clipped at the matrix edges) without occupying the load/store pipe.
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(e.tma_c, sbuf, col0, e.tma_row0 + (int)row0_warp);
+      bulk_commit_group();
+    }
+    return signs;
   }
   __syncwarp();
   // Not fully unrolled: eight independent 64-bit store addresses at once would
@@ -513,6 +532,7 @@ template <bool PAIR, bool TF32>
 __global__ void __launch_bounds__(UG_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c,
                  const __grid_constant__ UmmaGemmParams p) {
   extern __shared__ uint8_t ug_smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[UG_MAX_STAGES];
@@ -725,6 +745,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     e.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
     e.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
     e.gate_ld = p.N >> 5;
+    e.tma_c = p.tma_store ? &tmap_c : nullptr;
+    e.tma_row0 = 0;
     const bool general = p.beta != 0.0f || e.relu_grad;
     for (int work = worker; work < p.num_work; work += num_workers) {
       const int split = work / p.num_tiles;
@@ -746,6 +768,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       } else {
         const int n0 = n_blk * p.block_n;
+        e.tma_row0 = split * p.M;
         if (p.out_dtype == SB_F32 || p.out_dtype == SB_TF32) e.c = reinterpret_cast<float*>(p.C) + c_off;
         else e.c = reinterpret_cast<uint16_t*>(p.C) + c_off;
         bool ok;
@@ -777,9 +800,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  // Teardown.  After an expired wait, give copies and MMAs in flight time to
+  // Teardown.  Bulk stores of the epilogue must have completed; after an expired wait, give copies and MMAs in flight time to
   // land before shared and tensor memory are released.  In a pair neither CTA
   // may leave while its peer can still touch its shared memory or barriers.
+  if (warp >= 2 && lane == 0) bulk_wait_group<0>();
   __syncwarp();
   tc_fence_before_sync();
   if (PAIR) cluster_sync_all(); else __syncthreads();
@@ -1040,6 +1064,17 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
                  (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
                  (!(epi & SB_EPI_RELU_GRAD) || (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0)) ? 1 : 0;
 
+  // TMA stores of the finished boxes: no second tile is read (beta, activation gate), and with
+  // split-K -- the partials form one [splits * M, N] tensor -- no 32-row box may straddle two partials.
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  p.tma_store = 0;
+  if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || M % 32 == 0)) {
+    const int cdt = es_out == 4 ? SB_F32 : out_dtype;
+    rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, 32, es_out == 4 ? SWZ_128 : SWZ_64);
+    if (rc != SB_OK) return rc;
+    p.tma_store = 1;
+  }
   const size_t smem = umma_dyn_smem(p);
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -1054,8 +1089,8 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   sb_prof_before(stream);
   if (!p.pair) {
     const int grid = min(p.num_work, cached_sm_count());
-    if (p.kind_tf32) umma_gemm_kernel<false, true><<<grid, UG_THREADS, smem, stream>>>(ta, tb, p);
-    else umma_gemm_kernel<false, false><<<grid, UG_THREADS, smem, stream>>>(ta, tb, p);
+    if (p.kind_tf32) umma_gemm_kernel<false, true><<<grid, UG_THREADS, smem, stream>>>(ta, tb, tc, p);
+    else umma_gemm_kernel<false, false><<<grid, UG_THREADS, smem, stream>>>(ta, tb, tc, p);
   } else {
     // One cluster of two CTAs per worker; the two CTAs of a cluster share a TPC.
     const int workers = min(p.num_work, cached_sm_count() / 2);
@@ -1072,8 +1107,8 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (p.kind_tf32) SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, true>, ta, tb, p));
-    else SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, false>, ta, tb, p));
+    if (p.kind_tf32) SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, true>, ta, tb, tc, p));
+    else SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, false>, ta, tb, tc, p));
   }
   sb_prof_after(stream, 2.0 * M * N * K);
   SB_COUNT_LAUNCH();
