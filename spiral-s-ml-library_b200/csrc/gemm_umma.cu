@@ -253,8 +253,11 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
   if (tile_gate)
     load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(e.aux), e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
   if (!GENERAL && e.tma_c) {
-    // The store that last read this box must have finished reading it.
-    if (lane == 0) bulk_wait_group_read<0>();
+    // The store that last read this box must have finished reading it.  A 16-bit box is 2 KB, so
+    // the warp's 4 KB slot holds two that alternate and only the store before last is awaited.
+    if (lane == 0) {
+      if (sizeof(OutT) == 2) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+    }
     __syncwarp();
   }
 #pragma unroll
@@ -387,10 +390,13 @@ __device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_
       if (e.gate_in && row_ok && col0 < e.N) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
     }
   };
+  uint32_t box_sel = 0u;
   auto finish = [&](float* v, int c, float bias_lane, uint32_t gate) {
     const int col0 = n0 + c * 32;
     if (rows_live && col0 < e.N) {
-      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, GENERAL>(e, v, bias_lane, gate, row0_warp, col0, sbuf, bias_smem, lane);
+      const uint32_t box = sbuf + ((!GENERAL && sizeof(OutT) == 2 && e.tma_c) ? box_sel : 0u);
+      box_sel ^= 2048u;
+      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, GENERAL>(e, v, bias_lane, gate, row0_warp, col0, box, bias_smem, lane);
       if (e.gate_out && row_ok) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
     }
   };
