@@ -486,6 +486,8 @@ PROFILE_CASES = {
     "holdem_layer_fwd": (False, True, 65536, 1024, 1024, "bf16", "bf16", ("bias", "relu")),
     "holdem_layer_dgrad": (False, False, 65536, 1024, 1024, "bf16", "bf16", ("relu_grad",)),
     "holdem_layer_wgrad": (True, False, 1024, 1024, 65536, "bf16", "f32", ()),
+    "holdem_layer_dgrad_bits": (False, False, 65536, 1024, 1024, "bf16", "bf16", ("relu_grad_mask",)),
+    "holdem_head_dgrad_bits": (False, False, 65536, 1024, 16, "bf16", "bf16", ("relu_grad_mask",)),
 }
 
 
@@ -500,6 +502,8 @@ def run_profile_case(name, iters):
     c = sb.DeviceArray((m, n), odt)
     bias = sb.DeviceArray.from_numpy(rng.standard_normal(n, dtype=np.float32)) if "bias" in epi else None
     aux = sb.DeviceArray.from_numpy(rng.standard_normal((m, n), dtype=np.float32), odt) if "relu_grad" in epi else None
+    if "relu_grad_mask" in epi:
+        aux = sb.DeviceArray.from_numpy(rng.integers(-2**31, 2**31 - 1, size=(m, n // 32), dtype=np.int32))
     sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt, epilogue=epi, bias=bias, aux_in=aux)   # first-launch set-up
     sb.synchronize()
     e0 = sb.Event().record()

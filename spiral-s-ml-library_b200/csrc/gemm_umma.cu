@@ -178,55 +178,74 @@ __device__ __forceinline__ void load_chunk_to_box(const OutT* base, long long ld
   __syncwarp();
 }
 
-// Epilogue arguments held in registers.  The out-of-line epilogue takes them by
-// value: fields read through a reference to the kernel's parameter block would be
-// re-read after every shared-memory asm statement, and with the whole L1 carved
-// out as shared memory each such read costs an L2 round trip.
-struct EpiArgs {
-  void* c;                  // output, already offset to this split's partial
+// Per-launch epilogue constants.  They live in shared memory, written once by
+// thread 0: the out-of-line epilogue reads a field where it needs it (a shared
+// memory load) instead of carrying some twenty-five values in registers through
+// code that is already at the register budget of a 10-warp CTA, and instead of
+// reading the kernel's parameter block through a pointer (with the L1 carved out
+// as shared memory each such read would be an L2 round trip).
+struct EpiShared {
+  void* c;                  // output matrix (split partials follow each other)
   const void* aux;          // activation tile for the ReLU-gradient gate (SB_EPI_RELU_GRAD)
   const float* bias;
   const uint32_t* gate_in;  // ReLU sign bits, one word per row and 32 columns (SB_EPI_RELU_GRAD_MASK)
   uint32_t* gate_out;       // where the forward pass records them (SB_EPI_RELU_MASK_OUT)
+  const CUtensorMap* tma_c; // non-null: finished boxes leave through TMA stores (32 x 32 element boxes over C)
   long long ldc;
+  long long split_stride;
   int M, N;
   int gate_ld;              // words per row of the sign-bit matrices = N / 32
+  int block_n;
   float alpha, beta;
-  bool has_bias, relu, relu_grad, coalesced;
-  const CUtensorMap* tma_c; // non-null: finished boxes leave through TMA stores (32 x 32 element boxes over C)
-  int tma_row0;             // row offset of this split's partial inside the tensor map
+  int has_bias, relu, relu_grad, coalesced;
+  uint32_t box_base;        // shared-memory address of the first epilogue warp's 4 KB box
 };
+__shared__ EpiShared g_epi;
+__shared__ int g_abort_flag;
+__shared__ __align__(16) float g_bias_spread[8][32];
 
 // Finishes one 32-column chunk.  `bias_lane` = bias[col0 + lane]; `gate` = this
 // row's 32 ReLU sign bits of the chunk (when gating by bits).  Returns the sign
 // bits of the values this row produced (bit j = value j > 0 before the ReLU).
-// GENERAL = false leaves out the two rarely used features that read a second
-// tile (beta != 0 and the activation-tile gate), which keeps the common variants
-// inside the register budget of a 10-warp CTA.
-template <typename OutT, bool ROUND_TF32, bool GENERAL>
-__device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, float bias_lane, uint32_t gate,
-                                                    long long row0_warp, int col0, uint32_t sbuf,
+// MODE selects how much is decided at compile time, because every run-time flag
+// tested inside the unrolled per-element code costs instructions and registers
+// in a loop that is issue-bound:
+//   MODE >= 0 : alpha = 1, beta = 0 and exactly the features in the bit mask
+//               (1 bias, 2 ReLU, 4 record sign bits, 8 gate by sign bits);
+//   MODE = -1 : run-time flags, no second tile read;
+//   MODE = -2 : run-time flags plus the two features that read a second tile
+//               through the box (beta != 0, gate by the activation tile).
+template <typename OutT, bool ROUND_TF32, int MODE>
+__device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, uint32_t gate, int split,
+                                                    int row0_warp, int col0, uint32_t sbuf,
                                                     uint32_t bias_smem, int lane) {
   constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
   constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
   constexpr int ROWS_PER_INST = 32 / PIECES;
-  OutT* cbase = reinterpret_cast<OutT*>(e.c);
-  if (GENERAL && e.beta != 0.0f) {
+  constexpr bool GENERAL = MODE == -2;
+  const bool has_bias = MODE >= 0 ? (MODE & 1) != 0 : g_epi.has_bias != 0;
+  const bool relu = MODE >= 0 ? (MODE & 2) != 0 : g_epi.relu != 0;
+  const bool gate_out = MODE >= 0 ? (MODE & 4) != 0 : g_epi.gate_out != nullptr;
+  const bool gate_in = MODE >= 0 ? (MODE & 8) != 0 : g_epi.gate_in != nullptr;
+  if (GENERAL && g_epi.beta != 0.0f) {
     // v <- alpha * acc + beta * C_old, with the old tile read through the box.
-    load_chunk_to_box<OutT>(cbase, e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
+    OutT* cbase = reinterpret_cast<OutT*>(g_epi.c) + (long long)split * g_epi.split_stride;
+    load_chunk_to_box<OutT>(cbase, g_epi.ldc, row0_warp, g_epi.M, col0, g_epi.N, sbuf, lane);
+    const float alpha = g_epi.alpha, beta = g_epi.beta;
 #pragma unroll
     for (int q = 0; q < PIECES; ++q) {
       const uint4 raw = ld_shared_v4(sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q));
       const OutT* o = reinterpret_cast<const OutT*>(&raw);
 #pragma unroll
-      for (int t = 0; t < VEC; ++t) v[q * VEC + t] = e.alpha * v[q * VEC + t] + e.beta * load_as_float<OutT>(o + t);
+      for (int t = 0; t < VEC; ++t) v[q * VEC + t] = alpha * v[q * VEC + t] + beta * load_as_float<OutT>(o + t);
     }
     __syncwarp();
-  } else if (e.alpha != 1.0f) {
+  } else if (MODE < 0 && g_epi.alpha != 1.0f) {
+    const float alpha = g_epi.alpha;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+    for (int j = 0; j < 32; ++j) v[j] *= alpha;
   }
-  if (e.has_bias) {
+  if (has_bias) {
     // Lane j holds bias[col0 + j]; every lane needs all 32: spread them through
     // 128 bytes of shared memory and read them back as broadcasts.
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(bias_smem + 4u * (uint32_t)lane), "f"(bias_lane) : "memory");
@@ -241,18 +260,16 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
     }
   }
   uint32_t signs = 0u;
-  if (e.gate_out) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) signs |= (v[j] > 0.f ? 1u : 0u) << j;
-  }
-  if (e.gate_in) {
+  if (gate_in) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = ((gate >> j) & 1u) ? v[j] : 0.f;
   }
-  const bool tile_gate = GENERAL && e.relu_grad;
+  const bool tile_gate = GENERAL && g_epi.relu_grad != 0;
   if (tile_gate)
-    load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(e.aux), e.ldc, row0_warp, e.M, col0, e.N, sbuf, lane);
-  if (!GENERAL && e.tma_c) {
+    load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(g_epi.aux), g_epi.ldc, row0_warp, g_epi.M, col0, g_epi.N,
+                            sbuf, lane);
+  const bool tma_out = !GENERAL && g_epi.tma_c != nullptr;
+  if (tma_out) {
     // The store that last read this box must have finished reading it.  A 16-bit box is 2 KB, so
     // the warp's 4 KB slot holds two that alternate and only the store before last is awaited.
     if (lane == 0) {
@@ -270,20 +287,27 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
 #pragma unroll
     for (int t = 0; t < VEC; ++t) {
       float x = v[q * VEC + t];
-      if (e.relu) x = fmaxf(x, 0.f);
+      if (relu) x = fmaxf(x, 0.f);
       if (tile_gate) x = load_as_float<OutT>(acte + t) > 0.f ? x : 0.f;
       if (ROUND_TF32) x = round_tf32_rn(x);
       outv[t] = float_to<OutT>(x);
     }
+    if (gate_out) {
+      // Sign bits of this piece from the values just consumed (v is not needed afterwards).
+      uint32_t s = 0u;
+#pragma unroll
+      for (int t = 0; t < VEC; ++t) s |= (__float_as_int(v[q * VEC + t]) > 0 ? 1u : 0u) << t;
+      signs |= s << (q * VEC);
+    }
     st_shared_v4(mine, *reinterpret_cast<const uint4*>(outv));   // overwrites only what this lane just read
   }
-  if (!GENERAL && e.tma_c) {
+  if (tma_out) {
     // The box already has the layout of a swizzled TMA box: one asynchronous bulk store writes
     // it (clipped at the matrix edges) without occupying the load/store pipe.
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(e.tma_c, sbuf, col0, e.tma_row0 + (int)row0_warp);
+      tma_store_2d(g_epi.tma_c, sbuf, col0, split * g_epi.M + row0_warp);
       bulk_commit_group();
     }
     return signs;
@@ -291,22 +315,25 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
   __syncwarp();
   // Not fully unrolled: eight independent 64-bit store addresses at once would
   // push the 32-bit-output variant past its register budget.
+  OutT* cbase = reinterpret_cast<OutT*>(g_epi.c) + (long long)split * g_epi.split_stride;
+  const long long ldc = g_epi.ldc;
+  const int M = g_epi.M, N = g_epi.N;
 #pragma unroll 2
   for (int i = 0; i < PIECES; ++i) {
     const int r = i * ROWS_PER_INST + lane / PIECES;
     const int q = lane % PIECES;
-    const long long grow = row0_warp + r;
+    const long long grow = (long long)row0_warp + r;
     const int gcol = col0 + q * VEC;
-    if (grow < e.M && gcol < e.N) {
+    if (grow < M && gcol < N) {
       const uint4 val = ld_shared_v4(sbuf + box_offset<OutT>((uint32_t)r, (uint32_t)q));
-      OutT* dst = cbase + grow * e.ldc + gcol;
-      if (gcol + VEC <= e.N) {
+      OutT* dst = cbase + grow * ldc + gcol;
+      if (gcol + VEC <= N) {
         *reinterpret_cast<uint4*>(dst) = val;
       } else {
         const OutT* o = reinterpret_cast<const OutT*>(&val);
 #pragma unroll
         for (int t = 0; t < VEC; ++t)
-          if (gcol + t < e.N) dst[t] = o[t];
+          if (gcol + t < N) dst[t] = o[t];
       }
     }
   }
@@ -317,23 +344,27 @@ __device__ __forceinline__ uint32_t coalesced_chunk(const EpiArgs& e, float* v, 
 // Per-thread stores of `w` (16 or 32) columns of one row: the fallback when C's
 // row pitch or base is not 16-byte aligned, and the 16-column tail chunk.
 template <typename OutT, bool ROUND_TF32>
-__device__ __forceinline__ uint32_t direct_chunk(const EpiArgs& e, float* v, uint32_t gate, int w, long long row,
-                                                 int col0) {
-  const int valid = min(w, e.N - col0);
+__device__ __forceinline__ uint32_t direct_chunk(float* v, uint32_t gate, int w, long long row, int col0, int split) {
+  const int N = g_epi.N;
+  const int valid = min(w, N - col0);
   uint32_t signs = 0u;
   if (valid <= 0) return signs;
-  OutT* crow = reinterpret_cast<OutT*>(e.c) + row * e.ldc + col0;
-  const OutT* arow = reinterpret_cast<const OutT*>(e.aux) + row * e.ldc + col0;
+  const long long ldc = g_epi.ldc;
+  OutT* crow = reinterpret_cast<OutT*>(g_epi.c) + (long long)split * g_epi.split_stride + row * ldc + col0;
+  const OutT* arow = reinterpret_cast<const OutT*>(g_epi.aux) + row * ldc + col0;
+  const float alpha = g_epi.alpha, beta = g_epi.beta;
+  const float* bias = g_epi.has_bias ? g_epi.bias : nullptr;
+  const bool relu = g_epi.relu != 0, relu_grad = g_epi.relu_grad != 0, gate_in = g_epi.gate_in != nullptr;
 #pragma unroll
   for (int j = 0; j < 32; ++j) {      // static indices keep v[] in registers
     if (j < valid) {
-      float x = e.alpha * v[j];
-      if (e.beta != 0.0f) x += e.beta * load_as_float<OutT>(crow + j);
-      if (e.has_bias) x += __ldg(e.bias + col0 + j);
+      float x = alpha * v[j];
+      if (beta != 0.0f) x += beta * load_as_float<OutT>(crow + j);
+      if (bias) x += __ldg(bias + col0 + j);
       signs |= (x > 0.f ? 1u : 0u) << j;
-      if (e.gate_in) x = ((gate >> j) & 1u) ? x : 0.f;
-      if (e.relu) x = fmaxf(x, 0.f);
-      if (e.relu_grad) x = load_as_float<OutT>(arow + j) > 0.f ? x : 0.f;
+      if (gate_in) x = ((gate >> j) & 1u) ? x : 0.f;
+      if (relu) x = fmaxf(x, 0.f);
+      if (relu_grad) x = load_as_float<OutT>(arow + j) > 0.f ? x : 0.f;
       if (ROUND_TF32) x = round_tf32_rn(x);
       crow[j] = float_to<OutT>(x);
     }
@@ -344,10 +375,11 @@ __device__ __forceinline__ uint32_t direct_chunk(const EpiArgs& e, float* v, uin
 // Chunks that cannot take the coalesced path, from chunk `c` on: per-thread stores.
 // A function of its own so that its registers do not add to the fast path's.
 template <typename OutT, bool ROUND_TF32>
-__device__ __noinline__ void epilogue_rest(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0, int lane,
-                                           int c) {
+__device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0, int split, int c) {
+  const int lane = threadIdx.x & 31;
   const long long row = (long long)row0_warp + lane;
-  const bool row_ok = row < e.M;
+  const bool row_ok = row < g_epi.M;
+  const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
   for (; c < nchunks; c += UG_EPI_STRIDE) {
     uint32_t raw[32];
@@ -355,49 +387,49 @@ __device__ __noinline__ void epilogue_rest(EpiArgs e, uint32_t t_row, int block_
     if (w == 32) tmem_ld32(t_row + (uint32_t)(c * 32), raw); else tmem_ld16(t_row + (uint32_t)(c * 32), raw);
     tmem_ld_wait();
     const int col0 = n0 + c * 32;
-    if (row_ok && col0 < e.N) {
+    if (row_ok && col0 < g_epi.N) {
       uint32_t gate = 0u;
-      if (e.gate_in) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
-      const uint32_t signs = direct_chunk<OutT, ROUND_TF32>(e, reinterpret_cast<float*>(raw), gate, w, row, col0);
-      if (e.gate_out) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
+      if (g_epi.gate_in) gate = __ldg(g_epi.gate_in + row * g_epi.gate_ld + (col0 >> 5));
+      const uint32_t signs = direct_chunk<OutT, ROUND_TF32>(reinterpret_cast<float*>(raw), gate, w, row, col0, split);
+      if (g_epi.gate_out) g_epi.gate_out[row * g_epi.gate_ld + (col0 >> 5)] = signs;
     }
   }
 }
 
 // One warp drains its share of a tile: its 32 accumulator rows (TMEM lane
-// quadrant) and every UG_EPI_STRIDE-th 32-column chunk starting at `half` (with 8
-// epilogue warps two warps share a quadrant).  The bias values and ReLU sign word of a chunk are requested one
-// chunk ahead (the first before the wait for the accumulator), and the TMEM
-// load of the next chunk is in flight while the current one is finished.  Out
-// of line, one instance per output type.  Returns false when the wait for the
-// accumulator expired.
-template <typename OutT, bool ROUND_TF32, bool GENERAL>
-__device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_n, int row0_warp, int n0,
-                                           uint32_t sbuf, uint32_t bias_smem, int lane, int half,
-                                           uint32_t bar_full, uint32_t parity, volatile int* abortp) {
-  const long long row = (long long)row0_warp + lane;
-  const bool row_ok = row < e.M;
+// quadrant) and every UG_EPI_STRIDE-th 32-column chunk starting at its `half`
+// (with 8 epilogue warps two warps share a quadrant).  The bias values and ReLU
+// sign word of a chunk are requested one chunk ahead (the first before the wait
+// for the accumulator).  Out of line, one instance per output type and mode; it
+// must not spill: with the L1 carved out as shared memory a spilled register
+// costs an L2 round trip.  Returns false when the wait for the accumulator expired.
+template <typename OutT, bool ROUND_TF32, int MODE>
+__device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0, int split, uint32_t bar_full,
+                                           uint32_t parity) {
+  const int lane = threadIdx.x & 31;
+  const int ewarp = (int)(threadIdx.x >> 5) - 2;
+  const int half = ewarp >> 2;
+  const uint32_t sbuf = g_epi.box_base + (uint32_t)ewarp * 4096u;
+  const uint32_t bias_smem = smem_u32(&g_bias_spread[ewarp][0]);
+  const bool has_bias = MODE >= 0 ? (MODE & 1) != 0 : g_epi.has_bias != 0;
+  const bool want_gate_in = MODE >= 0 ? (MODE & 8) != 0 : g_epi.gate_in != nullptr;
+  const bool want_gate_out = MODE >= 0 ? (MODE & 4) != 0 : g_epi.gate_out != nullptr;
+  const int N = g_epi.N;
+  const bool row_ok = row0_warp + lane < g_epi.M;
+  const bool rows_live = row0_warp < g_epi.M;
+  const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
-  const int nfull = e.coalesced ? (block_n >> 5) : 0;     // chunks that take the coalesced path
-  const bool rows_live = row0_warp < e.M;
+  const int nfull = g_epi.coalesced ? (block_n >> 5) : 0;     // chunks that take the coalesced path
+  // This row's words of the sign-bit matrices.
+  const long long gate_row = (long long)(row0_warp + lane) * g_epi.gate_ld;
 
   auto fetch = [&](int c, float& bias_lane, uint32_t& gate) {
     bias_lane = 0.f;
     gate = 0u;
     const int col0 = n0 + c * 32;
     if (c < nchunks) {
-      if (e.has_bias && col0 + lane < e.N) bias_lane = __ldg(e.bias + col0 + lane);
-      if (e.gate_in && row_ok && col0 < e.N) gate = __ldg(e.gate_in + row * e.gate_ld + (col0 >> 5));
-    }
-  };
-  uint32_t box_sel = 0u;
-  auto finish = [&](float* v, int c, float bias_lane, uint32_t gate) {
-    const int col0 = n0 + c * 32;
-    if (rows_live && col0 < e.N) {
-      const uint32_t box = sbuf + ((!GENERAL && sizeof(OutT) == 2 && e.tma_c) ? box_sel : 0u);
-      box_sel ^= 2048u;
-      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, GENERAL>(e, v, bias_lane, gate, row0_warp, col0, box, bias_smem, lane);
-      if (e.gate_out && row_ok) e.gate_out[row * e.gate_ld + (col0 >> 5)] = signs;
+      if (has_bias && col0 + lane < N) bias_lane = __ldg(g_epi.bias + col0 + lane);
+      if (want_gate_in && row_ok && col0 < N) gate = __ldg(g_epi.gate_in + gate_row + (col0 >> 5));
     }
   };
 
@@ -405,21 +437,29 @@ __device__ __noinline__ bool epilogue_tile(EpiArgs e, uint32_t t_row, int block_
   float bias_cur, bias_nxt;
   uint32_t gate_cur, gate_nxt;
   fetch(c, bias_cur, gate_cur);
-  if (!mbar_wait(bar_full, parity, abortp, SB_SITE_EPI_TMEM_FULL)) return false;
+  if (!mbar_wait(bar_full, parity, &g_abort_flag, SB_SITE_EPI_TMEM_FULL)) return false;
   tc_fence_after_sync();
 
   uint32_t raw_a[32];
+  uint32_t box_sel = 0u;
   for (; c < nfull; c += UG_EPI_STRIDE) {
     tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
     fetch(c + UG_EPI_STRIDE, bias_nxt, gate_nxt);    // in flight while this chunk is finished
     tmem_ld_wait();
-    finish(reinterpret_cast<float*>(raw_a), c, bias_cur, gate_cur);
+    const int col0 = n0 + c * 32;
+    if (rows_live && col0 < N) {
+      const uint32_t box = sbuf + ((MODE != -2 && sizeof(OutT) == 2 && g_epi.tma_c) ? box_sel : 0u);
+      box_sel ^= 2048u;
+      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
+                                                                     split, row0_warp, col0, box, bias_smem, lane);
+      if (want_gate_out && row_ok) g_epi.gate_out[gate_row + (col0 >> 5)] = signs;
+    }
     bias_cur = bias_nxt;
     gate_cur = gate_nxt;
   }
   // What is left for this warp: a 16-column tail chunk, or every chunk when C
   // cannot take row-contiguous 16-byte stores.
-  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32>(e, t_row, block_n, row0_warp, n0, lane, c);
+  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32>(t_row, row0_warp, n0, split, c);
   return true;
 }
 
@@ -546,8 +586,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_tmem_full[2];
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
-  __shared__ __align__(16) float bias_spread[UG_EPI_WARPS][32];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -573,7 +611,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(smem_u32(&bar_tmem_full[a]), 1);
       mbar_init(smem_u32(&bar_tmem_empty[a]), PAIR ? 2 * UG_EPI_WARPS : UG_EPI_WARPS);
     }
-    abort_flag = 0;
+    g_abort_flag = 0;
+    g_epi.c = p.C; g_epi.aux = p.aux_in; g_epi.bias = p.bias;
+    g_epi.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
+    g_epi.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
+    g_epi.tma_c = p.tma_store ? &tmap_c : nullptr;
+    g_epi.ldc = p.ldc;
+    g_epi.split_stride = p.split_stride;
+    g_epi.M = p.M; g_epi.N = p.N; g_epi.gate_ld = p.N >> 5; g_epi.block_n = p.block_n;
+    g_epi.alpha = p.alpha; g_epi.beta = p.beta;
+    g_epi.has_bias = (p.epi & SB_EPI_BIAS) ? 1 : 0; g_epi.relu = (p.epi & SB_EPI_RELU) ? 1 : 0;
+    g_epi.relu_grad = (p.epi & SB_EPI_RELU_GRAD) ? 1 : 0; g_epi.coalesced = p.coalesced;
+    g_epi.box_base = stage_base + p.epi_offset;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -591,7 +640,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (PAIR) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
-  volatile int* abortp = &abort_flag;
+  volatile int* abortp = &g_abort_flag;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -741,22 +790,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool head = (p.epi & EPI_HEAD_MASK) != 0;
-    const uint32_t sbuf = stage_base + p.epi_offset + (uint32_t)(warp - 2) * 4096u;
-    const uint32_t bias_smem = smem_u32(&bias_spread[warp - 2][0]);
-    EpiArgs e;
-    e.aux = p.aux_in; e.bias = p.bias; e.ldc = p.ldc; e.M = p.M; e.N = p.N;
-    e.alpha = p.alpha; e.beta = p.beta;
-    e.has_bias = (p.epi & SB_EPI_BIAS) != 0; e.relu = (p.epi & SB_EPI_RELU) != 0;
-    e.relu_grad = (p.epi & SB_EPI_RELU_GRAD) != 0; e.coalesced = p.coalesced != 0;
-    e.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
-    e.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
-    e.gate_ld = p.N >> 5;
-    e.tma_c = p.tma_store ? &tmap_c : nullptr;
-    e.tma_row0 = 0;
-    const bool general = p.beta != 0.0f || e.relu_grad;
+    // Which compile-time variant of the epilogue serves this launch (see coalesced_chunk).
+    int epi_mode = (p.beta != 0.0f || (p.epi & SB_EPI_RELU_GRAD)) ? -2 : -1;
+    if (epi_mode == -1 && p.alpha == 1.0f) {
+      const int flags = ((p.epi & SB_EPI_BIAS) ? 1 : 0) | ((p.epi & SB_EPI_RELU) ? 2 : 0) |
+                        ((p.epi & SB_EPI_RELU_MASK_OUT) ? 4 : 0) | ((p.epi & SB_EPI_RELU_GRAD_MASK) ? 8 : 0);
+      if (flags == 0 || flags == 3 || flags == 7 || flags == 8) epi_mode = flags;
+    }
     for (int work = worker; work < p.num_work; work += num_workers) {
       const int split = work / p.num_tiles;
-      const long long c_off = (long long)split * p.split_stride;
       int m_blk, n_blk;
       tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
       const int row0_warp = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M + quad * 32;
@@ -774,23 +816,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       } else {
         const int n0 = n_blk * p.block_n;
-        e.tma_row0 = split * p.M;
-        if (p.out_dtype == SB_F32 || p.out_dtype == SB_TF32) e.c = reinterpret_cast<float*>(p.C) + c_off;
-        else e.c = reinterpret_cast<uint16_t*>(p.C) + c_off;
         bool ok;
-#define SB_EPI_CALL(T, R, G) \
-  epilogue_tile<T, R, G>(e, t_row, p.block_n, row0_warp, n0, sbuf, bias_smem, lane, half, full_bar, acc_phase, abortp)
-        if (general) {
-          if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, true);
-          else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, true);
-          else if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, true);
-          else ok = SB_EPI_CALL(__half, false, true);
-        } else {
-          if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, false);
-          else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, false);
-          else if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, false);
-          else ok = SB_EPI_CALL(__half, false, false);
+#define SB_EPI_CALL(T, R, G) epilogue_tile<T, R, G>(t_row, row0_warp, n0, split, full_bar, acc_phase)
+#define SB_EPI_BY_TYPE(G)                                                        \
+  do {                                                                           \
+    if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, G);                \
+    else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, G);           \
+    else if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, G);  \
+    else ok = SB_EPI_CALL(__half, false, G);                                     \
+  } while (0)
+        switch (epi_mode) {
+          case 0: SB_EPI_BY_TYPE(0); break;        // plain: standalone GEMMs, wgrad partials
+          case 3: SB_EPI_BY_TYPE(3); break;        // bias + ReLU: inference layers
+          case 7: SB_EPI_BY_TYPE(7); break;        // bias + ReLU + sign bits: training forward
+          case 8: SB_EPI_BY_TYPE(8); break;        // gate by sign bits: dgrad
+          case -2: SB_EPI_BY_TYPE(-2); break;
+          default: SB_EPI_BY_TYPE(-1); break;
         }
+#undef SB_EPI_BY_TYPE
 #undef SB_EPI_CALL
         if (!ok) break;
       }
