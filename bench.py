@@ -226,6 +226,29 @@ def gemm_sweep(sb, iters=10):
     return out
 
 
+def gemm_small_cases(sb, iters=20):
+    """Benchmark configuration 1 (512^3 NT fp32, uniform[-1,1), in the fp32-exact and TF32 classes)
+    and configuration 2's ragged case (4000 x 3000 x 1000), as microseconds and TFLOP/s."""
+    out = {}
+    rng = np.random.Generator(np.random.Philox(1))
+    cases = [("cfg1_512_fp32_NT", 512, 512, 512, "f32", False, True), ("cfg1_512_tf32_NT", 512, 512, 512, "tf32", False, True),
+             ("ragged_bf16_NT", 4000, 3000, 1000, "bf16", False, True), ("ragged_bf16_NN", 4000, 3000, 1000, "bf16", False, False),
+             ("ragged_bf16_TN", 4000, 3000, 1000, "bf16", True, False), ("ragged_tf32_NT", 4000, 3000, 1000, "tf32", False, True)]
+    for name, m, n, k, dt, at, bt in cases:
+        a = sb.DeviceArray.from_numpy(rng.uniform(-1, 1, size=(k, m) if at else (m, k)).astype(np.float32), "f32" if dt == "f32" else dt)
+        b = sb.DeviceArray.from_numpy(rng.uniform(-1, 1, size=(n, k) if bt else (k, n)).astype(np.float32), "f32" if dt == "f32" else dt)
+        c = sb.DeviceArray((m, n), "f32")
+        for _ in range(3):
+            sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt)
+        e0 = sb.Event().record()
+        for _ in range(iters):
+            sb.matmul(at, bt, 1.0, a, b, 0.0, c, in_dtype=dt)
+        e1 = sb.Event().record()
+        ms = e0.elapsed_ms(e1) / iters
+        out[name] = {"us": round(ms * 1e3, 2), "tflops": round(2.0 * m * n * k / ms / 1e9, 1)}
+    return out
+
+
 def reference_kernel_row(sb):
     """The reference's own TF32 WMMA GEMM (recompiled for sm_100a by oracle/build_ref.py) and this
     library's TF32 GEMM on the reference's baked shape, 8192 x 8192 x 4096 NT, alpha = beta = 1."""
@@ -450,6 +473,7 @@ def run_ours(args, rank, world, local_rank):
                "sample": "NumPy float32 %s step on %d rows, mean of 3" % ("training" if training else "forward", rows)}
         if not args.no_sweep:
             extra["gemm_4096_tflops"] = gemm_sweep(sb)
+            extra["gemm_small_cases"] = gemm_small_cases(sb)
             ref = reference_kernel_row(sb)
             if ref is not None:
                 extra["reference_wmma_kernel_8192x8192x4096_tf32"] = ref
