@@ -216,6 +216,17 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
                     float* grads, int with_bias, void* scratch, size_t scratch_bytes, float* loss,
                     void* stream);
 
+/* The same pass restricted to layers first_layer, first_layer-1, ..., last_layer
+ * (first_layer = n_layers-1 zeroes grads and computes d logits and the loss
+ * first).  Successive calls that together cover n_layers-1 .. 0 equal one
+ * sb_mlp_backward; a data-parallel caller uses them to start the all-reduce of
+ * a layer's gradient segment while the layers below are still being computed. */
+int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                          const void* x, const void* w_compute, void* const* activations,
+                          void* const* relu_bits, const float* probs, const uint8_t* mask,
+                          const float* target, float* grads, int with_bias, void* scratch,
+                          size_t scratch_bytes, float* loss, int first_layer, int last_layer, void* stream);
+
 /* params -= lr * grads over n elements, and w_compute (may be NULL) = params
  * rounded to compute_dtype.  No counterpart in the reference. */
 int sb_sgd_update(float* params, const float* grads, void* w_compute, long long n, float lr,

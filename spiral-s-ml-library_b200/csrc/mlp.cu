@@ -335,19 +335,22 @@ int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int
   return SB_OK;
 }
 
-int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
-                    const void* x, const void* w_compute, void* const* activations,
-                    void* const* relu_bits, const float* probs, const uint8_t* mask, const float* target,
-                    float* grads, int with_bias, void* scratch, size_t scratch_bytes, float* loss,
-                    void* stream) {
+int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                          const void* x, const void* w_compute, void* const* activations,
+                          void* const* relu_bits, const float* probs, const uint8_t* mask,
+                          const float* target, float* grads, int with_bias, void* scratch,
+                          size_t scratch_bytes, float* loss, int first_layer, int last_layer, void* stream) {
   int rc = check_layout("sb_mlp_backward", n_layers, sizes, batch, in_dtype);
   if (rc != SB_OK) return rc;
   if (!grads) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: grads is null");
+  if (first_layer < last_layer || first_layer >= n_layers || last_layer < 0)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: layer range [%d, %d] of %d layers", last_layer, first_layer, n_layers);
+  const bool from_top = first_layer == n_layers - 1;
   long long off[2 * MLP_MAX_LAYERS + 1];
   param_offsets(n_layers, sizes, off);
   cudaStream_t s = (cudaStream_t)stream;
   if (batch == 0) {
-    SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+    if (from_top) SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
     return SB_OK;
   }
   if (!x || !w_compute || !probs || !target || !scratch)
@@ -366,18 +369,21 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
   for (int i = 0; i < n_layers; ++i) max_w = max(max_w, padded_out(sizes[i + 1]));
   const size_t dy_bytes = (size_t)align_up((long long)batch * max_w * es, 256);
   char* sc = reinterpret_cast<char*>(scratch);
-  void* dy_cur = sc;
-  void* dy_next = sc + dy_bytes;
+  // The two dY buffers alternate once per dgrad: layer i reads the buffer chosen by the number of
+  // dgrads above it, so a pass split into several calls finds its input where the last call left it.
+  const bool odd = ((n_layers - 1 - first_layer) & 1) != 0;
+  void* dy_cur = odd ? sc + dy_bytes : sc;
+  void* dy_next = odd ? sc : sc + dy_bytes;
   float* partial = reinterpret_cast<float*>(sc + 2 * dy_bytes);
 
   // Bias gradients are accumulated with atomics into zeroed memory; weight
   // gradients are overwritten.  Zero the whole buffer (padding included) so that
   // the all-reduce and the SGD update can treat it as one flat vector.
-  SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+  if (from_top) SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
 
   const int n_out = sizes[n_layers];
   const int ld_out = padded_out(n_out);
-  {
+  if (from_top) {
     const int blocks = blocks_for(batch, 256);
     if (in_dtype == SB_BF16)
       ce_grad_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(probs, target, mask, (__nv_bfloat16*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
@@ -389,7 +395,7 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
   SB_CUDA(cudaGetLastError());
   }
 
-  for (int i = n_layers - 1; i >= 0; --i) {
+  for (int i = first_layer; i >= last_layer; --i) {
     const int fan_out = padded_out(sizes[i + 1]), fan_in = sizes[i];
     const void* h_in = i == 0 ? x : activations[i - 1];
     if (with_bias) {
@@ -434,6 +440,16 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
     }
   }
   return SB_OK;
+}
+
+int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                    const void* x, const void* w_compute, void* const* activations,
+                    void* const* relu_bits, const float* probs, const uint8_t* mask, const float* target,
+                    float* grads, int with_bias, void* scratch, size_t scratch_bytes, float* loss,
+                    void* stream) {
+  return sb_mlp_backward_range(n_layers, sizes, batch, inv_global_batch, in_dtype, x, w_compute, activations,
+                               relu_bits, probs, mask, target, grads, with_bias, scratch, scratch_bytes, loss,
+                               n_layers - 1, 0, stream);
 }
 
 int sb_sgd_update(float* params, const float* grads, void* w_compute, long long n, float lr,

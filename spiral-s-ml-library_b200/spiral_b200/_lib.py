@@ -85,6 +85,7 @@ SIGNATURES = {
     "sb_mlp_forward_static": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_backward_scratch_bytes": (_I, [_I, _IP, _I, _I, POINTER(c_size_t)]),
     "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),
+    "sb_mlp_backward_range": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _I, _I, _P]),
     "sb_sgd_update": (_I, [_P, _P, _P, ctypes.c_longlong, _F, _I, _P]),
     "sb_mlp_train_step": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _F, _P, _Z, _P, _P]),
 }

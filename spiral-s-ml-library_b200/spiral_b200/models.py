@@ -158,6 +158,22 @@ class PolicyMLP:
                   self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
         return self.grads
 
+    def backward_layers(self, x, mask, target, first_layer, last_layer, global_batch=None, stream=None):
+        """The backward pass of layers first_layer .. last_layer (descending); successive calls covering
+        n_layers-1 .. 0 equal one ``backward``."""
+        gb = self.batch if global_batch is None else int(global_batch)
+        _lib.call("sb_mlp_backward_range", self.n_layers, self._sizes_c, self.batch, ctypes.c_float(1.0 / gb),
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr, self._acts_c, self._bits_c,
+                  self.probs.ptr, device_ptr(mask), device_ptr(target), device_ptr(self.grads), int(self.with_bias),
+                  self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, int(first_layer), int(last_layer),
+                  stream_ptr(stream))
+        return self.grads
+
+    def layer_segment(self, layer):
+        """[begin, end) of layer `layer`'s weights and bias inside the flat parameter / gradient vectors."""
+        end = self.offsets[2 * layer + 2] if layer + 1 < self.n_layers else self.n_params
+        return self.offsets[2 * layer], end
+
     def sgd(self, lr, stream=None):
         _lib.call("sb_sgd_update", self.params.ptr, device_ptr(self.grads), self.w_compute.ptr,
                   ctypes.c_longlong(self.n_params), ctypes.c_float(lr), _lib.DTYPE_CODES[self.storage],

@@ -27,21 +27,38 @@ def bucket_ranges(n_elements, bucket_elements):
 class DataParallel:
     """Wraps a ``PolicyMLP`` built for this rank's shard."""
 
-    def __init__(self, net, global_batch, all_reduce=None, world_size=1, rank=0):
+    def __init__(self, net, global_batch, all_reduce=None, world_size=1, rank=0, all_reduce_segment=None):
+        """``all_reduce(buffer)`` sums the whole flat gradient buffer in place.  Optional
+        ``all_reduce_segment(buffer, begin, end)`` starts an asynchronous sum of elements
+        [begin, end) and returns a handle with ``wait()`` (or None when it completed in order)."""
         self.net, self.global_batch = net, int(global_batch)
         self.all_reduce, self.world_size, self.rank = all_reduce, int(world_size), int(rank)
-        if self.world_size > 1 and all_reduce is None:
+        self.all_reduce_segment = all_reduce_segment
+        if self.world_size > 1 and all_reduce is None and all_reduce_segment is None:
             raise ValueError("more than one rank needs an all_reduce callable")
 
     def train_step(self, x, mask, target, lr, stream=None):
         """forward + backward on the local shard (gradients already scaled by 1/global_batch),
-        one all-reduce of the flat gradient buffer, then the same SGD update on every rank."""
+        all-reduce of the flat gradient buffer, then the same SGD update on every rank.
+
+        With ``all_reduce_segment`` the exchange is issued layer by layer, top layer first, as soon as
+        that layer's gradients are enqueued, so it overlaps the backward of the layers below."""
         net = self.net
         net.loss.fill_zero(stream)
         net.forward(x, mask, stream=stream)
-        net.backward(x, mask, target, global_batch=self.global_batch, stream=stream)
-        if self.world_size > 1:
-            self.all_reduce(net.grads)
+        if self.world_size > 1 and self.all_reduce_segment is not None:
+            pending = []
+            for layer in range(net.n_layers - 1, -1, -1):
+                net.backward_layers(x, mask, target, layer, layer, global_batch=self.global_batch, stream=stream)
+                begin, end = net.layer_segment(layer)
+                pending.append(self.all_reduce_segment(net.grads, begin, end))
+            for handle in pending:
+                if handle is not None:
+                    handle.wait()
+        else:
+            net.backward(x, mask, target, global_batch=self.global_batch, stream=stream)
+            if self.world_size > 1:
+                self.all_reduce(net.grads)
         net.sgd(lr, stream=stream)
 
     def infer(self, x, mask=None, stream=None):

@@ -187,3 +187,26 @@ def test_fused_forward_other_shapes_and_limits(gpu):
     with pytest.raises(SpiralError) as err:
         wide.forward_fused(gpu.DeviceArray((128, 512), "bf16"))
     assert err.value.code == -3
+
+
+def test_backward_split_by_layer_equals_whole_pass(gpu):
+    """sb_mlp_backward_range over layers 3, 2, 1, 0 in four calls gives the gradients of one call
+    (weight gradients bit-identical; bias gradients are atomic sums, equal to rounding)."""
+    sizes, batch = [32, 256, 256, 256, 3], 2048
+    net, ws, bs = build(gpu, sizes, batch, "bf16", 21, training=True, bias_scale=0.05)
+    x, mask = so.leduc_inputs(21, batch)
+    target = so.random_target(22, mask)
+    dx, dm, dt = gpu.to_storage(x, "bf16"), gpu.DeviceArray.from_numpy(mask), gpu.DeviceArray.from_numpy(target)
+    net.forward(dx, dm, head_flags=8)
+    whole = net.backward(dx, dm, dt).numpy().copy()
+    loss_whole = float(net.loss.numpy()[0])
+    net.loss.fill_zero()
+    net.grads.fill_zero()
+    for layer in (3, 2, 1, 0):
+        net.backward_layers(dx, dm, dt, layer, layer)
+    split = net.grads.numpy()
+    for i, ((gw, gb), (ww, wb)) in enumerate(zip(net.split_flat(split), net.split_flat(whole))):
+        np.testing.assert_array_equal(gw, ww)
+        np.testing.assert_allclose(gb, wb, rtol=1e-4, atol=1e-7)
+    assert abs(float(net.loss.numpy()[0]) - loss_whole) <= 1e-5 * abs(loss_whole)
+    assert net.layer_segment(0)[0] == 0 and net.layer_segment(3)[1] == net.n_params
