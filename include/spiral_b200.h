@@ -86,6 +86,13 @@ int sb_stream_wait_event(void* stream, void* event);        /* later work on str
  * waits: status[0] = first wait site that expired (0 = healthy), status[1] =
  * count of expired waits.  Synchronises the device. */
 int sb_device_status(int* status2, int clear);
+/* Exercises the bounded device-side wait on purpose: one small kernel waits on
+ * a barrier nothing signals; after the library's wait limit (0.4 s) it must
+ * return with result5 = {0, 0, ms waited by the first waiter, ms waited by the
+ * second, 1} and sb_device_status must report wait site 8.  The context stays
+ * usable.  No counterpart in the reference (a failed device assert kills its
+ * context, ml/matmul/run.py:1240).  Allocates 20 bytes for the duration of the call. */
+int sb_selftest_bounded_wait(int* result5);
 /* Number of kernels this library has launched in this process so far. */
 unsigned long long sb_launch_count(void);
 /* Device-side timing of the tensor-core GEMM launches between begin and end:

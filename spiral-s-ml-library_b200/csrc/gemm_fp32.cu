@@ -16,8 +16,8 @@ template <bool A_TRANS, bool B_TRANS>
 __global__ void __launch_bounds__(F_THREADS)
 sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M,
              int N, int K, float alpha, float beta, int epi, const float* __restrict__ bias) {
-  __shared__ float As[F_BK][F_BM + 4];
-  __shared__ float Bs[F_BK][F_BN + 4];
+  __shared__ __align__(16) float As[F_BK][F_BM + 4];
+  __shared__ __align__(16) float Bs[F_BK][F_BN + 4];
   const int tid = threadIdx.x;
   const int tx = tid & 15;   // column group
   const int ty = tid >> 4;   // row group
@@ -50,11 +50,11 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < F_BK; ++k) {
-      float a[4], b[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx * 4 + j];
+      // one 16-byte shared-memory load per operand (rows are 272 bytes apart, a multiple of 16)
+      const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 bv = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+      const float a[4] = {av.x, av.y, av.z, av.w};
+      const float b[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll

@@ -8,3 +8,4 @@
 #include "api.cu"
 #include "mlp.cu"
 #include "mlp_fused.cu"
+#include "selftest.cu"

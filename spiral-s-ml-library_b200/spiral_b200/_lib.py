@@ -66,6 +66,7 @@ SIGNATURES = {
     "sb_stream_wait_event": (_I, [_P, _P]),
     "sb_event_elapsed_ms": (_I, [_P, _P, POINTER(c_float)]),
     "sb_device_status": (_I, [_IP, _I]),
+    "sb_selftest_bounded_wait": (_I, [_IP]),
     "sb_launch_count": (ctypes.c_ulonglong, []),
     "sb_gemm_profile_begin": (_I, []),
     "sb_gemm_profile_end": (_I, [_IP, POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
