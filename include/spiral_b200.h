@@ -53,7 +53,14 @@ enum {
   /* ReLU sign bits instead of the activation tile (N % 32 == 0): word
    * [row, c] of a uint32[M, N/32] matrix, bit j = (value[row, 32c + j] > 0). */
   SB_EPI_RELU_MASK_OUT = 64,  /* with SB_EPI_RELU: also write the sign bits to aux_out */
-  SB_EPI_RELU_GRAD_MASK = 128 /* gate by the sign bits in aux_in (the backward twin of the above) */
+  SB_EPI_RELU_GRAD_MASK = 128,/* gate by the sign bits in aux_in (the backward twin of the above) */
+  /* Column sums of the finished values (after the sign-bit gate, before storage
+   * rounding) are ADDED to aux_out: fp32[N], which the caller zeroes.  This is
+   * the bias gradient of the layer below when the GEMM is a dgrad.  N % 32 == 0,
+   * alpha == 1, beta == 0, tensor-core classes; combines only with
+   * SB_EPI_RELU_GRAD_MASK.  The additions are atomic: their order, hence the
+   * last bits of the sums, can differ between runs. */
+  SB_EPI_COLSUM_OUT = 256
 };
 
 /* ---- runtime ------------------------------------------------------------ */

@@ -18,7 +18,7 @@ int sb_sgemm_launch(int a_trans, int b_trans, float alpha, const float* A, const
 namespace {
 constexpr int HEAD_FLAGS = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
 constexpr int GATE_FLAGS = SB_EPI_RELU_MASK_OUT | SB_EPI_RELU_GRAD_MASK;
-constexpr int ALL_FLAGS = SB_EPI_BIAS | SB_EPI_RELU | SB_EPI_RELU_GRAD | HEAD_FLAGS | GATE_FLAGS;
+constexpr int ALL_FLAGS = SB_EPI_BIAS | SB_EPI_RELU | SB_EPI_RELU_GRAD | HEAD_FLAGS | GATE_FLAGS | SB_EPI_COLSUM_OUT;
 
 int run_heads_unfused(float* C, int M, int N, int epi, const uint8_t* mask, void* aux_out,
                       void* stream) {
@@ -61,6 +61,15 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
     if ((epilogue & SB_EPI_RELU_MASK_OUT) && !aux_out) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_RELU_MASK_OUT without aux_out");
     if ((epilogue & SB_EPI_RELU_GRAD_MASK) && (!aux_in || (epilogue & SB_EPI_RELU_GRAD)))
       return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_RELU_GRAD_MASK needs aux_in and excludes SB_EPI_RELU_GRAD");
+  }
+  if (epilogue & SB_EPI_COLSUM_OUT) {
+    if (!aux_out) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul: SB_EPI_COLSUM_OUT without aux_out");
+    if (N % 32 != 0) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_COLSUM_OUT needs N %% 32 == 0 (N=%d)", N);
+    if (in_dtype == SB_F32) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_COLSUM_OUT needs a tensor-core input class");
+    if (epilogue & ~(SB_EPI_COLSUM_OUT | SB_EPI_RELU_GRAD_MASK))
+      return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_COLSUM_OUT combines only with SB_EPI_RELU_GRAD_MASK");
+    if (beta != 0.0f || alpha != 1.0f)
+      return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_COLSUM_OUT needs alpha == 1 and beta == 0");
   }
   if (in_dtype == SB_F32 && out_dtype == SB_TF32) out_dtype = SB_F32;
   if ((epilogue & HEAD_FLAGS) && out_dtype != SB_F32)

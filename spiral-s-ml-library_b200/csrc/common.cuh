@@ -13,6 +13,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "../../include/spiral_b200.h"
 
@@ -64,6 +65,48 @@ static inline int sb_dtype_size(int dt) {
 }
 
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  A kernel launched through sb_launch() may
+// become resident while the kernel before it on the stream is still draining:
+// its CTAs set themselves up (barriers, tensor memory, descriptor prefetch) and
+// then block in sb_grid_dependency_wait() until the earlier grid has completed
+// and its writes are visible.  Every kernel launched this way must call
+// sb_grid_dependency_wait() before its first access to global memory, and
+// calls sb_grid_dependents_launch() right after it so that its own successor
+// can move up the same way.  SB_NO_PDL=1 in the environment turns the
+// attribute off (plain stream order); the device calls are then no-ops.
+__device__ __forceinline__ void sb_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void sb_grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool sb_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (sb_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 constexpr int SB_NUM_SMS_FALLBACK = 148;
 // Wall-clock limit of one device-side wait (nanoseconds of %globaltimer).

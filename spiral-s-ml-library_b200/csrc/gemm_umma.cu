@@ -190,6 +190,7 @@ struct EpiShared {
   const float* bias;
   const uint32_t* gate_in;  // ReLU sign bits, one word per row and 32 columns (SB_EPI_RELU_GRAD_MASK)
   uint32_t* gate_out;       // where the forward pass records them (SB_EPI_RELU_MASK_OUT)
+  float* colsum;            // column sums of the output are added here (SB_EPI_COLSUM_OUT)
   const CUtensorMap* tma_c; // non-null: finished boxes leave through TMA stores (32 x 32 element boxes over C)
   long long ldc;
   long long split_stride;
@@ -341,6 +342,29 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
   return signs;
 }
 
+// Adds the column sums of a finished 32-row x 32-column chunk to g_epi.colsum.
+// Each lane holds one row (v[0..31], already scaled, biased and gated); a
+// butterfly of 31 shuffles folds the 32 rows so that lane j ends with the sum
+// of column j, and the warp issues one 128-byte vector reduction to global
+// memory.  The sums are taken before the rounding to the storage type.
+template <int MODE>
+__device__ __forceinline__ void chunk_colsum(float* v, int col0, int lane) {
+  static_assert(MODE >= 0 && (MODE & 3) == 0, "column sums are built for the modes without bias and ReLU");
+  // Rows beyond M are zero: their rows of A were zero-filled and nothing was added to them.
+#define SB_FOLD(HALF)                                                      \
+  {                                                                        \
+    const bool up = (lane & HALF) != 0;                                    \
+    _Pragma("unroll") for (int i = 0; i < HALF; ++i) {                     \
+      const float send = up ? v[i] : v[i + HALF];                          \
+      const float keep = up ? v[i + HALF] : v[i];                          \
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, HALF);              \
+    }                                                                      \
+  }
+  SB_FOLD(16) SB_FOLD(8) SB_FOLD(4) SB_FOLD(2) SB_FOLD(1)
+#undef SB_FOLD
+  if (col0 + lane < g_epi.N) atomicAdd(g_epi.colsum + col0 + lane, v[0]);
+}
+
 // Per-thread stores of `w` (16 or 32) columns of one row: the fallback when C's
 // row pitch or base is not 16-byte aligned, and the 16-column tail chunk.
 template <typename OutT, bool ROUND_TF32>
@@ -453,6 +477,7 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
       const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
                                                                      split, row0_warp, col0, box, bias_smem, lane);
       if (want_gate_out && row_ok) g_epi.gate_out[gate_row + (col0 >> 5)] = signs;
+      if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_a), col0, lane);
     }
     bias_cur = bias_nxt;
     gate_cur = gate_nxt;
@@ -615,6 +640,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     g_epi.c = p.C; g_epi.aux = p.aux_in; g_epi.bias = p.bias;
     g_epi.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
     g_epi.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
+    g_epi.colsum = (p.epi & SB_EPI_COLSUM_OUT) ? reinterpret_cast<float*>(p.aux_out) : nullptr;
     g_epi.tma_c = p.tma_store ? &tmap_c : nullptr;
     g_epi.ldc = p.ldc;
     g_epi.split_stride = p.split_stride;
@@ -641,6 +667,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &g_abort_flag;
+  // Everything above touched only this CTA's shared and tensor memory; from here on the
+  // kernel reads what earlier kernels on the stream wrote.
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -794,8 +824,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int epi_mode = (p.beta != 0.0f || (p.epi & SB_EPI_RELU_GRAD)) ? -2 : -1;
     if (epi_mode == -1 && p.alpha == 1.0f) {
       const int flags = ((p.epi & SB_EPI_BIAS) ? 1 : 0) | ((p.epi & SB_EPI_RELU) ? 2 : 0) |
-                        ((p.epi & SB_EPI_RELU_MASK_OUT) ? 4 : 0) | ((p.epi & SB_EPI_RELU_GRAD_MASK) ? 8 : 0);
-      if (flags == 0 || flags == 3 || flags == 7 || flags == 8) epi_mode = flags;
+                        ((p.epi & SB_EPI_RELU_MASK_OUT) ? 4 : 0) | ((p.epi & SB_EPI_RELU_GRAD_MASK) ? 8 : 0) |
+                        ((p.epi & SB_EPI_COLSUM_OUT) ? 16 : 0);
+      if (flags == 0 || flags == 3 || flags == 7 || flags == 8 || flags == 16 || flags == 24) epi_mode = flags;
     }
     for (int work = worker; work < p.num_work; work += num_workers) {
       const int split = work / p.num_tiles;
@@ -830,6 +861,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           case 3: SB_EPI_BY_TYPE(3); break;        // bias + ReLU: inference layers
           case 7: SB_EPI_BY_TYPE(7); break;        // bias + ReLU + sign bits: training forward
           case 8: SB_EPI_BY_TYPE(8); break;        // gate by sign bits: dgrad
+          case 16: SB_EPI_BY_TYPE(16); break;      // plain + column sums
+          case 24: SB_EPI_BY_TYPE(24); break;      // dgrad that also sums its output columns (bias gradient)
           case -2: SB_EPI_BY_TYPE(-2); break;
           default: SB_EPI_BY_TYPE(-1); break;
         }
@@ -1071,7 +1104,8 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_trans ? 1 : 0;   // A stored [K,M]: M contiguous
   p.b_mn = b_trans ? 0 : 1;   // B stored [K,N]: N contiguous
-  plan_umma(p, in_dtype, cached_sm_count(), !(epi & EPI_HEAD_MASK) && sb_pair_mode_enabled(), (epi & EPI_GATE_MASK) != 0);
+  plan_umma(p, in_dtype, cached_sm_count(), !(epi & EPI_HEAD_MASK) && sb_pair_mode_enabled(),
+            (epi & (EPI_GATE_MASK | SB_EPI_COLSUM_OUT)) != 0);
   p.alpha = alpha; p.beta = beta;
   p.C = C; p.ldc = N; p.out_dtype = out_dtype;
   p.epi = epi; p.bias = bias; p.mask = mask; p.aux_in = aux_in; p.aux_out = aux_out;
@@ -1138,26 +1172,13 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   sb_prof_before(stream);
   if (!p.pair) {
     const int grid = min(p.num_work, cached_sm_count());
-    if (p.kind_tf32) umma_gemm_kernel<false, true><<<grid, UG_THREADS, smem, stream>>>(ta, tb, tc, p);
-    else umma_gemm_kernel<false, false><<<grid, UG_THREADS, smem, stream>>>(ta, tb, tc, p);
+    if (p.kind_tf32) SB_CUDA(sb_launch(umma_gemm_kernel<false, true>, dim3(grid), dim3(UG_THREADS), smem, stream, 1, ta, tb, tc, p));
+    else SB_CUDA(sb_launch(umma_gemm_kernel<false, false>, dim3(grid), dim3(UG_THREADS), smem, stream, 1, ta, tb, tc, p));
   } else {
     // One cluster of two CTAs per worker; the two CTAs of a cluster share a TPC.
     const int workers = min(p.num_work, cached_sm_count() / 2);
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(2 * workers, 1, 1);
-    cfg.blockDim = dim3(UG_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (p.kind_tf32) SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, true>, ta, tb, tc, p));
-    else SB_CUDA(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<true, false>, ta, tb, tc, p));
+    if (p.kind_tf32) SB_CUDA(sb_launch(umma_gemm_kernel<true, true>, dim3(2 * workers), dim3(UG_THREADS), smem, stream, 2, ta, tb, tc, p));
+    else SB_CUDA(sb_launch(umma_gemm_kernel<true, false>, dim3(2 * workers), dim3(UG_THREADS), smem, stream, 2, ta, tb, tc, p));
   }
   sb_prof_after(stream, 2.0 * M * N * K);
   SB_COUNT_LAUNCH();

@@ -66,6 +66,8 @@ template <typename DyT, bool ROUND_TF32>
 __global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __restrict__ target,
                                const uint8_t* __restrict__ mask, DyT* __restrict__ dy, int rows, int n,
                                int ld, float inv_batch, float* __restrict__ loss) {
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
   float local = 0.f;
   for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
        r += (long long)gridDim.x * blockDim.x) {
@@ -109,6 +111,8 @@ __global__ void __launch_bounds__(256)
 colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int n, int rows_per_block) {
   constexpr int VEC = 16 / sizeof(DyT);
   __shared__ float part[8][32 * VEC + 1];
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col0 = (blockIdx.x * 32 + lane) * VEC;
   const int r0 = blockIdx.y * rows_per_block;
@@ -145,6 +149,8 @@ colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int 
 // grads[i] = sum over splits of partial[s][i]; deterministic order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                      long long n, int splits) {
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
     float s = 0.f;
@@ -156,6 +162,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* _
 // params -= lr * grads ; compute copy = params rounded to the storage type.
 __global__ void sgd_kernel(float* __restrict__ params, const float* __restrict__ grads,
                            void* __restrict__ compute, long long n, float lr, int dt) {
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
     const float w = params[i] - lr * grads[i];
@@ -386,19 +394,23 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
   if (from_top) {
     const int blocks = blocks_for(batch, 256);
     if (in_dtype == SB_BF16)
-      ce_grad_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(probs, target, mask, (__nv_bfloat16*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
+      SB_CUDA(sb_launch(ce_grad_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (__nv_bfloat16*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss));
     else if (in_dtype == SB_F16)
-      ce_grad_kernel<__half, false><<<blocks, 256, 0, s>>>(probs, target, mask, (__half*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
+      SB_CUDA(sb_launch(ce_grad_kernel<__half, false>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (__half*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss));
     else
-      ce_grad_kernel<float, true><<<blocks, 256, 0, s>>>(probs, target, mask, (float*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss);
+      SB_CUDA(sb_launch(ce_grad_kernel<float, true>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (float*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss));
     SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   }
 
+  // True when dY of the current layer came out of a dgrad whose epilogue already added its column
+  // sums to the bias gradient, so that the stand-alone column-sum pass (a second read of dY) is skipped.
+  // A pass split into several calls: the dgrad of the layer above ran in an earlier call.
+  bool bias_done = !from_top && with_bias && relu_bits && relu_bits[first_layer] && sizes[first_layer + 1] % 32 == 0;
   for (int i = first_layer; i >= last_layer; --i) {
     const int fan_out = padded_out(sizes[i + 1]), fan_in = sizes[i];
     const void* h_in = i == 0 ? x : activations[i - 1];
-    if (with_bias) {
+    if (with_bias && !bias_done) {
       // Enough blocks to fill the GPU a few times over, each with a long row slab.
       const int strip = 32 * (16 / es);
       const int strips = (fan_out + strip - 1) / strip;
@@ -407,9 +419,9 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
       if (rows_per_block < 64) rows_per_block = 64;
       dim3 grid(strips, (batch + rows_per_block - 1) / rows_per_block);
       float* db = grads + off[2 * i + 1];
-      if (in_dtype == SB_BF16) colsum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dy_cur, db, batch, fan_out, rows_per_block);
-      else if (in_dtype == SB_F16) colsum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)dy_cur, db, batch, fan_out, rows_per_block);
-      else colsum_kernel<float><<<grid, 256, 0, s>>>((const float*)dy_cur, db, batch, fan_out, rows_per_block);
+      if (in_dtype == SB_BF16) SB_CUDA(sb_launch(colsum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, 1, (const __nv_bfloat16*)dy_cur, db, batch, fan_out, rows_per_block));
+      else if (in_dtype == SB_F16) SB_CUDA(sb_launch(colsum_kernel<__half>, dim3(grid), dim3(256), 0, s, 1, (const __half*)dy_cur, db, batch, fan_out, rows_per_block));
+      else SB_CUDA(sb_launch(colsum_kernel<float>, dim3(grid), dim3(256), 0, s, 1, (const float*)dy_cur, db, batch, fan_out, rows_per_block));
       SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
     }
@@ -422,7 +434,7 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
     if (rc != SB_OK) return rc;
     if (want > 1) {
       const long long n = (long long)fan_out * fan_in;
-      splitk_reduce_kernel<<<blocks_for(n, 256), 256, 0, s>>>(partial, dw, n, used);
+      SB_CUDA(sb_launch(splitk_reduce_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, s, 1, partial, dw, n, used));
       SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
     }
@@ -432,10 +444,16 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
       // The gate is ReLU'(H_in): read from the sign bits the forward pass recorded
       // when they exist (4 bytes per row and 32 columns), else from H_in itself.
       const bool bits = relu_bits && relu_bits[i - 1] && fan_in % 32 == 0;
+      // The output is dY of layer i-1, whose column sums are that layer's bias gradient
+      // (fan_in = sizes[i] is its unpadded width: hidden widths are multiples of 8 and, here, of 32).
+      const bool sum_cols = bits && with_bias;
+      float* db_below = grads + off[2 * (i - 1) + 1];
       rc = sb_umma_gemm_launch(0, 0, 1.0f, dy_cur, w, 0.0f, dy_next, batch, fan_in, fan_out, in_dtype, st,
-                               bits ? SB_EPI_RELU_GRAD_MASK : SB_EPI_RELU_GRAD, nullptr, nullptr,
-                               bits ? (const void*)relu_bits[i - 1] : h_in, nullptr, s, 1, nullptr);
+                               bits ? (SB_EPI_RELU_GRAD_MASK | (sum_cols ? SB_EPI_COLSUM_OUT : 0)) : SB_EPI_RELU_GRAD,
+                               nullptr, nullptr, bits ? (const void*)relu_bits[i - 1] : h_in,
+                               sum_cols ? (void*)db_below : nullptr, s, 1, nullptr);
       if (rc != SB_OK) return rc;
+      bias_done = sum_cols;
       void* t = dy_cur; dy_cur = dy_next; dy_next = t;
     }
   }
@@ -457,7 +475,7 @@ int sb_sgd_update(float* params, const float* grads, void* w_compute, long long 
   if (n < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_sgd_update: negative length");
   if (n == 0) return SB_OK;
   if (!params || !grads) return sb_fail(SB_ERR_BAD_ARG, "sb_sgd_update: null pointer");
-  sgd_kernel<<<blocks_for(n, 256), 256, 0, (cudaStream_t)stream>>>(params, grads, w_compute, n, lr, compute_dtype);
+  SB_CUDA(sb_launch(sgd_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, (cudaStream_t)stream, 1, params, grads, w_compute, n, lr, compute_dtype));
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;

@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 static thread_local char t_error[512] = "";
@@ -21,6 +22,15 @@ double g_prof_flops[PROF_MAX];
 float g_prof_ms[PROF_MAX];
 int g_prof_last_n = 0;
 }  // namespace
+
+bool sb_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SB_NO_PDL");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
 
 void sb_prof_before(cudaStream_t s) {
   if (!g_prof_on || g_prof_n >= PROF_MAX) return;

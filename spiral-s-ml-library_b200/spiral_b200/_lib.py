@@ -23,7 +23,7 @@ DTYPE_CODES = {"f32": F32, "tf32": TF32, "bf16": BF16, "f16": F16, "i32": I32, "
 # epilogue flags
 EPI_NONE, EPI_BIAS, EPI_RELU, EPI_RELU_GRAD = 0, 1, 2, 4
 EPI_MASKED_SOFTMAX, EPI_REGRET_MATCHING, EPI_ARGMAX = 8, 16, 32
-EPI_RELU_MASK_OUT, EPI_RELU_GRAD_MASK = 64, 128
+EPI_RELU_MASK_OUT, EPI_RELU_GRAD_MASK, EPI_COLSUM_OUT = 64, 128, 256
 
 
 class SpiralError(RuntimeError):

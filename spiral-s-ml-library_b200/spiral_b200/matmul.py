@@ -13,6 +13,7 @@ EPILOGUE_FLAGS = {
     "bias": _lib.EPI_BIAS, "relu": _lib.EPI_RELU, "relu_grad": _lib.EPI_RELU_GRAD,
     "masked_softmax": _lib.EPI_MASKED_SOFTMAX, "regret_matching": _lib.EPI_REGRET_MATCHING,
     "argmax": _lib.EPI_ARGMAX, "relu_mask_out": _lib.EPI_RELU_MASK_OUT, "relu_grad_mask": _lib.EPI_RELU_GRAD_MASK,
+    "colsum_out": _lib.EPI_COLSUM_OUT,
 }
 
 

@@ -158,6 +158,40 @@ def test_relu_sign_bits_forward_and_backward_gate(gpu):
     np.testing.assert_array_equal(by_bits, by_tile)
 
 
+@pytest.mark.parametrize("m,n,k,out_dtype", [(300, 320, 128, "bf16"), (1000, 512, 64, "f32"), (64, 32, 16, "f16")])
+@pytest.mark.parametrize("gated", [False, True])
+def test_column_sums_epilogue(gpu, m, n, k, out_dtype, gated):
+    """SB_EPI_COLSUM_OUT adds the column sums of the (gated) product to aux_out, which may already
+    hold a value; ragged last row blocks add nothing."""
+    in_dtype = "f16" if out_dtype == "f16" else "bf16"
+    a, b, c = operands(41, False, False, m, n, k, in_dtype)
+    sums0 = so.rng(42).normal(size=n).astype(np.float32)
+    sums = gpu.DeviceArray.from_numpy(sums0, "f32")
+    prod = so.matmul(False, False, 1.0, a, b, 0.0, None)
+    kw = dict(epilogue=("colsum_out",), aux_out=sums)
+    if gated:
+        gate = so.rng(43).integers(0, 2 ** 32, size=(m, n // 32), dtype=np.uint64).astype(np.uint32)
+        keep = np.unpackbits(gate.view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n).astype(bool)
+        prod = np.where(keep, prod, 0)
+        kw = dict(epilogue=("relu_grad_mask", "colsum_out"), aux_in=gpu.DeviceArray.from_numpy(gate.view(np.int32), "i32"),
+                  aux_out=sums)
+    got = run(gpu, False, False, 1.0, a, b, 0.0, c, in_dtype, out_dtype=out_dtype, **kw)
+    assert so.rel_frobenius(got, so.round_input(prod.astype(np.float32), out_dtype) if out_dtype != "f32" else prod) <= 3e-3
+    want = sums0 + prod.sum(axis=0, dtype=np.float64)
+    np.testing.assert_allclose(sums.numpy(), want, rtol=0, atol=2e-4 * np.sqrt(m * k))
+
+
+def test_column_sums_rejects_unsupported_combinations(gpu):
+    a, b, c = operands(44, False, True, 64, 64, 64, "bf16")
+    sums = gpu.DeviceArray.zeros((64,), "f32")
+    with pytest.raises(gpu.SpiralError):
+        run(gpu, False, True, 1.0, a, b, 0.0, c, "bf16", epilogue=("relu", "colsum_out"), aux_out=sums)
+    with pytest.raises(gpu.SpiralError):
+        run(gpu, False, True, 2.0, a, b, 0.0, c, "bf16", epilogue=("colsum_out",), aux_out=sums)
+    with pytest.raises(gpu.SpiralError):
+        run(gpu, False, True, 1.0, a, b, 0.0, c, "bf16", epilogue=("colsum_out",))
+
+
 @pytest.mark.parametrize("n", [3, 10, 16, 17, 32, 40])
 @pytest.mark.parametrize("heads", [("masked_softmax",), ("regret_matching",), ("masked_softmax", "regret_matching")])
 def test_fused_row_heads(gpu, n, heads):
