@@ -51,7 +51,9 @@ enum {
   SB_EPI_REGRET_MATCHING = 16,/* ml/primitives.spi:761-780, same mask */
   SB_EPI_ARGMAX = 32,         /* ml/primitives.spi:705-708; aux_out: int32[M], lowest index on ties */
   /* ReLU sign bits instead of the activation tile (N % 32 == 0): word
-   * [row, c] of a uint32[M, N/32] matrix, bit j = (value[row, 32c + j] > 0). */
+   * [c, row] of a uint32[N/32, M] matrix, bit j = (value[row, 32c + j] > 0).
+   * Stored column-block-major so that the 32 rows a warp finishes together
+   * are 32 consecutive words. */
   SB_EPI_RELU_MASK_OUT = 64,  /* with SB_EPI_RELU: also write the sign bits to aux_out */
   SB_EPI_RELU_GRAD_MASK = 128,/* gate by the sign bits in aux_in (the backward twin of the above) */
   /* Column sums of the finished values (after the sign-bit gate, before storage
@@ -153,6 +155,18 @@ int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream); 
  * SB_F16 -> 16-bit; SB_TF32 -> fp32 with the low 13 mantissa bits cleared,
  * round-to-nearest-even). */
 int sb_convert(const float* x, void* out, size_t n, int out_dtype, void* stream);
+/* Game-state encoder: compact records -> the dense network input x [rows,
+ * sum(widths) + n_dense] in storage type `dtype`.  Replaces the device-side
+ * serialisation of ml/models.spi:30-41 (zero the input tensor, then pickle each
+ * state into it) for states made of bounded ints (one-hot groups,
+ * corebase/pickler.spi:20-37) followed by real values.  fields: uint8 [rows,
+ * n_fields], value v < widths[j] sets feature offset_j + v of group j, any
+ * other value leaves the group zero; widths: HOST array, each in [1, 255],
+ * at most 64 fields and 2048 one-hot features; dense: [rows, n_dense] in
+ * `dtype`, copied unchanged behind the one-hot groups (may be NULL when
+ * n_dense == 0). */
+int sb_encode_states(const uint8_t* fields, int n_fields, const int* widths, const void* dense, int n_dense,
+                     void* x, long long rows, int dtype, void* stream);
 
 /* ---- dense policy network ---------------------------------------------------
  * A ReLU MLP `sizes[0] -> sizes[1] -> ... -> sizes[n_layers]` with a row head
@@ -175,7 +189,7 @@ int sb_mlp_param_offsets(int n_layers, const int* sizes, long long* offsets);
  * activations: host array of n_layers-1 device pointers, activations[i] =
  * [batch, sizes[i+1]] in the storage type (workspace, overwritten); params may
  * be NULL (no bias, as in the reference); relu_bits: NULL, or a host array of
- * n_layers-1 device pointers, relu_bits[i] = uint32 [batch, sizes[i+1]/32]
+ * n_layers-1 device pointers, relu_bits[i] = uint32 [sizes[i+1]/32, batch]
  * receiving the ReLU sign bits of hidden layer i (SB_EPI_RELU_MASK_OUT; used
  * when the width is a multiple of 32, so that backward need not re-read the
  * activations to gate its gradients); head: SB_EPI_MASKED_SOFTMAX |

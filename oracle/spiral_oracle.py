@@ -283,48 +283,78 @@ def mlp_weights(seed, sizes):
     return ws, bs
 
 
-def one_hot_field(gen, rows, width, allow_none=False):
-    """A one-hot field written the way corebase/pickler.spi:20-37 writes a bounded int."""
-    out = np.zeros((rows, width), dtype=np.float32)
-    idx = gen.integers(0, width + (1 if allow_none else 0), size=rows)
-    ok = idx < width
-    out[np.arange(rows)[ok], idx[ok]] = 1.0
-    return out
+def encode_states(fields, widths, dense=None):
+    """Dense network input from compact game states: field j (an integer in [0, widths[j]]) becomes
+    a one-hot group of widths[j] features, the value widths[j] (or anything above) meaning "none"
+    (all zeros), the way corebase/pickler.spi:20-37 serialises a bounded int into the input tensor
+    that ml/models.spi:30-41 zeroes first; `dense` [rows, n] values follow unchanged."""
+    fields = np.asarray(fields)
+    rows = fields.shape[0]
+    total = int(np.sum(widths))
+    n_dense = 0 if dense is None else dense.shape[1]
+    x = np.zeros((rows, total + n_dense), dtype=np.float32)
+    col = 0
+    r = np.arange(rows)
+    for j, w in enumerate(widths):
+        idx = fields[:, j].astype(np.int64)
+        ok = idx < w
+        x[r[ok], col + idx[ok]] = 1.0
+        col += w
+    if n_dense:
+        x[:, total:] = dense
+    return x
 
 
-def leduc_inputs(seed, batch):
-    """[batch, 32] {0,1} states: card one-hot(3) | community one-hot(4) | pot one-hot(14)
-    | raises-left one-hot(3) | 8 history bits; plus a mask with 2 or 3 legal actions of 3."""
+LEDUC_WIDTHS = (3, 4, 14, 3) + (1,) * 8
+HOLDEM_WIDTHS = (4, 13) * 7
+
+
+def leduc_states(seed, batch):
+    """Compact Leduc states: uint8 [batch, 12] = card(3) | community(4) | pot(14) | raises left(3) |
+    8 history bits (width-1 fields: 0 = set, 1 = clear); plus a mask with 2 or 3 legal actions of 3."""
     gen = rng(seed)
-    x = np.concatenate([
-        one_hot_field(gen, batch, 3), one_hot_field(gen, batch, 4), one_hot_field(gen, batch, 14),
-        one_hot_field(gen, batch, 3), (gen.random((batch, 8)) < 0.5).astype(np.float32)], axis=1)
+    cols = [gen.integers(0, w, size=batch) for w in LEDUC_WIDTHS[:4]]
+    bits = gen.random((batch, 8)) < 0.5
+    fields = np.concatenate([np.stack(cols, axis=1), np.where(bits, 0, 1)], axis=1).astype(np.uint8)
     mask = np.ones((batch, 3), dtype=np.uint8)
     drop = gen.integers(0, 4, size=batch)          # 3 = keep all three legal
     rows = np.arange(batch)[drop < 3]
     mask[rows, drop[drop < 3]] = 0
-    return x.astype(np.float32), mask
+    return fields, mask
 
 
-def holdem_inputs(seed, batch, features=512, actions=10):
-    """[batch, 512]: 7 card slots x (suit one-hot(4) + rank one-hot(13)) = 119 {0,1}
-    features (game/nl_hu_holdem/model_cem.spi:13-15,26-27; trailing board slots
-    empty according to a random street), then continuous U[0,1) stack/pot values;
-    plus a mask with 2..actions legal actions."""
+def leduc_inputs(seed, batch):
+    """[batch, 32] {0,1} states (the encoding of leduc_states) and the legal-action mask."""
+    fields, mask = leduc_states(seed, batch)
+    return encode_states(fields, LEDUC_WIDTHS), mask
+
+
+def holdem_states(seed, batch, features=512, actions=10):
+    """Compact Hold'em states: uint8 [batch, 14] = 7 card slots x (suit in [0,4], rank in [0,13]),
+    the top value meaning an empty slot (game/nl_hu_holdem/model_cem.spi:13-15,26-27; trailing
+    board slots are empty according to a random street); float32 [batch, features - 119]
+    continuous U[0,1) stack/pot values; and a mask with 2..actions legal actions."""
     gen = rng(seed)
-    x = np.zeros((batch, features), dtype=np.float32)
+    fields = np.zeros((batch, 14), dtype=np.uint8)
     street_cards = np.array([2, 5, 6, 7])[gen.integers(0, 4, size=batch)]
     for slot in range(7):
         live = street_cards > slot
-        suit = one_hot_field(gen, batch, 4)
-        rank = one_hot_field(gen, batch, 13)
-        x[:, slot * 17:slot * 17 + 4] = suit * live[:, None]
-        x[:, slot * 17 + 4:slot * 17 + 17] = rank * live[:, None]
-    x[:, 119:] = gen.random((batch, features - 119), dtype=np.float32)
+        suit = gen.integers(0, 4, size=batch)
+        rank = gen.integers(0, 13, size=batch)
+        fields[:, 2 * slot] = np.where(live, suit, 4)
+        fields[:, 2 * slot + 1] = np.where(live, rank, 13)
+    dense = gen.random((batch, features - 119), dtype=np.float32)
     mask = (gen.random((batch, actions)) < 0.6).astype(np.uint8)
     mask[:, 0] = 1
     mask[:, 1] = 1
-    return x, mask
+    return fields, dense, mask
+
+
+def holdem_inputs(seed, batch, features=512, actions=10):
+    """[batch, 512]: 119 {0,1} card features then the continuous values (the encoding of
+    holdem_states) and the legal-action mask."""
+    fields, dense, mask = holdem_states(seed, batch, features, actions)
+    return encode_states(fields, HOLDEM_WIDTHS, dense), mask
 
 
 def random_target(seed, mask):

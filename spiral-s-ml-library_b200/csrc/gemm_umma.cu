@@ -78,6 +78,7 @@ struct UmmaGemmParams {
   int pair;            // 1: CTA pairs (cta_group::2), 256-row tiles
   int coalesced;       // 1: 32-column chunks are transposed through shared memory for row-contiguous stores
   int tma_store;       // 1: and the finished boxes are written by TMA stores
+  int wide;            // 1: 16-bit output boxes span two chunks (64 columns, 128-byte rows)
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
 };
 
@@ -114,6 +115,41 @@ __device__ __forceinline__ __nv_bfloat16 float_to<__nv_bfloat16>(float v) {
 }
 template <>
 __device__ __forceinline__ __half float_to<__half>(float v) { return __float2half_rn(v); }
+
+// Two floats -> one 32-bit word of two 16-bit values (lo in the low half), round to nearest even,
+// optionally with the ReLU folded into the conversion.  The packed form is one ALU-class
+// instruction per pair; scalar conversions go through the quarter-rate conversion pipe, which an
+// epilogue of 32768 values per tile saturates.
+template <typename OutT, bool RELU>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16, false>(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16, true>(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half, false>(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half, true>(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<float, false>(float lo, float) { return __float_as_uint(lo); }
+template <>
+__device__ __forceinline__ uint32_t pack2<float, true>(float lo, float) { return __float_as_uint(lo); }
 
 __device__ __forceinline__ float round_tf32_rn(float v) {
   uint32_t u = __float_as_uint(v);
@@ -188,14 +224,13 @@ struct EpiShared {
   void* c;                  // output matrix (split partials follow each other)
   const void* aux;          // activation tile for the ReLU-gradient gate (SB_EPI_RELU_GRAD)
   const float* bias;
-  const uint32_t* gate_in;  // ReLU sign bits, one word per row and 32 columns (SB_EPI_RELU_GRAD_MASK)
+  const uint32_t* gate_in;  // ReLU sign bits, uint32 [N / 32, M]: one word per 32 columns and row (SB_EPI_RELU_GRAD_MASK)
   uint32_t* gate_out;       // where the forward pass records them (SB_EPI_RELU_MASK_OUT)
   float* colsum;            // column sums of the output are added here (SB_EPI_COLSUM_OUT)
   const CUtensorMap* tma_c; // non-null: finished boxes leave through TMA stores (32 x 32 element boxes over C)
   long long ldc;
   long long split_stride;
   int M, N;
-  int gate_ld;              // words per row of the sign-bit matrices = N / 32
   int block_n;
   float alpha, beta;
   int has_bias, relu, relu_grad, coalesced;
@@ -216,10 +251,10 @@ __shared__ __align__(16) float g_bias_spread[8][32];
 //   MODE = -1 : run-time flags, no second tile read;
 //   MODE = -2 : run-time flags plus the two features that read a second tile
 //               through the box (beta != 0, gate by the activation tile).
-template <typename OutT, bool ROUND_TF32, int MODE>
+template <typename OutT, bool ROUND_TF32, int MODE, bool WIDE = false>
 __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, uint32_t gate, int split,
                                                     int row0_warp, int col0, uint32_t sbuf,
-                                                    uint32_t bias_smem, int lane) {
+                                                    uint32_t bias_smem, int lane, int e) {
   constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
   constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
   constexpr int ROWS_PER_INST = 32 / PIECES;
@@ -249,6 +284,7 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
   if (has_bias) {
     // Lane j holds bias[col0 + j]; every lane needs all 32: spread them through
     // 128 bytes of shared memory and read them back as broadcasts.
+    if (WIDE && e == 1) __syncwarp();   // every lane has read the first chunk's values (no other warp-wide sync lies between)
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(bias_smem + 4u * (uint32_t)lane), "f"(bias_lane) : "memory");
     __syncwarp();
 #pragma unroll
@@ -270,28 +306,48 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
     load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(g_epi.aux), g_epi.ldc, row0_warp, g_epi.M, col0, g_epi.N,
                             sbuf, lane);
   const bool tma_out = !GENERAL && g_epi.tma_c != nullptr;
+  // A wide box (16-bit output) is 32 rows x 64 columns with 128-byte rows in the 128-byte swizzle:
+  // chunk e = 0 / 1 of a column pair fills pieces 4e .. 4e+3 of every row and the pair leaves as one
+  // store of full 128-byte row segments.  A narrow 16-bit box is 32 x 32 (64-byte swizzle).
+  constexpr bool wide = WIDE;
+  static_assert(!WIDE || (!GENERAL && sizeof(OutT) == 2), "wide boxes: 16-bit output through TMA stores only");
   if (tma_out) {
-    // The store that last read this box must have finished reading it.  A 16-bit box is 2 KB, so
-    // the warp's 4 KB slot holds two that alternate and only the store before last is awaited.
-    if (lane == 0) {
-      if (sizeof(OutT) == 2) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+    // The store that last read this box must have finished reading it.  A narrow 16-bit box is 2 KB,
+    // so the warp's 4 KB slot holds two that alternate and only the store before last is awaited.
+    if (!wide || e == 0) {
+      if (lane == 0) {
+        if (sizeof(OutT) == 2 && !wide) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+      }
+      __syncwarp();
     }
-    __syncwarp();
   }
+  const uint32_t wide_row = sbuf + (uint32_t)lane * 128u;
+  const uint32_t wide_key = (uint32_t)(4 * e) ^ ((uint32_t)lane & 7u);   // (4e + q) ^ key == (4e ^ key) ^ q for q < 4
 #pragma unroll
   for (int q = 0; q < PIECES; ++q) {
-    const uint32_t mine = sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
+    const uint32_t mine = wide ? wide_row + (((wide_key ^ (uint32_t)q) & 7u) << 4)
+                               : sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
     uint4 araw = make_uint4(0u, 0u, 0u, 0u);
     if (tile_gate) araw = ld_shared_v4(mine);     // this lane's piece of the activation tile
     const OutT* acte = reinterpret_cast<const OutT*>(&araw);
-    OutT outv[VEC];
+    // ReLU of a compile-time mode rides on the 16-bit conversion itself.
+    constexpr bool RELU_IN_CVT = sizeof(OutT) == 2 && MODE >= 0 && (MODE & 2) != 0;
+    float x[VEC];
 #pragma unroll
     for (int t = 0; t < VEC; ++t) {
-      float x = v[q * VEC + t];
-      if (relu) x = fmaxf(x, 0.f);
-      if (tile_gate) x = load_as_float<OutT>(acte + t) > 0.f ? x : 0.f;
-      if (ROUND_TF32) x = round_tf32_rn(x);
-      outv[t] = float_to<OutT>(x);
+      x[t] = v[q * VEC + t];
+      if (relu && !RELU_IN_CVT) x[t] = fmaxf(x[t], 0.f);
+      if (tile_gate) x[t] = load_as_float<OutT>(acte + t) > 0.f ? x[t] : 0.f;
+      if (ROUND_TF32) x[t] = round_tf32_rn(x[t]);
+    }
+    uint4 outw;
+    if (sizeof(OutT) == 2) {
+      outw.x = pack2<OutT, RELU_IN_CVT>(x[0], x[1]);
+      outw.y = pack2<OutT, RELU_IN_CVT>(x[2], x[3]);
+      outw.z = pack2<OutT, RELU_IN_CVT>(x[4 % VEC], x[5 % VEC]);
+      outw.w = pack2<OutT, RELU_IN_CVT>(x[6 % VEC], x[7 % VEC]);
+    } else {
+      outw = make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3]));
     }
     if (gate_out) {
       // Sign bits of this piece from the values just consumed (v is not needed afterwards).
@@ -300,16 +356,18 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
       for (int t = 0; t < VEC; ++t) s |= (__float_as_int(v[q * VEC + t]) > 0 ? 1u : 0u) << t;
       signs |= s << (q * VEC);
     }
-    st_shared_v4(mine, *reinterpret_cast<const uint4*>(outv));   // overwrites only what this lane just read
+    st_shared_v4(mine, outw);   // overwrites only what this lane just read
   }
   if (tma_out) {
     // The box already has the layout of a swizzled TMA box: one asynchronous bulk store writes
     // it (clipped at the matrix edges) without occupying the load/store pipe.
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(g_epi.tma_c, sbuf, col0, split * g_epi.M + row0_warp);
-      bulk_commit_group();
+    if (!wide || e == 1) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(g_epi.tma_c, sbuf, wide ? col0 - 32 : col0, split * g_epi.M + row0_warp);
+        bulk_commit_group();
+      }
     }
     return signs;
   }
@@ -365,39 +423,35 @@ __device__ __forceinline__ void chunk_colsum(float* v, int col0, int lane) {
   if (col0 + lane < g_epi.N) atomicAdd(g_epi.colsum + col0 + lane, v[0]);
 }
 
-// Per-thread stores of `w` (16 or 32) columns of one row: the fallback when C's
-// row pitch or base is not 16-byte aligned, and the 16-column tail chunk.
+// Per-thread stores of 16 columns of one row: the fallback when C's row pitch or base is not
+// 16-byte aligned, and the 16-column tail chunk.  The sign-bit and column-sum epilogues never come
+// here (they need N % 32 == 0 and an aligned C, which always takes the coalesced path).
 template <typename OutT, bool ROUND_TF32>
-__device__ __forceinline__ uint32_t direct_chunk(float* v, uint32_t gate, int w, long long row, int col0, int split) {
-  const int N = g_epi.N;
-  const int valid = min(w, N - col0);
-  uint32_t signs = 0u;
-  if (valid <= 0) return signs;
+__device__ __forceinline__ void direct_chunk16(float* v, long long row, int col0, int split) {
+  const int valid = min(16, g_epi.N - col0);
+  if (valid <= 0) return;
   const long long ldc = g_epi.ldc;
   OutT* crow = reinterpret_cast<OutT*>(g_epi.c) + (long long)split * g_epi.split_stride + row * ldc + col0;
   const OutT* arow = reinterpret_cast<const OutT*>(g_epi.aux) + row * ldc + col0;
   const float alpha = g_epi.alpha, beta = g_epi.beta;
   const float* bias = g_epi.has_bias ? g_epi.bias : nullptr;
-  const bool relu = g_epi.relu != 0, relu_grad = g_epi.relu_grad != 0, gate_in = g_epi.gate_in != nullptr;
+  const bool relu = g_epi.relu != 0, relu_grad = g_epi.relu_grad != 0;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {      // static indices keep v[] in registers
+  for (int j = 0; j < 16; ++j) {      // static indices keep v[] in registers
     if (j < valid) {
       float x = alpha * v[j];
       if (beta != 0.0f) x += beta * load_as_float<OutT>(crow + j);
       if (bias) x += __ldg(bias + col0 + j);
-      signs |= (x > 0.f ? 1u : 0u) << j;
-      if (gate_in) x = ((gate >> j) & 1u) ? x : 0.f;
       if (relu) x = fmaxf(x, 0.f);
       if (relu_grad) x = load_as_float<OutT>(arow + j) > 0.f ? x : 0.f;
       if (ROUND_TF32) x = round_tf32_rn(x);
       crow[j] = float_to<OutT>(x);
     }
   }
-  return signs;
 }
 
-// Chunks that cannot take the coalesced path, from chunk `c` on: per-thread stores.
-// A function of its own so that its registers do not add to the fast path's.
+// Chunks that cannot take the coalesced path, from chunk `c` on: per-thread stores, 16 columns at
+// a time.  A function of its own so that its registers do not add to the fast path's.
 template <typename OutT, bool ROUND_TF32>
 __device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0, int split, int c) {
   const int lane = threadIdx.x & 31;
@@ -406,16 +460,13 @@ __device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0
   const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
   for (; c < nchunks; c += UG_EPI_STRIDE) {
-    uint32_t raw[32];
     const int w = min(32, block_n - c * 32);
-    if (w == 32) tmem_ld32(t_row + (uint32_t)(c * 32), raw); else tmem_ld16(t_row + (uint32_t)(c * 32), raw);
-    tmem_ld_wait();
-    const int col0 = n0 + c * 32;
-    if (row_ok && col0 < g_epi.N) {
-      uint32_t gate = 0u;
-      if (g_epi.gate_in) gate = __ldg(g_epi.gate_in + row * g_epi.gate_ld + (col0 >> 5));
-      const uint32_t signs = direct_chunk<OutT, ROUND_TF32>(reinterpret_cast<float*>(raw), gate, w, row, col0, split);
-      if (g_epi.gate_out) g_epi.gate_out[row * g_epi.gate_ld + (col0 >> 5)] = signs;
+    for (int h = 0; h < w; h += 16) {
+      uint32_t raw[16];
+      tmem_ld16(t_row + (uint32_t)(c * 32 + h), raw);
+      tmem_ld_wait();
+      const int col0 = n0 + c * 32 + h;
+      if (row_ok && col0 < g_epi.N) direct_chunk16<OutT, ROUND_TF32>(reinterpret_cast<float*>(raw), row, col0, split);
     }
   }
 }
@@ -444,8 +495,10 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
   const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
   const int nfull = g_epi.coalesced ? (block_n >> 5) : 0;     // chunks that take the coalesced path
-  // This row's words of the sign-bit matrices.
-  const long long gate_row = (long long)(row0_warp + lane) * g_epi.gate_ld;
+  // The sign-bit matrices are stored [N / 32, M]: the 32 rows of a warp are 32 consecutive words,
+  // so a chunk's words move as one 128-byte transaction.
+  const long long gate_row = (long long)(row0_warp + lane);
+  const long long gate_pitch = g_epi.M;
 
   auto fetch = [&](int c, float& bias_lane, uint32_t& gate) {
     bias_lane = 0.f;
@@ -453,7 +506,7 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
     const int col0 = n0 + c * 32;
     if (c < nchunks) {
       if (has_bias && col0 + lane < N) bias_lane = __ldg(g_epi.bias + col0 + lane);
-      if (want_gate_in && row_ok && col0 < N) gate = __ldg(g_epi.gate_in + gate_row + (col0 >> 5));
+      if (want_gate_in && row_ok && col0 < N) gate = __ldg(g_epi.gate_in + (col0 >> 5) * gate_pitch + gate_row);
     }
   };
 
@@ -475,8 +528,8 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
       const uint32_t box = sbuf + ((MODE != -2 && sizeof(OutT) == 2 && g_epi.tma_c) ? box_sel : 0u);
       box_sel ^= 2048u;
       const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
-                                                                     split, row0_warp, col0, box, bias_smem, lane);
-      if (want_gate_out && row_ok) g_epi.gate_out[gate_row + (col0 >> 5)] = signs;
+                                                                     split, row0_warp, col0, box, bias_smem, lane, 0);
+      if (want_gate_out && row_ok) g_epi.gate_out[(col0 >> 5) * gate_pitch + gate_row] = signs;
       if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_a), col0, lane);
     }
     bias_cur = bias_nxt;
@@ -485,6 +538,81 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
   // What is left for this warp: a 16-column tail chunk, or every chunk when C
   // cannot take row-contiguous 16-byte stores.
   if (c < nchunks) epilogue_rest<OutT, ROUND_TF32>(t_row, row0_warp, n0, split, c);
+  return true;
+}
+
+// The same for a 16-bit output whose tile is a whole number of 64-column chunk pairs and leaves
+// through TMA stores: the two warps of a quadrant take alternate PAIRS of adjacent chunks
+// (with two warps per quadrant, warp 0: chunks 0 1 4 5 ..., warp 1: 2 3 6 7 ...).  Both accumulator chunks of a pair are
+// requested from tensor memory at once, both halves go into one 32-row x 64-column box with
+// 128-byte rows, and one store (one proxy fence, one wait for the box to be free) serves the pair.
+template <typename OutT, int MODE>
+__device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, int n0, int split, uint32_t bar_full,
+                                                uint32_t parity) {
+  static_assert(sizeof(OutT) == 2 && MODE != -2, "wide boxes: 16-bit output through TMA stores only");
+  const int lane = threadIdx.x & 31;
+  const int ewarp = (int)(threadIdx.x >> 5) - 2;
+  const int half = ewarp >> 2;
+  const uint32_t sbuf = g_epi.box_base + (uint32_t)ewarp * 4096u;
+  const uint32_t bias_smem = smem_u32(&g_bias_spread[ewarp][0]);
+  const bool has_bias = MODE >= 0 ? (MODE & 1) != 0 : g_epi.has_bias != 0;
+  const bool want_gate_in = MODE >= 0 ? (MODE & 8) != 0 : g_epi.gate_in != nullptr;
+  const bool want_gate_out = MODE >= 0 ? (MODE & 4) != 0 : g_epi.gate_out != nullptr;
+  const int N = g_epi.N;
+  const bool row_ok = row0_warp + lane < g_epi.M;
+  const bool rows_live = row0_warp < g_epi.M;
+  const int nchunks = g_epi.block_n >> 5;     // even
+  const long long gate_row = (long long)(row0_warp + lane);
+  const long long gate_pitch = g_epi.M;
+
+  auto fetch = [&](int c, float& bias_lane, uint32_t& gate) {
+    bias_lane = 0.f;
+    gate = 0u;
+    const int col0 = n0 + c * 32;
+    if (c < nchunks) {
+      if (has_bias && col0 + lane < N) bias_lane = __ldg(g_epi.bias + col0 + lane);
+      if (want_gate_in && row_ok && col0 < N) gate = __ldg(g_epi.gate_in + (col0 >> 5) * gate_pitch + gate_row);
+    }
+  };
+
+  int c = 2 * half;
+  float bias_a, bias_b, bias_na, bias_nb;
+  uint32_t gate_a, gate_b, gate_na, gate_nb;
+  fetch(c, bias_a, gate_a);
+  fetch(c + 1, bias_b, gate_b);
+  if (!mbar_wait(bar_full, parity, &g_abort_flag, SB_SITE_EPI_TMEM_FULL)) return false;
+  tc_fence_after_sync();
+
+  // With the column sums (a 32-register butterfly per chunk) or with run-time flags both chunks do
+  // not fit in the register budget at once: those modes read the second chunk after the first is
+  // finished.
+  constexpr bool BOTH_AT_ONCE = MODE >= 0 && (MODE & 16) == 0;
+  uint32_t raw_a[32], raw_b[32];
+  for (; c < nchunks; c += 2 * UG_EPI_STRIDE) {
+    tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
+    if (BOTH_AT_ONCE) tmem_ld32(t_row + (uint32_t)(c * 32 + 32), raw_b);
+    fetch(c + 2 * UG_EPI_STRIDE, bias_na, gate_na);      // the next pair's, in flight meanwhile
+    fetch(c + 2 * UG_EPI_STRIDE + 1, bias_nb, gate_nb);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    // A second chunk beyond N is all zeros and the store clips it; it is still written into the box.
+    if (rows_live && col0 < N) {
+      const uint32_t sa = coalesced_chunk<OutT, false, MODE, true>(reinterpret_cast<float*>(raw_a), bias_a, gate_a, split,
+                                                                   row0_warp, col0, sbuf, bias_smem, lane, 0);
+      if (want_gate_out && row_ok) g_epi.gate_out[(col0 >> 5) * gate_pitch + gate_row] = sa;
+      if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_a), col0, lane);
+      if (!BOTH_AT_ONCE) {
+        tmem_ld32(t_row + (uint32_t)(c * 32 + 32), raw_b);
+        tmem_ld_wait();
+      }
+      const uint32_t sb = coalesced_chunk<OutT, false, MODE, true>(reinterpret_cast<float*>(raw_b), bias_b, gate_b, split,
+                                                                   row0_warp, col0 + 32, sbuf, bias_smem, lane, 1);
+      if (want_gate_out && row_ok && col0 + 32 < N) g_epi.gate_out[((col0 >> 5) + 1) * gate_pitch + gate_row] = sb;
+      if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_b), col0 + 32, lane);
+    }
+    bias_a = bias_na; bias_b = bias_nb;
+    gate_a = gate_na; gate_b = gate_nb;
+  }
   return true;
 }
 
@@ -644,7 +772,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     g_epi.tma_c = p.tma_store ? &tmap_c : nullptr;
     g_epi.ldc = p.ldc;
     g_epi.split_stride = p.split_stride;
-    g_epi.M = p.M; g_epi.N = p.N; g_epi.gate_ld = p.N >> 5; g_epi.block_n = p.block_n;
+    g_epi.M = p.M; g_epi.N = p.N; g_epi.block_n = p.block_n;
     g_epi.alpha = p.alpha; g_epi.beta = p.beta;
     g_epi.has_bias = (p.epi & SB_EPI_BIAS) ? 1 : 0; g_epi.relu = (p.epi & SB_EPI_RELU) ? 1 : 0;
     g_epi.relu_grad = (p.epi & SB_EPI_RELU_GRAD) ? 1 : 0; g_epi.coalesced = p.coalesced;
@@ -849,12 +977,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int n0 = n_blk * p.block_n;
         bool ok;
 #define SB_EPI_CALL(T, R, G) epilogue_tile<T, R, G>(t_row, row0_warp, n0, split, full_bar, acc_phase)
+#define SB_EPI_WIDE(T, G) epilogue_tile_wide<T, (G) == -2 ? -1 : (G)>(t_row, row0_warp, n0, split, full_bar, acc_phase)
 #define SB_EPI_BY_TYPE(G)                                                        \
   do {                                                                           \
     if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, G);                \
     else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, G);           \
-    else if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, G);  \
-    else ok = SB_EPI_CALL(__half, false, G);                                     \
+    else if (p.out_dtype == SB_BF16)                                             \
+      ok = (p.wide && (G) != -2) ? SB_EPI_WIDE(__nv_bfloat16, G) : SB_EPI_CALL(__nv_bfloat16, false, G); \
+    else ok = (p.wide && (G) != -2) ? SB_EPI_WIDE(__half, G) : SB_EPI_CALL(__half, false, G);            \
   } while (0)
         switch (epi_mode) {
           case 0: SB_EPI_BY_TYPE(0); break;        // plain: standalone GEMMs, wgrad partials
@@ -867,6 +997,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           default: SB_EPI_BY_TYPE(-1); break;
         }
 #undef SB_EPI_BY_TYPE
+#undef SB_EPI_WIDE
 #undef SB_EPI_CALL
         if (!ok) break;
       }
@@ -1147,6 +1278,9 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
                  (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
                  (!(epi & SB_EPI_RELU_GRAD) || (reinterpret_cast<uintptr_t>(aux_in) & 15) == 0)) ? 1 : 0;
 
+  if (!p.coalesced && (epi & (EPI_GATE_MASK | SB_EPI_COLSUM_OUT)))
+    return sb_fail(SB_ERR_MISALIGNED, "the sign-bit and column-sum epilogues need a 16-byte aligned C");
+
   // TMA stores of the finished boxes: no second tile is read (beta, activation gate), and with
   // split-K -- the partials form one [splits * M, N] tensor -- no 32-row box may straddle two partials.
   CUtensorMap tc;
@@ -1154,7 +1288,9 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.tma_store = 0;
   if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || M % 32 == 0)) {
     const int cdt = es_out == 4 ? SB_F32 : out_dtype;
-    rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, 32, es_out == 4 ? SWZ_128 : SWZ_64);
+    p.wide = (es_out == 2 && p.block_n % 64 == 0) ? 1 : 0;
+    rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, p.wide ? 64 : 32,
+                      (es_out == 4 || p.wide) ? SWZ_128 : SWZ_64);
     if (rc != SB_OK) return rc;
     p.tma_store = 1;
   }

@@ -155,6 +155,67 @@ __global__ void convert_kernel(const float* __restrict__ x, void* __restrict__ o
   }
 }
 
+// Game-state encoder.  The reference zeroes the input tensor and pickles each
+// game state into it on the device (ml/models.spi:30-41): a bounded int becomes
+// a one-hot group (corebase/pickler.spi:20-37).  Here the host ships compact
+// records -- one byte per one-hot field plus the dense values -- and this kernel
+// writes the dense network input [rows, features] in the storage type: field j
+// with value v < widths[j] sets feature (offset_j + v), any other value leaves
+// the group zero; `dense` [rows, n_dense] follows unchanged.
+constexpr int ENC_MAX_FIELDS = 64;
+constexpr int ENC_MAX_ONEHOT = 2048;
+struct EncodeLayout {
+  int n_fields;
+  int onehot;                       // sum of widths
+  unsigned char widths[ENC_MAX_FIELDS];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+encode_states_kernel(const uint8_t* __restrict__ fields, const T* __restrict__ dense, T* __restrict__ x,
+                     long long rows, int n_dense, EncodeLayout lay) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ unsigned char field_of[ENC_MAX_ONEHOT];   // which field owns a one-hot feature
+  __shared__ unsigned char pos_of[ENC_MAX_ONEHOT];     // and which value of the field sets it
+  for (int j = 0, col = 0; j < lay.n_fields; ++j) {
+    const int w = lay.widths[j];
+    for (int t = threadIdx.x; t < w; t += blockDim.x) {
+      field_of[col + t] = (unsigned char)j;
+      pos_of[col + t] = (unsigned char)t;
+    }
+    col += w;
+  }
+  __syncthreads();
+  const int features = lay.onehot + n_dense;
+  const int pieces = (features + VEC - 1) / VEC;           // 16-byte pieces per output row
+  const long long total = rows * pieces;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  const bool vec_ok = features % VEC == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const long long r = i / pieces;
+    const int f0 = (int)(i - r * pieces) * VEC;
+    T out[VEC];
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) {
+      const int f = f0 + t;
+      T v = (T)0.f;
+      if (f < lay.onehot) {
+        if (fields[r * lay.n_fields + field_of[f]] == pos_of[f]) v = (T)1.f;
+      } else if (f < features) {
+        v = dense[r * n_dense + (f - lay.onehot)];
+      }
+      out[t] = v;
+    }
+    if (vec_ok) {
+      *reinterpret_cast<uint4*>(x + r * features + f0) = *reinterpret_cast<const uint4*>(out);
+    } else {
+#pragma unroll
+      for (int t = 0; t < VEC; ++t)
+        if (f0 + t < features) x[r * features + f0 + t] = out[t];
+    }
+  }
+}
+
 int grid_for(long long work_items, int per_block) {
   long long b = (work_items + per_block - 1) / per_block;
   if (b < 1) b = 1;
@@ -226,6 +287,39 @@ int sb_convert(const float* x, void* out, size_t n, int out_dtype, void* stream)
   if (out_dtype != SB_BF16 && out_dtype != SB_F16 && out_dtype != SB_TF32 && out_dtype != SB_F32)
     return sb_fail(SB_ERR_BAD_ARG, "sb_convert: unknown output dtype %d", out_dtype);
   convert_kernel<<<grid_for((long long)n, 256), 256, 0, (cudaStream_t)stream>>>(x, out, n, out_dtype);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_encode_states(const uint8_t* fields, int n_fields, const int* widths, const void* dense, int n_dense,
+                     void* x, long long rows, int dtype, void* stream) {
+  if (rows < 0 || n_fields < 0 || n_dense < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_encode_states: negative size");
+  if (n_fields > ENC_MAX_FIELDS) return sb_fail(SB_ERR_TOO_LARGE, "sb_encode_states: at most %d one-hot fields", ENC_MAX_FIELDS);
+  if (n_fields > 0 && !widths) return sb_fail(SB_ERR_BAD_ARG, "sb_encode_states: widths is null");
+  if (dtype != SB_F32 && dtype != SB_TF32 && dtype != SB_BF16 && dtype != SB_F16)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_encode_states: unknown storage dtype %d", dtype);
+  EncodeLayout lay;
+  memset(&lay, 0, sizeof(lay));
+  lay.n_fields = n_fields;
+  for (int j = 0; j < n_fields; ++j) {
+    if (widths[j] < 1 || widths[j] > 255) return sb_fail(SB_ERR_BAD_ARG, "sb_encode_states: widths[%d] = %d is outside [1, 255]", j, widths[j]);
+    lay.widths[j] = (unsigned char)widths[j];
+    lay.onehot += widths[j];
+  }
+  if (lay.onehot > ENC_MAX_ONEHOT) return sb_fail(SB_ERR_TOO_LARGE, "sb_encode_states: at most %d one-hot features", ENC_MAX_ONEHOT);
+  if (rows == 0 || lay.onehot + n_dense == 0) return SB_OK;
+  if (!x || (n_fields > 0 && !fields) || (n_dense > 0 && !dense)) return sb_fail(SB_ERR_BAD_ARG, "sb_encode_states: null pointer");
+  const int es = sb_dtype_size(dtype);
+  const long long pieces = (long long)rows * ((lay.onehot + n_dense + 16 / es - 1) / (16 / es));
+  const int grid = grid_for(pieces, 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SB_BF16)
+    encode_states_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(fields, (const __nv_bfloat16*)dense, (__nv_bfloat16*)x, rows, n_dense, lay);
+  else if (dtype == SB_F16)
+    encode_states_kernel<__half><<<grid, 256, 0, s>>>(fields, (const __half*)dense, (__half*)x, rows, n_dense, lay);
+  else
+    encode_states_kernel<float><<<grid, 256, 0, s>>>(fields, (const float*)dense, (float*)x, rows, n_dense, lay);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;

@@ -80,6 +80,7 @@ SIGNATURES = {
     "sb_row_argmax": (_I, [_P, _P, _I, _I, _P]),
     "sb_row_ln_l2": (_I, [_P, _P, _I, _I, _P]),
     "sb_convert": (_I, [_P, _P, _Z, _I, _P]),
+    "sb_encode_states": (_I, [_P, _I, _IP, _P, _I, _P, ctypes.c_longlong, _I, _P]),
     "sb_mlp_param_offsets": (_I, [_I, _IP, POINTER(ctypes.c_longlong)]),
     "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),

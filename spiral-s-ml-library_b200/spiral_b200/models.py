@@ -60,7 +60,7 @@ class PolicyMLP:
         self.relu_bits = []
         self._bits_c = None
         if self.training and all(w % 32 == 0 for w in self.sizes[1:-1]) and self.n_layers > 1:
-            self.relu_bits = [DeviceArray((self.batch, self.sizes[i + 1] // 32), "i32")
+            self.relu_bits = [DeviceArray((self.sizes[i + 1] // 32, self.batch), "i32")
                               for i in range(self.n_layers - 1)]
             self._bits_c = (ctypes.c_void_p * (self.n_layers - 1))(*[b.ptr for b in self.relu_bits])
         self.grads = None

@@ -60,6 +60,31 @@ def ln_l2(x, out=None, stream=None):
     return out
 
 
+def encode_states(fields, widths, dense, out, stream=None):
+    """Compact game states -> the dense network input ``out`` [rows, sum(widths) + n_dense].
+
+    ``fields``: uint8 device array [rows, len(widths)], value v < widths[j] sets feature v of the
+    j-th one-hot group, any other value leaves the group zero (the bounded-int pickler of
+    corebase/pickler.spi:20-37, run on the device as ml/models.spi:30-41 does); ``dense``: device
+    array [rows, n_dense] in the dtype of ``out`` (or None), copied behind the one-hot groups.
+    """
+    import ctypes
+    rows = int(out.shape[0])
+    widths = [int(w) for w in widths]
+    n_dense = 0 if dense is None else int(dense.shape[1])
+    if int(out.shape[1]) != sum(widths) + n_dense:
+        raise ValueError("encode_states: out has %d features, the layout describes %d"
+                         % (out.shape[1], sum(widths) + n_dense))
+    if tuple(fields.shape) != (rows, len(widths)):
+        raise ValueError("encode_states: fields must be [%d, %d], got %s" % (rows, len(widths), tuple(fields.shape)))
+    if dense is not None and (int(dense.shape[0]) != rows or dense.dtype != out.dtype):
+        raise ValueError("encode_states: dense must be [%d, n] in the dtype of out" % rows)
+    w_c = (ctypes.c_int * max(1, len(widths)))(*widths)
+    _lib.call("sb_encode_states", device_ptr(fields), len(widths), w_c, device_ptr(dense), n_dense,
+              device_ptr(out), rows, _lib.DTYPE_CODES[out.dtype], stream_ptr(stream))
+    return out
+
+
 def convert(x, out, stream=None):
     """fp32 device array -> `out` (bf16 / f16 / tf32-rounded fp32 / fp32)."""
     _lib.call("sb_convert", device_ptr(x), device_ptr(out), int(x.size), _lib.DTYPE_CODES[out.dtype],

@@ -80,3 +80,37 @@ def test_convert_rounding_matches_host(gpu):
         out = gpu.DeviceArray(x.shape, tag)
         got = gpu.primitives.convert(dx, out).numpy()
         np.testing.assert_array_equal(got, rounder(x))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+def test_encode_states_holdem_and_leduc_bit_exact(gpu, dtype):
+    """The device encoder writes exactly the dense input the oracle builds from the same compact
+    states: one-hot groups with "none" values, then the dense columns unchanged (bit-exact)."""
+    P = gpu.primitives
+    fields, dense, _ = so.holdem_states(7, 3001)            # ragged row count
+    dense = so.round_input(dense, dtype) if dtype != "f32" else dense
+    want = so.encode_states(fields, so.HOLDEM_WIDTHS, dense)
+    out = gpu.DeviceArray((3001, 512), dtype)
+    P.encode_states(_dev(gpu, fields), so.HOLDEM_WIDTHS, _dev(gpu, dense, dtype), out)
+    np.testing.assert_array_equal(out.numpy(), want)
+    assert np.array_equal(want, so.holdem_inputs(7, 3001)[0]) or dtype != "f32"
+    fields, _ = so.leduc_states(8, 1000)
+    out = gpu.DeviceArray((1000, 32), dtype)
+    P.encode_states(_dev(gpu, fields), so.LEDUC_WIDTHS, None, out)
+    np.testing.assert_array_equal(out.numpy(), so.leduc_inputs(8, 1000)[0])
+
+
+def test_encode_states_edge_cases(gpu):
+    P = gpu.primitives
+    # a row width that is not a multiple of the 16-byte store (scalar path), values above the width
+    fields = np.array([[0, 5], [2, 1], [3, 0], [255, 2]], dtype=np.uint8)
+    dense = so.rng(3).random((4, 3), dtype=np.float32)
+    out = gpu.DeviceArray((4, 3 + 3 + 3), "f32")
+    P.encode_states(_dev(gpu, fields), (3, 3), _dev(gpu, dense), out)
+    np.testing.assert_array_equal(out.numpy(), so.encode_states(fields, (3, 3), dense))
+    # no rows: nothing is launched
+    P.encode_states(gpu.DeviceArray((0, 2), "u8"), (3, 3), gpu.DeviceArray((0, 3), "f32"), gpu.DeviceArray((0, 9), "f32"))
+    with pytest.raises(ValueError):
+        P.encode_states(_dev(gpu, fields), (3, 3), _dev(gpu, dense), gpu.DeviceArray((4, 10), "f32"))
+    with pytest.raises(gpu.SpiralError):
+        P.encode_states(_dev(gpu, fields), (3, 300), None, gpu.DeviceArray((4, 303), "f32"))

@@ -136,21 +136,32 @@ def test_relu_grad_epilogue(gpu):
     assert np.all(got[act <= 0] == 0)
 
 
+def bits_to_bool(words, m, n):
+    """uint32 [n/32, m] sign words (bit j of word [c, row] = column 32c+j of that row) -> bool [m, n]."""
+    by_row = np.ascontiguousarray(words.view(np.uint32).reshape(n // 32, m).T)
+    return np.unpackbits(by_row.view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n).astype(bool)
+
+
+def bool_to_bits(keep):
+    m, n = keep.shape
+    by_row = np.packbits(keep.reshape(m, n // 32, 32), axis=-1, bitorder="little").view(np.uint32).reshape(m, n // 32)
+    return np.ascontiguousarray(by_row.T)
+
+
 def test_relu_sign_bits_forward_and_backward_gate(gpu):
-    """SB_EPI_RELU_MASK_OUT records bit j of word [row, c] = (value[row, 32c+j] > 0); gating a second
+    """SB_EPI_RELU_MASK_OUT records bit j of word [c, row] = (value[row, 32c+j] > 0); gating a second
     GEMM by those bits equals gating by the activation tile itself."""
     m, n, k = 300, 320, 128
     a, b, c = operands(31, False, True, m, n, k, "bf16")
-    bits = gpu.DeviceArray.zeros((m, n // 32), "i32")
+    bits = gpu.DeviceArray.zeros((n // 32, m), "i32")
     act = run(gpu, False, True, 1.0, a, b, 0.0, c, "bf16", out_dtype="bf16", epilogue=("relu", "relu_mask_out"),
               aux_out=bits)
     pre = so.matmul(False, True, 1.0, a, b, 0.0, None)
-    want_bits = np.packbits((pre > 0).reshape(m, n // 32, 32), axis=-1, bitorder="little").view(np.uint32).reshape(m, n // 32)
-    got_bits = bits.numpy().view(np.uint32)
+    got = bits_to_bool(bits.numpy(), m, n)
     decided = np.abs(pre) > 1e-3                       # leave out values within rounding of zero
-    diff = np.unpackbits((got_bits ^ want_bits).view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n)
-    assert not (diff.astype(bool) & decided).any()
-    np.testing.assert_array_equal(act > 0, np.unpackbits(got_bits.view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n).astype(bool))
+    assert not ((got != (pre > 0)) & decided).any()
+    np.testing.assert_array_equal(act > 0, got)
+    np.testing.assert_array_equal(bool_to_bits(got), bits.numpy().view(np.uint32).reshape(n // 32, m))
     a2, b2, c2 = operands(32, False, False, m, n, 64, "bf16")
     by_bits = run(gpu, False, False, 1.0, a2, b2, 0.0, c2, "bf16", out_dtype="bf16", epilogue=("relu_grad_mask",), aux_in=bits)
     by_tile = run(gpu, False, False, 1.0, a2, b2, 0.0, c2, "bf16", out_dtype="bf16", epilogue=("relu_grad",),
@@ -170,8 +181,8 @@ def test_column_sums_epilogue(gpu, m, n, k, out_dtype, gated):
     prod = so.matmul(False, False, 1.0, a, b, 0.0, None)
     kw = dict(epilogue=("colsum_out",), aux_out=sums)
     if gated:
-        gate = so.rng(43).integers(0, 2 ** 32, size=(m, n // 32), dtype=np.uint64).astype(np.uint32)
-        keep = np.unpackbits(gate.view(np.uint8).reshape(m, -1), axis=1, bitorder="little").reshape(m, n).astype(bool)
+        gate = so.rng(43).integers(0, 2 ** 32, size=(n // 32, m), dtype=np.uint64).astype(np.uint32)
+        keep = bits_to_bool(gate, m, n)
         prod = np.where(keep, prod, 0)
         kw = dict(epilogue=("relu_grad_mask", "colsum_out"), aux_in=gpu.DeviceArray.from_numpy(gate.view(np.int32), "i32"),
                   aux_out=sums)

@@ -113,3 +113,24 @@ def test_train_step_gradient_matches_finite_difference():
         wm[li][i, j] -= eps
         lm = so.cross_entropy_loss(so.mlp_forward(x, wm, bs, mask), tgt, mask)
         assert abs((lp - lm) / (2 * eps) - grads[li][0][i, j]) < 2e-3
+
+
+def test_state_encoder_matches_the_dense_generators():
+    """encode_states follows the bounded-int pickler (corebase/pickler.spi:20-37): one feature set per
+    field, none for the out-of-range value; the dense generators are its image of the compact ones."""
+    fields, dense, mask = so.holdem_states(11, 257)
+    x, mask2 = so.holdem_inputs(11, 257)
+    assert x.shape == (257, 512) and np.array_equal(mask, mask2)
+    cards = x[:, :119].reshape(257, 7, 17)
+    live = fields[:, 0::2] < 4
+    assert np.array_equal(cards[:, :, :4].sum(axis=2) == 1, live)        # suit groups
+    assert np.array_equal(cards[:, :, 4:].sum(axis=2) == 1, live)        # rank groups
+    assert np.array_equal(np.argmax(cards[:, :, 4:], axis=2)[live], fields[:, 1::2][live])
+    assert np.array_equal(x[:, 119:], dense)
+    assert set(np.sum(live, axis=1)) <= {2, 5, 6, 7}
+    f2, m2 = so.leduc_states(12, 100)
+    x2, _ = so.leduc_inputs(12, 100)
+    assert x2.shape == (100, 32) and np.all(x2[:, :24].reshape(100, -1).sum(axis=1) == 4)
+    assert np.array_equal(x2[:, 24:], (f2[:, 4:] == 0).astype(np.float32))
+    tiny = so.encode_states(np.array([[1, 2], [3, 0]], np.uint8), (3, 2), np.array([[0.5], [0.25]], np.float32))
+    assert np.array_equal(tiny, np.array([[0, 1, 0, 0, 0, 0.5], [0, 0, 0, 1, 0, 0.25]], np.float32))
