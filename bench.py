@@ -337,7 +337,8 @@ def run_ours(args, rank, world, local_rank):
     dense_store = to_store(denseh) if denseh is not None else None
 
     grads = None
-    if training and world > 1:
+    peer_mode = training and world > 1 and args.update == "peer"
+    if training and world > 1 and not peer_mode:
         n_params = sb.param_offsets(sizes)[-1]
         grads = torch.zeros(n_params, dtype=torch.float32, device="cuda")
     head = ("masked_softmax",) if training else ("masked_softmax", "regret_matching", "argmax")
@@ -366,8 +367,17 @@ def run_ours(args, rank, world, local_rank):
         # one all-reduce at the end on 2 and 8 B200s (the persistent GEMMs leave NCCL no free SM, and
         # five small messages cost more than one of 14.7 MB), so it is off by default.
         seg = lambda g, b, e: dist.all_reduce(g[b:e], async_op=True)
+    peer = None
+    if peer_mode:
+        # The library's own reduce + update + redistribute kernel over peer memory; torch.distributed
+        # only carries the 64-byte memory handles at set-up.
+        def exchange(payload):
+            out = [None] * world
+            dist.all_gather_object(out, payload)
+            return out
+        peer = sb.PeerUpdate(net, world, rank, exchange)
     dp = sb.DataParallel(net, gbatch, all_reduce=(lambda g: dist.all_reduce(g)) if dist is not None else None,
-                         world_size=world, rank=rank, all_reduce_segment=seg)
+                         world_size=world, rank=rank, all_reduce_segment=seg, peer_update=peer)
 
     def step():
         if training:
@@ -477,6 +487,11 @@ def run_ours(args, rank, world, local_rank):
     status = sb.device_status()
     if status != (0, 0):
         raise SystemExit("device-side wait expired during the benchmark: %s" % (status,))
+    if peer is not None:
+        if peer.status() != 0:
+            raise SystemExit("a peer-update barrier gave up waiting: status 0x%x" % peer.status())
+        barrier_sync()
+        peer.close()
 
     if rank != 0:
         if dist is not None:
@@ -521,6 +536,7 @@ def run_ours(args, rank, world, local_rank):
         "dtype": in_dtype, "data": "synthetic",
         "config": {"workload": workload, "layers": sizes, "global_batch": gbatch, "batch_per_gpu": batch,
                    "parallelism": "dp%d" % world, "lr": LR,
+                   "gradient_exchange": ("peer-memory reduce+update kernel" if peer_mode else "nccl all-reduce") if (training and world > 1) else "none",
                    "l2": l2_note},
         "roofline": {"bound": "tensor", "kernel": "mlp_fused_kernel" if fused else "umma_gemm_kernel",
                      "achieved": round(achieved, 1), "peak": peak,
@@ -597,6 +613,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--overlap", action="store_true", help="per-layer asynchronous all-reduce instead of one at the end")
+    ap.add_argument("--update", choices=("peer", "nccl"), default="peer",
+                    help="N > 1 training: the library's reduce+update kernel over peer memory, or NCCL all-reduce + SGD")
     ap.add_argument("--layerwise", action="store_true", help="narrow-net inference through one GEMM per layer")
     ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
                     help="run a few launches of one GEMM shape (for ncu) and exit")

@@ -267,6 +267,46 @@ int sb_mlp_train_step(int n_layers, const int* sizes, int batch, int in_dtype, c
                       const float* target, float* probs, float* grads, int with_bias, float lr,
                       void* scratch, size_t scratch_bytes, float* loss, void* stream);
 
+/* ---- data-parallel update over peer memory ---------------------------------
+ * No reference counterpart (the reference is single-device, corecuda/base.spi:7);
+ * follows the benchmark's data-parallel training configurations.  One process
+ * per GPU.  Each rank exports its gradient, master-parameter, compute-copy and
+ * flag buffers (sb_ipc_export), sends the 64-byte handles to its peers by any
+ * host channel, and opens theirs (sb_ipc_open): the tables passed below are HOST
+ * arrays of world_size DEVICE pointers, entry [rank] being the rank's own
+ * buffer.  Buffers come from sb_malloc / cudaMalloc (whole allocations). */
+int sb_ipc_export(void* dev_ptr, void* handle64);
+int sb_ipc_open(const void* handle64, void** dev_ptr);
+int sb_ipc_close(void* dev_ptr);
+/* Size of one rank's flag block; the caller zero-fills it once before the first step. */
+int sb_dp_flag_bytes(void);
+/* [begin, end) of the parameter slice rank `rank` reduces and updates (n % 4 == 0). */
+int sb_dp_slice(long long n, int world_size, int rank, long long* begin_end);
+/* Gradient reduction + SGD + redistribution in one kernel: waits until every
+ * rank has reached this call (flag barrier), then for this rank's slice
+ *   g = sum over ranks (in rank order) of grads[r][i];  w = params[rank][i] - lr * g;
+ *   params[r][i] = w and w_compute[r][i] = round(w) for every rank r,
+ * and closes with a second barrier, after which every rank holds the complete
+ * new weights.  Replaces all-reduce + sb_sgd_update.  `epoch` must be odd and
+ * grow by 2 per call, the same on every rank (the call uses epoch and epoch+1).
+ * mode: SB_DP_REPLICATED as above; SB_DP_SHARDED_MASTER stores the fp32 master
+ * value only on the owner of a slice, except inside the `replicate` ranges
+ * (HOST array of n_replicate [begin, end) element pairs in whole 4-element
+ * vectors -- the biases, which the forward pass reads in fp32): a third of the
+ * bytes leave the GPU, and a rank's master vector is current only in its own
+ * slice until SB_DP_GATHER_MASTER (no gradients, no step: every owner's slice
+ * is copied to all ranks) is called.  Every wait is bounded by timeout_ms; when
+ * one expires the update is skipped, sb_dp_status reports 0x100 + the rank
+ * that did not arrive, and the flag block must be zeroed before it is used
+ * again.  barriers = 0 runs the update without either barrier (single rank, or
+ * ranks ordered by the caller). */
+enum { SB_DP_REPLICATED = 0, SB_DP_SHARDED_MASTER = 1, SB_DP_GATHER_MASTER = 2 };
+int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float* const* params,
+                     void* const* w_compute, void* const* flags, unsigned int epoch, long long n, float lr,
+                     int compute_dtype, int mode, const long long* replicate, int n_replicate, int timeout_ms,
+                     int barriers, void* stream);
+int sb_dp_status(const void* flags, int* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,4 +8,5 @@
 #include "api.cu"
 #include "mlp.cu"
 #include "mlp_fused.cu"
+#include "dp.cu"
 #include "selftest.cu"

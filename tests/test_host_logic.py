@@ -107,3 +107,19 @@ def test_two_rank_gloo_data_parallel_step(tmp_path):
                                       stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=180)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+
+
+@pytest.mark.parametrize("n,world", [(3681856, 8), (3681856, 3), (64, 8), (8, 16), (0, 2), (4, 1)])
+def test_peer_update_slices_partition_the_parameter_vector(n, world):
+    """Every element is reduced and updated by exactly one rank; slices are whole 4-element vectors."""
+    import spiral_b200 as sb
+    cover = np.zeros(n, np.int32)
+    for r in range(world):
+        b, e = sb.update_slice(n, world, r)
+        assert 0 <= b <= e <= n and b % 4 == 0 and e % 4 == 0
+        cover[b:e] += 1
+    assert np.all(cover == 1)
+    with pytest.raises(sb.SpiralError):
+        sb.update_slice(6, 2, 0)
+    with pytest.raises(sb.SpiralError):
+        sb.update_slice(64, 2, 2)
