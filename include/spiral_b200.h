@@ -280,10 +280,12 @@ int sb_ipc_open(const void* handle64, void** dev_ptr);
 int sb_ipc_close(void* dev_ptr);
 /* Size of one rank's flag block; the caller zero-fills it once before the first step. */
 int sb_dp_flag_bytes(void);
-/* [begin, end) of the parameter slice rank `rank` reduces and updates (n % 4 == 0). */
-int sb_dp_slice(long long n, int world_size, int rank, long long* begin_end);
-/* Gradient reduction + SGD + redistribution in one kernel: waits until every
- * rank has reached this call (flag barrier), then for this rank's slice
+/* The part of the element range [begin, end) (whole 4-element vectors) that rank `rank` reduces and
+ * updates when the range is handled by one sb_dp_sgd_update call. */
+int sb_dp_slice(long long begin, long long end, int world_size, int rank, long long* begin_end);
+/* Gradient reduction + SGD + redistribution in one kernel for the elements
+ * [begin, end) of the flat vectors: waits until every rank has reached this
+ * call (flag barrier), then for this rank's slice of the range
  *   g = sum over ranks (in rank order) of grads[r][i];  w = params[rank][i] - lr * g;
  *   params[r][i] = w and w_compute[r][i] = round(w) for every rank r,
  * and closes with a second barrier, after which every rank holds the complete
@@ -299,12 +301,14 @@ int sb_dp_slice(long long n, int world_size, int rank, long long* begin_end);
  * one expires the update is skipped, sb_dp_status reports 0x100 + the rank
  * that did not arrive, and the flag block must be zeroed before it is used
  * again.  barriers = 0 runs the update without either barrier (single rank, or
- * ranks ordered by the caller). */
+ * ranks ordered by the caller).  A step may be split into several calls over
+ * disjoint ranges; calls that can be in flight at the same time need flag
+ * blocks of their own.  max_blocks caps the grid (0 = no cap). */
 enum { SB_DP_REPLICATED = 0, SB_DP_SHARDED_MASTER = 1, SB_DP_GATHER_MASTER = 2 };
 int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float* const* params,
-                     void* const* w_compute, void* const* flags, unsigned int epoch, long long n, float lr,
-                     int compute_dtype, int mode, const long long* replicate, int n_replicate, int timeout_ms,
-                     int barriers, void* stream);
+                     void* const* w_compute, void* const* flags, unsigned int epoch, long long begin, long long end,
+                     float lr, int compute_dtype, int mode, const long long* replicate, int n_replicate,
+                     int max_blocks, int timeout_ms, int barriers, void* stream);
 int sb_dp_status(const void* flags, int* status);
 
 #ifdef __cplusplus

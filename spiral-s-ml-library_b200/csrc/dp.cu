@@ -34,6 +34,7 @@ namespace {
 
 constexpr int DP_MAX_WORLD = 16;
 constexpr int DP_MAX_RANGES = 16;
+constexpr int DP_THREADS = 128;
 constexpr int DP_STATUS_WORD = 16;     // index of the status word in a flag block
 constexpr int DP_COUNTER_WORD = 17;    // CTAs of the running update that have finished their stores
 constexpr int DP_FLAG_WORDS = 32;      // words per flag block: [0, 16) peer epochs, [16] status, [17] counter
@@ -134,9 +135,9 @@ __device__ __forceinline__ void store_compute4(void* base, long long i, float4 w
 // One launch per step and rank.  `n` is a multiple of 4; slices are whole
 // 4-element vectors.  barriers = 0 skips both barriers (single rank, or a
 // caller that ordered the ranks by other means).
-__global__ void __launch_bounds__(256)
-dp_update_kernel(DpPeers peers, int world, int rank, unsigned int epoch, long long n, float lr, int dt,
-                 unsigned long long timeout_ns, int barriers) {
+__global__ void __launch_bounds__(DP_THREADS)
+dp_update_kernel(DpPeers peers, int world, int rank, unsigned int epoch, long long begin, long long end, float lr,
+                 int dt, unsigned long long timeout_ns, int barriers) {
   unsigned int* my_flags = peers.flags[rank];
   __shared__ int is_last;
   if (barriers) {
@@ -145,24 +146,31 @@ dp_update_kernel(DpPeers peers, int world, int rank, unsigned int epoch, long lo
   } else if (ld_volatile_u32(my_flags + DP_STATUS_WORD) != 0u) {
     return;
   }
-  const long long nvec = n >> 2;
+  const long long nvec = (end - begin) >> 2;
   const long long per = (nvec + world - 1) / world;
-  const long long v_begin = per * rank;
-  const long long v_end = min(nvec, v_begin + per);
+  const long long v_begin = (begin >> 2) + min(nvec, per * rank);
+  const long long v_end = (begin >> 2) + min(nvec, per * rank + per);
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long v = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v_end; v += step) {
     const long long i = v << 2;
     float4 w = *reinterpret_cast<const float4*>(peers.params[rank] + i);
     bool master_everywhere = peers.shard_master == 0;
     if (!peers.gather_only) {
-      float4 g[DP_MAX_WORLD];
-#pragma unroll
-      for (int r = 0; r < DP_MAX_WORLD; ++r)
-        if (r < world) g[r] = ld_volatile_f4(peers.grads[r] + i);      // all loads in flight before the first add
+      // Eight loads in flight before the first add (two rounds for more than eight ranks): a CTA of
+      // this kernel must fit beside a resident GEMM CTA, which leaves it some 90 registers a thread.
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int r = 0; r < DP_MAX_WORLD; ++r)
-        if (r < world) { s.x += g[r].x; s.y += g[r].y; s.z += g[r].z; s.w += g[r].w; }
+      for (int r0 = 0; r0 < DP_MAX_WORLD; r0 += 8) {
+        if (r0 < world) {
+          float4 g[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r0 + r < world) g[r] = ld_volatile_f4(peers.grads[r0 + r] + i);
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r0 + r < world) { s.x += g[r].x; s.y += g[r].y; s.z += g[r].z; s.w += g[r].w; }
+        }
+      }
       w.x -= lr * s.x; w.y -= lr * s.y; w.z -= lr * s.z; w.w -= lr * s.w;
       if (!master_everywhere)
         for (int k = 0; k < peers.n_ranges; ++k)     // ranges are whole vectors (64-element aligned segments)
@@ -226,28 +234,31 @@ int sb_ipc_close(void* dev_ptr) {
 
 int sb_dp_flag_bytes(void) { return DP_FLAG_WORDS * (int)sizeof(unsigned int); }
 
-int sb_dp_slice(long long n, int world_size, int rank, long long* begin_end) {
+int sb_dp_slice(long long begin, long long end, int world_size, int rank, long long* begin_end) {
   if (!begin_end) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_slice: null output");
-  if (n < 0 || n % 4 != 0) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_slice: n must be a non-negative multiple of 4");
+  if (begin < 0 || end < begin || begin % 4 != 0 || end % 4 != 0)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_dp_slice: [begin, end) must be whole 4-element vectors");
   if (world_size < 1 || world_size > DP_MAX_WORLD || rank < 0 || rank >= world_size)
     return sb_fail(SB_ERR_BAD_ARG, "sb_dp_slice: rank %d of world size %d (at most %d ranks)", rank, world_size, DP_MAX_WORLD);
-  const long long nvec = n >> 2;
+  const long long nvec = (end - begin) >> 2;
   const long long per = (nvec + world_size - 1) / world_size;
   long long b = per * rank, e = b + per;
   if (b > nvec) b = nvec;
   if (e > nvec) e = nvec;
-  begin_end[0] = b << 2;
-  begin_end[1] = e << 2;
+  begin_end[0] = begin + (b << 2);
+  begin_end[1] = begin + (e << 2);
   return SB_OK;
 }
 
 int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float* const* params,
-                     void* const* w_compute, void* const* flags, unsigned int epoch, long long n, float lr,
-                     int compute_dtype, int mode, const long long* replicate, int n_replicate, int timeout_ms,
-                     int barriers, void* stream) {
+                     void* const* w_compute, void* const* flags, unsigned int epoch, long long begin, long long end,
+                     float lr, int compute_dtype, int mode, const long long* replicate, int n_replicate,
+                     int max_blocks, int timeout_ms, int barriers, void* stream) {
   if (world_size < 1 || world_size > DP_MAX_WORLD || rank < 0 || rank >= world_size)
     return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: rank %d of world size %d (at most %d ranks)", rank, world_size, DP_MAX_WORLD);
-  if (n < 0 || n % 4 != 0) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: n must be a non-negative multiple of 4");
+  if (begin < 0 || end < begin || begin % 4 != 0 || end % 4 != 0)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: [begin, end) must be whole 4-element vectors");
+  if (max_blocks < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: negative max_blocks");
   if (mode != SB_DP_REPLICATED && mode != SB_DP_SHARDED_MASTER && mode != SB_DP_GATHER_MASTER)
     return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: unknown mode %d", mode);
   if ((!grads && mode != SB_DP_GATHER_MASTER) || !params || !flags) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: null pointer table");
@@ -281,14 +292,15 @@ int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float*
   }
   cudaStream_t s = (cudaStream_t)stream;
   const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
-  const long long slice_vecs = ((n >> 2) + world_size - 1) / world_size;
-  long long blocks = (slice_vecs + 255) / 256;
+  const long long slice_vecs = (((end - begin) >> 2) + world_size - 1) / world_size;
+  long long blocks = (slice_vecs + DP_THREADS - 1) / DP_THREADS;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  const long long cap = max_blocks > 0 ? max_blocks : 148 * 8;
+  if (blocks > cap) blocks = cap;
   // A plain launch (no programmatic dependent launch): the first thing this kernel does is to tell
   // its peers that the gradients of this rank -- the work of the kernels before it -- are complete.
-  dp_update_kernel<<<(int)blocks, 256, 0, s>>>(peers, world_size, rank, epoch, n, lr, compute_dtype, timeout_ns,
-                                               barriers ? 1 : 0);
+  dp_update_kernel<<<(int)blocks, DP_THREADS, 0, s>>>(peers, world_size, rank, epoch, begin, end, lr, compute_dtype,
+                                                      timeout_ns, barriers ? 1 : 0);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;

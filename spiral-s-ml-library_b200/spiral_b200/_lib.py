@@ -84,9 +84,9 @@ SIGNATURES = {
     "sb_ipc_open": (_I, [_P, _PP]),
     "sb_ipc_close": (_I, [_P]),
     "sb_dp_flag_bytes": (_I, []),
-    "sb_dp_slice": (_I, [ctypes.c_longlong, _I, _I, POINTER(ctypes.c_longlong)]),
-    "sb_dp_sgd_update": (_I, [_I, _I, _PP, _PP, _PP, _PP, ctypes.c_uint, ctypes.c_longlong, ctypes.c_float, _I, _I,
-                              POINTER(ctypes.c_longlong), _I, _I, _I, _P]),
+    "sb_dp_slice": (_I, [ctypes.c_longlong, ctypes.c_longlong, _I, _I, POINTER(ctypes.c_longlong)]),
+    "sb_dp_sgd_update": (_I, [_I, _I, _PP, _PP, _PP, _PP, ctypes.c_uint, ctypes.c_longlong, ctypes.c_longlong,
+                              ctypes.c_float, _I, _I, POINTER(ctypes.c_longlong), _I, _I, _I, _I, _P]),
     "sb_dp_status": (_I, [_P, _IP]),
     "sb_encode_states": (_I, [_P, _I, _IP, _P, _I, _P, ctypes.c_longlong, _I, _P]),
     "sb_mlp_param_offsets": (_I, [_I, _IP, POINTER(ctypes.c_longlong)]),

@@ -32,10 +32,12 @@ def bucket_ranges(n_elements, bucket_elements):
     return [(b, min(n_elements, b + bucket_elements)) for b in range(0, int(n_elements), int(bucket_elements))]
 
 
-def update_slice(n_params, world_size, rank):
-    """[begin, end) of the flat parameter vector that ``rank`` reduces and updates in a peer update."""
+def update_slice(n_params, world_size, rank, begin=0):
+    """The part of [begin, n_params) of the flat parameter vector that ``rank`` reduces and updates
+    when a peer update covers that range in one call."""
     out = (ctypes.c_longlong * 2)()
-    _lib.call("sb_dp_slice", ctypes.c_longlong(int(n_params)), int(world_size), int(rank), out)
+    _lib.call("sb_dp_slice", ctypes.c_longlong(int(begin)), ctypes.c_longlong(int(n_params)), int(world_size),
+              int(rank), out)
     return int(out[0]), int(out[1])
 
 
@@ -76,9 +78,9 @@ class PeerUpdate:
         if len(everyone) != self.world_size:
             raise ValueError("exchange returned %d payloads for %d ranks" % (len(everyone), self.world_size))
         self._opened = []
-        tables = [[None] * self.world_size for _ in range(4)]
+        tables = [[None] * self.world_size for _ in mine]
         for r, payload in enumerate(everyone):
-            for k in range(4):
+            for k in range(len(mine)):
                 if r == self.rank:
                     tables[k][r] = mine[k]
                 else:
@@ -90,7 +92,7 @@ class PeerUpdate:
         self._tables = [(ctypes.c_void_p * self.world_size)(*t) for t in tables]
 
     def step(self, lr, stream=None):
-        """All ranks call this after their backward pass; returns once the launches are enqueued."""
+        """All ranks call this after their backward pass; returns once the launch is enqueued."""
         self._call(self.SHARDED_MASTER if self.shard_master else self.REPLICATED, lr, stream)
 
     def gather_master(self, stream=None):
@@ -101,8 +103,9 @@ class PeerUpdate:
         net = self.net
         g, p, w, f = self._tables
         _lib.call("sb_dp_sgd_update", self.world_size, self.rank, g, p, w, f, ctypes.c_uint(self.epoch),
-                  ctypes.c_longlong(net.n_params), ctypes.c_float(lr), _lib.DTYPE_CODES[net.storage],
-                  mode, self._ranges, self._n_ranges, self.timeout_ms, 1, stream_ptr(stream))
+                  ctypes.c_longlong(0), ctypes.c_longlong(net.n_params), ctypes.c_float(lr),
+                  _lib.DTYPE_CODES[net.storage], mode, self._ranges, self._n_ranges, 0, self.timeout_ms, 1,
+                  stream_ptr(stream))
         self.epoch += 2
 
     def status(self):

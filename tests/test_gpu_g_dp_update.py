@@ -44,8 +44,8 @@ def test_emulated_ranks_reduce_update_and_redistribute(gpu, world, n, storage):
     g_t, p_t, w_t, f_t = _tables(bufs)
     lr = 0.05
     for r in range(world):       # one rank after the other, barriers off
-        _lib.call("sb_dp_sgd_update", world, r, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(n),
-                  ctypes.c_float(lr), _lib.DTYPE_CODES[storage], 0, None, 0, 100, 0, None)
+        _lib.call("sb_dp_sgd_update", world, r, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(0), ctypes.c_longlong(n),
+                  ctypes.c_float(lr), _lib.DTYPE_CODES[storage], 0, None, 0, 0, 100, 0, None)
     gpu.synchronize()
     total = np.zeros(n, np.float32)
     for g in host_grads:         # the kernel adds in rank order, in fp32
@@ -79,8 +79,8 @@ def test_sharded_master_keeps_biases_everywhere_and_gather_completes_it(gpu):
     g_t, p_t, w_t, f_t = _tables(bufs)
     ranges = (ctypes.c_longlong * 4)(400, 800, 11000, 11200)       # two replicated ranges, in different slices
     for r in range(world):
-        _lib.call("sb_dp_sgd_update", world, r, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(n),
-                  ctypes.c_float(lr), _lib.DTYPE_CODES["bf16"], 1, ranges, 2, 100, 0, None)
+        _lib.call("sb_dp_sgd_update", world, r, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(0), ctypes.c_longlong(n),
+                  ctypes.c_float(lr), _lib.DTYPE_CODES["bf16"], 1, ranges, 2, 0, 100, 0, None)
     gpu.synchronize()
     total = np.zeros(n, np.float32)
     for g in host_grads:
@@ -99,12 +99,38 @@ def test_sharded_master_keeps_biases_everywhere_and_gather_completes_it(gpu):
         np.testing.assert_allclose(bufs[r][2].numpy(), so.round_bf16(want), rtol=0, atol=2e-2 * np.abs(want).max())
         np.testing.assert_array_equal(bufs[r][2].numpy(), bufs[0][2].numpy())
     for r in range(world):
-        _lib.call("sb_dp_sgd_update", world, r, None, p_t, w_t, f_t, ctypes.c_uint(3), ctypes.c_longlong(n),
-                  ctypes.c_float(0.0), _lib.DTYPE_CODES["bf16"], 2, None, 0, 100, 0, None)
+        _lib.call("sb_dp_sgd_update", world, r, None, p_t, w_t, f_t, ctypes.c_uint(3), ctypes.c_longlong(0), ctypes.c_longlong(n),
+                  ctypes.c_float(0.0), _lib.DTYPE_CODES["bf16"], 2, None, 0, 0, 100, 0, None)
     gpu.synchronize()
     for r in range(world):
         np.testing.assert_allclose(bufs[r][1].numpy(), want, rtol=0, atol=1e-6)
         np.testing.assert_array_equal(bufs[r][1].numpy(), bufs[0][1].numpy())
+
+
+def test_a_sub_range_leaves_the_rest_untouched(gpu):
+    from spiral_b200 import _lib
+    world, n, lr = 2, 4096, 0.25
+    params0 = so.rng(41).normal(size=n).astype(np.float32)
+    host_grads, bufs = [], []
+    for r in range(world):
+        g, b = _rank_buffers(gpu, n, 42 + r, "f32", params0)
+        host_grads.append(g)
+        bufs.append(b)
+    g_t, p_t, w_t, f_t = _tables(bufs)
+    begin, end = 1024, 3000
+    for r in range(world):
+        _lib.call("sb_dp_sgd_update", world, r, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(begin),
+                  ctypes.c_longlong(end), ctypes.c_float(lr), _lib.DTYPE_CODES["f32"], 0, None, 0, 3, 100, 0, None)
+    gpu.synchronize()
+    want = params0.copy()
+    want[begin:end] = (params0 - np.float32(lr) * (host_grads[0] + host_grads[1]))[begin:end]
+    for r in range(world):
+        np.testing.assert_allclose(bufs[r][1].numpy(), want, rtol=0, atol=1e-6)
+    cover = np.zeros(n, np.int32)
+    for r in range(world):
+        b, e = gpu.update_slice(end, world, r, begin=begin)
+        cover[b:e] += 1
+    assert np.all(cover[begin:end] == 1) and cover.sum() == end - begin
 
 
 def test_single_rank_equals_the_plain_sgd_update(gpu):
@@ -113,8 +139,8 @@ def test_single_rank_equals_the_plain_sgd_update(gpu):
     params0 = so.rng(2).normal(size=n).astype(np.float32)
     g, (grads, params, compute, flags) = _rank_buffers(gpu, n, 3, "bf16", params0)
     g_t, p_t, w_t, f_t = _tables([(grads, params, compute, flags)])
-    _lib.call("sb_dp_sgd_update", 1, 0, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(n),
-              ctypes.c_float(0.01), _lib.DTYPE_CODES["bf16"], 0, None, 0, 100, 1, None)      # barriers on: a rank always meets itself
+    _lib.call("sb_dp_sgd_update", 1, 0, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(0), ctypes.c_longlong(n),
+              ctypes.c_float(0.01), _lib.DTYPE_CODES["bf16"], 0, None, 0, 0, 100, 1, None)      # barriers on: a rank always meets itself
     ref_p = gpu.DeviceArray.from_numpy(params0.copy())
     ref_c = gpu.DeviceArray.zeros((n,), "bf16")
     _lib.call("sb_sgd_update", ref_p.ptr, grads.ptr, ref_c.ptr, ctypes.c_longlong(n), ctypes.c_float(0.01),
@@ -135,8 +161,8 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status(gpu):
     _, b0 = _rank_buffers(gpu, n, 5, "bf16", params0)
     _, b1 = _rank_buffers(gpu, n, 6, "bf16", params0)
     g_t, p_t, w_t, f_t = _tables([b0, b1])
-    _lib.call("sb_dp_sgd_update", 2, 0, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(n),
-              ctypes.c_float(0.5), _lib.DTYPE_CODES["bf16"], 0, None, 0, 50, 1, None)
+    _lib.call("sb_dp_sgd_update", 2, 0, g_t, p_t, w_t, f_t, ctypes.c_uint(1), ctypes.c_longlong(0), ctypes.c_longlong(n),
+              ctypes.c_float(0.5), _lib.DTYPE_CODES["bf16"], 0, None, 0, 0, 50, 1, None)
     gpu.synchronize()
     status = ctypes.c_int(0)
     _lib.call("sb_dp_status", b0[3].ptr, ctypes.byref(status))
@@ -153,5 +179,5 @@ def test_argument_checks(gpu):
     for bad in [dict(world=0), dict(rank=1), dict(n=6), dict(timeout=0), dict(dtype=99), dict(mode=7)]:
         with pytest.raises(gpu.SpiralError):
             _lib.call("sb_dp_sgd_update", bad.get("world", 1), bad.get("rank", 0), g_t, p_t, w_t, f_t, ctypes.c_uint(1),
-                      ctypes.c_longlong(bad.get("n", n)), ctypes.c_float(0.1), bad.get("dtype", _lib.DTYPE_CODES["bf16"]),
-                      bad.get("mode", 0), None, 0, bad.get("timeout", 100), 0, None)
+                      ctypes.c_longlong(0), ctypes.c_longlong(bad.get("n", n)), ctypes.c_float(0.1),
+                      bad.get("dtype", _lib.DTYPE_CODES["bf16"]), bad.get("mode", 0), None, 0, 0, bad.get("timeout", 100), 0, None)
