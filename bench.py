@@ -540,7 +540,8 @@ def run_ours(args, rank, world, local_rank):
                    "l2": l2_note},
         "roofline": {"bound": "tensor", "kernel": "mlp_fused_kernel" if fused else "umma_gemm_kernel",
                      "achieved": round(achieved, 1), "peak": peak,
-                     "unit": "TFLOP/s", "frac": round(achieved / peak, 4) if peak else None, "traffic": None,
+                     "unit": "TFLOP/s", "frac": round(achieved / peak, 4) if peak else None,
+                     "traffic": NCU_TRAFFIC.get((workload, batch)),
                      "peak_kind": "%s, sustained cuBLAS bf16" % peaks["source"]},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(h2d) * world,
@@ -553,6 +554,12 @@ def run_ours(args, rank, world, local_rank):
     if dist is not None:
         dist.destroy_process_group()
 
+
+# DRAM bytes (read + write) of one launch of the dominant GEMM shape of a workload, from an ncu capture
+# of a quarter of the batch rows scaled by the rows (the capture is described under profiles/, file
+# umma_gemm_kernel_holdem_layer_fwd_bits.md); keyed by (workload, rows per GPU).  The bound of that
+# kernel is the tensor pipe; the figure shows that its operands are read from DRAM once.
+NCU_TRAFFIC = {("holdem_train", 262144): 4 * (136404992 + 101345792)}
 
 PROFILE_CASES = {
     # name: (a_trans, b_trans, M, N, K, in_dtype, out_dtype, epilogue)

@@ -114,3 +114,26 @@ def test_encode_states_edge_cases(gpu):
         P.encode_states(_dev(gpu, fields), (3, 3), _dev(gpu, dense), gpu.DeviceArray((4, 10), "f32"))
     with pytest.raises(gpu.SpiralError):
         P.encode_states(_dev(gpu, fields), (3, 300), None, gpu.DeviceArray((4, 303), "f32"))
+
+
+def test_encode_states_wide_dense_rows_and_many_rows(gpu):
+    """More than one CTA pass over the rows, a row count that is not a multiple of the 32-row group,
+    fp32 dense rows wide enough to need the shared-memory opt-in, and a misaligned dense base."""
+    P = gpu.primitives
+    rows, n_dense = 148 * 16 * 32 + 45, 24
+    g = so.rng(5)
+    fields = g.integers(0, 5, size=(rows, 3)).astype(np.uint8)
+    dense = g.random((rows, n_dense), dtype=np.float32)
+    out = gpu.DeviceArray((rows, 4 + 4 + 4 + n_dense), "f32")
+    P.encode_states(_dev(gpu, fields), (4, 4, 4), _dev(gpu, dense), out)
+    np.testing.assert_array_equal(out.numpy(), so.encode_states(fields, (4, 4, 4), dense))
+    rows, n_dense = 70, 500                                       # 32 x 500 x 4 B = 64000 B of shared memory
+    fields = g.integers(0, 3, size=(rows, 1)).astype(np.uint8)
+    dense = g.random((rows, n_dense), dtype=np.float32)
+    out = gpu.DeviceArray((rows, 2 + n_dense), "f32")
+    P.encode_states(_dev(gpu, fields), (2,), _dev(gpu, dense), out)
+    np.testing.assert_array_equal(out.numpy(), so.encode_states(fields, (2,), dense))
+    whole = gpu.DeviceArray.from_numpy(np.concatenate([np.zeros(1, np.float32), dense.ravel()]))
+    shifted = whole.view((rows, n_dense), "f32", 4)               # dense base 4 bytes off a 16-byte boundary
+    P.encode_states(_dev(gpu, fields), (2,), shifted, out)
+    np.testing.assert_array_equal(out.numpy(), so.encode_states(fields, (2,), dense))
