@@ -89,13 +89,16 @@ __device__ __forceinline__ bool dp_wait(unsigned int* my_flags, int world, unsig
   if ((int)threadIdx.x < world) {
     const unsigned long long t0 = global_timer_ns();
     bool ok = true;
-    // epochs only grow; the signed difference tolerates wrap-around
+    unsigned int polls = 0;
+    // Epochs only grow; the signed difference tolerates wrap-around.  The clock and the status word
+    // are looked at every 16th poll only: the common case is a flag that arrives within microseconds.
     while ((int)(ld_volatile_u32(my_flags + threadIdx.x) - epoch) < 0) {
-      if (global_timer_ns() - t0 > timeout_ns || ld_volatile_u32(my_flags + DP_STATUS_WORD) != 0u) {
+      if ((++polls & 15u) == 0u &&
+          (global_timer_ns() - t0 > timeout_ns || ld_volatile_u32(my_flags + DP_STATUS_WORD) != 0u)) {
         ok = false;
         break;
       }
-      __nanosleep(64);
+      __nanosleep(20);
     }
     if (!ok) {
       atomicCAS(my_flags + DP_STATUS_WORD, 0u, 0x100u + threadIdx.x);   // 0x100 + the rank that never arrived
