@@ -62,13 +62,21 @@ void param_offsets(int n_layers, const int* sizes, long long* off) {
 
 // d logits of cross-entropy(masked softmax): (p * sum(t) - t) / global_batch on
 // legal entries, 0 elsewhere; also accumulates the loss.  One thread per row.
-template <typename DyT, bool ROUND_TF32>
+// LD > 0: the padded row width is the compile-time LD and the column sums of
+// d logits -- the head layer's bias gradient -- are added to db here (a CTA-wide
+// reduction, then LD atomics per CTA) instead of in a pass of their own over dY.
+template <typename DyT, bool ROUND_TF32, int LD>
 __global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __restrict__ target,
                                const uint8_t* __restrict__ mask, DyT* __restrict__ dy, int rows, int n,
-                               int ld, float inv_batch, float* __restrict__ loss) {
+                               int ld, float inv_batch, float* __restrict__ loss, float* __restrict__ db) {
+  constexpr int NACC = LD > 0 ? LD : 1;
+  __shared__ float colpart[8][NACC];
   sb_grid_dependency_wait();
   sb_grid_dependents_launch();
   float local = 0.f;
+  float colacc[NACC];
+#pragma unroll
+  for (int j = 0; j < NACC; ++j) colacc[j] = 0.f;
   for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
        r += (long long)gridDim.x * blockDim.x) {
     const float* pr = probs + r * n;
@@ -77,7 +85,7 @@ __global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __r
     float tsum = 0.f;
     for (int j = 0; j < n; ++j)
       if (!mr || mr[j]) tsum += tr[j];
-    for (int j = 0; j < ld; ++j) {
+    auto one = [&](int j) {
       const bool lg = j < n && (!mr || mr[j]);
       float g = 0.f;
       if (lg) {
@@ -92,12 +100,36 @@ __global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __r
       }
       if (sizeof(DyT) == 4) reinterpret_cast<float*>(dy)[r * ld + j] = g;
       else if (sizeof(DyT) == 2) dy[r * ld + j] = (DyT)g;
+      return g;
+    };
+    if (LD > 0) {
+#pragma unroll
+      for (int j = 0; j < NACC; ++j) colacc[j] += one(j);
+    } else {
+      for (int j = 0; j < ld; ++j) one(j);
     }
   }
   if (loss) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
     if ((threadIdx.x & 31) == 0 && local != 0.f) atomicAdd(loss, local * inv_batch);
+  }
+  if (LD > 0 && db) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int j = 0; j < NACC; ++j) {
+      float v = colacc[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) colpart[warp][j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < NACC && (int)threadIdx.x < n) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += colpart[w][threadIdx.x];
+      if (t != 0.f) atomicAdd(db + threadIdx.x, t);
+    }
   }
 }
 
@@ -391,22 +423,35 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
 
   const int n_out = sizes[n_layers];
   const int ld_out = padded_out(n_out);
+  bool head_bias_done = false;
   if (from_top) {
     const int blocks = blocks_for(batch, 256);
-    if (in_dtype == SB_BF16)
-      SB_CUDA(sb_launch(ce_grad_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (__nv_bfloat16*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss));
-    else if (in_dtype == SB_F16)
-      SB_CUDA(sb_launch(ce_grad_kernel<__half, false>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (__half*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss));
-    else
-      SB_CUDA(sb_launch(ce_grad_kernel<float, true>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (float*)dy_cur, batch, n_out, ld_out, inv_global_batch, loss));
+    // The head layer's bias gradient is summed by this kernel when its padded width is 8 or 16.
+    head_bias_done = with_bias && first_layer == n_layers - 1 && (ld_out == 8 || ld_out == 16);
+    float* db_head = head_bias_done ? grads + off[2 * (n_layers - 1) + 1] : nullptr;
+#define SB_CE_LAUNCH(T, R, L)                                                                                     \
+  SB_CUDA(sb_launch(ce_grad_kernel<T, R, L>, dim3(blocks), dim3(256), 0, s, 1, probs, target, mask, (T*)dy_cur, \
+                    batch, n_out, ld_out, inv_global_batch, loss, db_head))
+#define SB_CE_BY_LD(T, R)                                     \
+  do {                                                        \
+    if (head_bias_done && ld_out == 8) SB_CE_LAUNCH(T, R, 8); \
+    else if (head_bias_done) SB_CE_LAUNCH(T, R, 16);          \
+    else SB_CE_LAUNCH(T, R, 0);                               \
+  } while (0)
+    if (in_dtype == SB_BF16) SB_CE_BY_LD(__nv_bfloat16, false);
+    else if (in_dtype == SB_F16) SB_CE_BY_LD(__half, false);
+    else SB_CE_BY_LD(float, true);
+#undef SB_CE_BY_LD
+#undef SB_CE_LAUNCH
     SB_COUNT_LAUNCH();
-  SB_CUDA(cudaGetLastError());
+    SB_CUDA(cudaGetLastError());
   }
 
   // True when dY of the current layer came out of a dgrad whose epilogue already added its column
   // sums to the bias gradient, so that the stand-alone column-sum pass (a second read of dY) is skipped.
   // A pass split into several calls: the dgrad of the layer above ran in an earlier call.
-  bool bias_done = !from_top && with_bias && relu_bits && relu_bits[first_layer] && sizes[first_layer + 1] % 32 == 0;
+  bool bias_done = from_top ? head_bias_done
+                            : (with_bias && relu_bits && relu_bits[first_layer] && sizes[first_layer + 1] % 32 == 0);
   for (int i = first_layer; i >= last_layer; --i) {
     const int fan_out = padded_out(sizes[i + 1]), fan_in = sizes[i];
     const void* h_in = i == 0 ? x : activations[i - 1];
