@@ -1,6 +1,6 @@
 """Builds the reference's own GEMM kernel for sm_100a into oracle/_ref/.  TEST INFRASTRUCTURE ONLY.
 
-    python oracle/build_ref.py [/root/reference]
+    python oracle/build_ref.py [<reference checkout>]
 
 The reference has no CPU implementation of this path and no hand-written CUDA: its kernels are
 Spiral-generated CUDA C++ embedded as a string in generated Python files, compiled at run time by

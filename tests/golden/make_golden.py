@@ -3,7 +3,7 @@ tests/golden/primitives_golden.npz.
 
 Run in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <reference checkout>
 
 Sources (all under test_text_outputs/primitives/, printed by the tests in
 ml/primitives.spi:851-989 with seed 12344321): test2/{a,b} print the first 1024
