@@ -609,6 +609,77 @@ def run_profile_case(name, iters):
           % (name, ms, 2.0 * m * n * k / ms / 1e9, sb.device_status()), flush=True)
 
 
+def run_exchange_profile(args, rank, world, local_rank):
+    """Times the data-parallel exchange of the Hold'em net by itself (under torchrun, N >= 2): the
+    library's peer-memory update and its parts (remote reads only, remote stores only, local memory
+    with and without the flag barriers) beside NCCL all-reduce + SGD.  One table on rank 0."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    import spiral_b200 as sb
+    from spiral_b200 import _lib
+    torch.cuda.set_device(local_rank)
+    sb.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sizes = WORKLOADS["holdem_train"][0]
+    net = sb.PolicyMLP(sizes, 1024, in_dtype="bf16", training=True)
+
+    def exchange(payload):
+        out = [None] * world
+        dist.all_gather_object(out, payload)
+        return out
+
+    peer = sb.PeerUpdate(net, world, rank, exchange)
+    tg = torch.zeros(net.n_params, dtype=torch.float32, device="cuda")
+
+    def timed(fn):
+        for _ in range(5):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sb.synchronize()
+        e0 = sb.Event().record()
+        for _ in range(args.iters):
+            fn()
+        e1 = sb.Event().record()
+        ms = e0.elapsed_ms(e1) / args.iters
+        torch.cuda.synchronize()
+        return ms * 1e3
+
+    g, p, w, f = peer._tables
+
+    def own(table):
+        return (ctypes.c_void_p * world)(*[table[rank]] * world)
+
+    def call(gt, pt, wt, mode, barriers=1):
+        _lib.call("sb_dp_sgd_update", world, rank, gt, pt, wt, f, ctypes.c_uint(peer.epoch), ctypes.c_longlong(0),
+                  ctypes.c_longlong(net.n_params), ctypes.c_float(1e-3), _lib.DTYPE_CODES["bf16"], mode,
+                  peer._ranges, peer._n_ranges, 0, 2000, barriers, None)
+        peer.epoch += 2
+
+    rows = [
+        ("peer update, sharded master (the default)", lambda: call(g, p, w, 1)),
+        ("peer update, replicated master", lambda: call(g, p, w, 0)),
+        ("  remote reads only (stores to own memory)", lambda: call(g, own(p), own(w), 0)),
+        ("  remote stores only (reads from own memory)", lambda: call(own(g), p, w, 0)),
+        ("  own memory only, both barriers", lambda: call(own(g), own(p), own(w), 0)),
+        ("  own memory only, no barrier", lambda: call(own(g), own(p), own(w), 0, 0)),
+        ("nccl all-reduce + sgd kernel", lambda: (dist.all_reduce(tg), net.sgd(1e-3))),
+        ("nccl all-reduce", lambda: dist.all_reduce(tg)),
+    ]
+    results = [(name, timed(fn)) for name, fn in rows]
+    status = peer.status()
+    if rank == 0:
+        print("exchange of %d parameters (%.1f MB of fp32 gradients) on %d GPUs, microseconds per step:"
+              % (net.n_params, net.n_params * 4 / 1e6, world))
+        for name, us in results:
+            print("  %-48s %7.1f" % (name, us))
+        print("status 0x%x" % status, flush=True)
+    dist.barrier()
+    peer.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -626,6 +697,8 @@ def main():
     ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
                     help="run a few launches of one GEMM shape (for ncu) and exit")
     ap.add_argument("--iters", type=int, default=4)
+    ap.add_argument("--profile-exchange", action="store_true",
+                    help="under torchrun: time the data-parallel exchange and its parts (no JSON line)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args.profile_case, args.iters)
@@ -633,6 +706,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.profile_exchange:
+        if world < 2:
+            raise SystemExit("--profile-exchange needs a torchrun launch with at least 2 ranks")
+        run_exchange_profile(args, rank, world, local_rank)
+        return
     if args.impl == "reference":
         run_reference(args, rank)
         return
