@@ -209,6 +209,16 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
 int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
                          const void* w_compute, const float* params, int head, const uint8_t* mask,
                          float* out, int32_t* actions, void* stream);
+/* The same for an ensemble of `members` nets of one architecture on ONE input batch, the way the
+ * reference's games run their policies (layers.matmul_ensemble, ml/layers.spi:468-471: weights
+ * [ensemble, out, in], the graph run once per member, ml/layers.spi:339-344): here all members are
+ * one launch, a CTA works on (row tile, member) pairs.  w_compute and params hold the members'
+ * flat parameter vectors one after the other (member e at element e * sb_mlp_param_offsets(...)
+ * [2 * n_layers]); out: fp32 [members, batch, n_out]; actions: int32 [members, batch]; mask
+ * [batch, n_out] is shared by the members. */
+int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                                  const void* x, const void* w_compute, const float* params, int head,
+                                  const uint8_t* mask, float* out, int32_t* actions, void* stream);
 
 /* The same forward pass for callers that cannot allocate device memory (a host
  * that owns no allocator, a plugin in a context where allocation is forbidden,

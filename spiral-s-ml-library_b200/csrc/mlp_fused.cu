@@ -31,7 +31,7 @@ constexpr uint32_t FM_STAGE_BYTES = 256u * 128u;       // weight stage: up to 25
 
 struct FusedMaps {
   CUtensorMap x;                      // [batch, in] box {64, 128}
-  CUtensorMap w[FM_MAX_LAYERS];       // W_l [out_l, in_l] box {64, rows_l}
+  CUtensorMap w[FM_MAX_LAYERS];       // W_l [members, out_l, in_l] box {64, rows_l, 1}
 };
 
 struct FusedParams {
@@ -45,7 +45,10 @@ struct FusedParams {
   const float* bias[FM_MAX_LAYERS];   // may be null
   int is_bf16;
   int tmem_cols;
-  int num_tiles;
+  int num_tiles;                      // 128-row tiles of the batch
+  int num_items;                      // work items = tiles x ensemble members
+  long long member_stride;            // elements between two members' parameter vectors
+  long long out_stride;               // elements between two members' outputs (batch x n_out)
   uint32_t x_chunks;                  // chunks of the input tile
   uint32_t act_offset, w_offset;      // byte offsets of the activation tile and the weight ring
   // head
@@ -236,7 +239,8 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
       int stage = 0;
       uint32_t w_phase = 0, x_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        const int member = item / p.num_tiles, tile = item - member * p.num_tiles;
         if (!mbar_wait(smem_u32(&bar_x_empty), x_phase ^ 1u, abortp, SB_SITE_MLP_ACT)) break;
         x_phase ^= 1u;
         mbar_arrive_expect_tx(smem_u32(&bar_x_full), p.x_chunks * FM_CHUNK_BYTES);
@@ -249,7 +253,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
               break;
             }
             mbar_arrive_expect_tx(smem_u32(&bar_w_full[stage]), p.w_bytes[l]);
-            tma_load_2d(w_base + (uint32_t)stage * FM_STAGE_BYTES, &maps.w[l], c * 64, 0, smem_u32(&bar_w_full[stage]));
+            tma_load_3d(w_base + (uint32_t)stage * FM_STAGE_BYTES, &maps.w[l], c * 64, 0, member, smem_u32(&bar_w_full[stage]));
             if (++stage == FM_W_STAGES) {
               stage = 0;
               w_phase ^= 1u;
@@ -264,7 +268,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
       uint32_t w_phase = 0, x_phase = 0, act_phase = 0;
       bool ok = true;
       const uint32_t hi = (uint32_t)(umma_smem_desc(0u, 16u, 1024u, 2u) >> 32);
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         for (int l = 0; ok && l < L; ++l) {
           uint32_t a_base;
           if (l == 0) {
@@ -300,7 +304,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
           tc_commit(smem_u32(&bar_acc_full));
         }
         // The next tile's first layer overwrites the accumulator: wait until the head has read it.
-        if (ok && tile + (int)gridDim.x < p.num_tiles) {
+        if (ok && item + (int)gridDim.x < p.num_items) {
           if (!mbar_wait(smem_u32(&bar_act_ready), act_phase, abortp, SB_SITE_MLP_ACT)) break;
           act_phase ^= 1u;
         }
@@ -316,14 +320,20 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
     h.out = p.out; h.bias = p.bias[L - 1]; h.mask = p.mask; h.actions = p.actions;
     h.N = p.width[L]; h.epi = p.head;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      const int member = item / p.num_tiles, tile = item - member * p.num_tiles;
+      const long long pofs = (long long)member * p.member_stride;
+      h.out = p.out + (long long)member * p.out_stride;
+      h.actions = p.actions ? p.actions + (long long)member * p.batch : nullptr;
+      h.bias = p.bias[L - 1] ? p.bias[L - 1] + pofs : nullptr;
       for (int l = 0; l < L; ++l) {
         if (!mbar_wait(smem_u32(&bar_acc_full), acc_phase, abortp, SB_SITE_MLP_ACC)) { ok = false; break; }
         acc_phase ^= 1u;
         tc_fence_after_sync();
         if (l < L - 1) {
-          if (p.is_bf16) fused_hidden<true>(t_row, p.n_pad[l], p.bias[l], act_base, bias_smem, row_in_tile, lane, half);
-          else fused_hidden<false>(t_row, p.n_pad[l], p.bias[l], act_base, bias_smem, row_in_tile, lane, half);
+          const float* bias_l = p.bias[l] ? p.bias[l] + pofs : nullptr;
+          if (p.is_bf16) fused_hidden<true>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half);
+          else fused_hidden<false>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half);
           // generic-proxy writes of the activation tile must be visible to the MMA's async-proxy reads
           fence_proxy_async_smem();
         } else if (half == 0) {
@@ -354,9 +364,42 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
 
 }  // namespace
 
+// 3-D tensor map over the weights of one layer of every ensemble member: [members, rows, cols] with
+// `member_stride` elements between members, box {64 columns, box_rows, 1 member}, 128-byte swizzle.
+static int make_tmap_members(CUtensorMap* map, const void* base, int in_dtype, int members, long long member_stride,
+                             int rows, int cols, int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return sb_fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMapDataType dt = in_dtype == SB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t gdim[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)members};
+  cuuint64_t gstride[2] = {(cuuint64_t)cols * 2u, (cuuint64_t)member_stride * 2u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (members == 1) gstride[1] = (cuuint64_t)rows * cols * 2u;      // unused dimension: any legal stride
+  gstride[1] = (gstride[1] + 15u) / 16u * 16u;
+  CUresult r = enc(map, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return sb_fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d (members=%d rows=%d cols=%d)",
+                   (int)r, members, rows, cols);
+  return SB_OK;
+}
+
+extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                                             const void* x, const void* w_compute, const float* params, int head,
+                                             const uint8_t* mask, float* out, int32_t* actions, void* stream);
+
 extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
                                     const void* w_compute, const float* params, int head, const uint8_t* mask,
                                     float* out, int32_t* actions, void* stream) {
+  return sb_mlp_forward_fused_ensemble(n_layers, sizes, batch, 1, in_dtype, x, w_compute, params, head, mask, out,
+                                       actions, stream);
+}
+
+extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                                             const void* x, const void* w_compute, const float* params, int head,
+                                             const uint8_t* mask, float* out, int32_t* actions, void* stream) {
+  if (members < 1 || members > 1024) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: 1..1024 ensemble members");
   if (n_layers < 1 || n_layers > FM_MAX_LAYERS) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: 1..%d layers", FM_MAX_LAYERS);
   if (!sizes) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: sizes is null");
   if (in_dtype != SB_F16 && in_dtype != SB_BF16)
@@ -386,6 +429,9 @@ extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, i
   p.batch = batch;
   p.is_bf16 = in_dtype == SB_BF16;
   p.num_tiles = (batch + 127) / 128;
+  p.num_items = p.num_tiles * members;
+  p.member_stride = off[2 * n_layers];
+  p.out_stride = (long long)batch * sizes[n_layers];
   int max_n = 32;
   uint32_t max_act_chunks = 1;
   for (int l = 0; l <= n_layers; ++l) p.width[l] = sizes[l];
@@ -399,7 +445,7 @@ extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, i
     if (p.n_pad[l] > max_n) max_n = p.n_pad[l];
     if (l > 0 && (uint32_t)p.k_chunks[l] > max_act_chunks) max_act_chunks = (uint32_t)p.k_chunks[l];
     const void* w = reinterpret_cast<const char*>(w_compute) + off[2 * l] * 2;
-    rc = make_tmap_2d(&maps.w[l], w, in_dtype, sizes[l + 1], sizes[l], p.n_pad[l], 64, SWZ_128);
+    rc = make_tmap_members(&maps.w[l], w, in_dtype, members, p.member_stride, sizes[l + 1], sizes[l], p.n_pad[l]);
     if (rc != SB_OK) return rc;
   }
   for (int l = n_layers; l < FM_MAX_LAYERS; ++l) maps.w[l] = maps.w[0];
@@ -423,9 +469,9 @@ extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, i
   if (smem > 225 * 1024) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: %zu bytes of shared memory needed", smem);
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+  const int grid = p.num_items < sms ? p.num_items : sms;
   double flops = 0.0;
-  for (int l = 0; l < n_layers; ++l) flops += 2.0 * batch * (double)sizes[l] * sizes[l + 1];
+  for (int l = 0; l < n_layers; ++l) flops += 2.0 * batch * (double)sizes[l] * sizes[l + 1] * members;
   sb_prof_before((cudaStream_t)stream);
   mlp_fused_kernel<<<grid, FM_THREADS, smem, (cudaStream_t)stream>>>(maps, p);
   sb_prof_after((cudaStream_t)stream, flops);

@@ -9,6 +9,6 @@ from .device import (DeviceArray, Event, Stream, wait_event, GemmProfile, launch
                      synchronize)
 from .matmul import matmul, matmul_plan, matmul_tf32  # noqa: F401
 from . import primitives  # noqa: F401
-from .models import PolicyMLP, param_offsets, to_storage  # noqa: F401
+from .models import EnsemblePolicyMLP, PolicyMLP, param_offsets, to_storage  # noqa: F401
 from . import layers  # noqa: F401
 from .parallel import DataParallel, PeerUpdate, shard_rows, bucket_ranges, update_slice  # noqa: F401

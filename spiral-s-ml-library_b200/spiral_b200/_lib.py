@@ -92,6 +92,7 @@ SIGNATURES = {
     "sb_mlp_param_offsets": (_I, [_I, _IP, POINTER(ctypes.c_longlong)]),
     "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "sb_mlp_forward_fused_ensemble": (_I, [_I, _IP, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_static": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_backward_scratch_bytes": (_I, [_I, _IP, _I, _I, POINTER(c_size_t)]),
     "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),

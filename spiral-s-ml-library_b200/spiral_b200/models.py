@@ -196,3 +196,62 @@ class PolicyMLP:
 def to_storage(x, in_dtype):
     """Host fp32 array -> DeviceArray in the storage type of an arithmetic class."""
     return DeviceArray.from_numpy(np.asarray(x, np.float32), in_dtype)
+
+
+class EnsemblePolicyMLP:
+    """An ensemble of ``members`` policy nets of one architecture evaluated on ONE input batch in a
+    single launch of the fused kernel (the reference builds such nets with ``layers.matmul_ensemble``,
+    ml/layers.spi:468-471, and runs the graph once per member, ml/models.spi:47-49).
+
+    16-bit arithmetic classes and the fused kernel's width limits only (input <= 256, hidden layers
+    multiples of 64 up to 256, at most 32 outputs).  Outputs: ``probs`` fp32 [members, batch, n_out]
+    and, with an argmax head, ``actions`` int32 [members, batch].
+    """
+
+    def __init__(self, sizes, batch, members, in_dtype="f16", head=("masked_softmax",), with_bias=True):
+        if in_dtype not in ("bf16", "f16"):
+            raise ValueError("the fused ensemble forward runs in 'bf16' or 'f16'")
+        self.sizes = [int(s) for s in sizes]
+        self.n_layers = len(self.sizes) - 1
+        self.batch, self.members = int(batch), int(members)
+        self.in_dtype = self.storage = in_dtype
+        self.head = tuple(head)
+        self.head_flags = 0
+        for h in self.head:
+            self.head_flags |= HEAD_FLAGS[h]
+        self.with_bias = bool(with_bias)
+        self.offsets = param_offsets(self.sizes)
+        self.n_params = self.offsets[-1]
+        self._sizes_c = (ctypes.c_int * len(self.sizes))(*self.sizes)
+        self.params = DeviceArray.zeros((self.members, self.n_params), "f32")
+        self.w_compute = DeviceArray.zeros((self.members, self.n_params), self.storage)
+        self.probs = DeviceArray((self.members, self.batch, self.sizes[-1]), "f32")
+        self.actions = DeviceArray((self.members, self.batch), "i32") if "argmax" in self.head else None
+
+    def load_weights(self, member_weights, member_biases=None):
+        """``member_weights[e][i]`` = layer i's [out, in] fp32 weights of member e (biases alike)."""
+        if len(member_weights) != self.members:
+            raise ValueError("%d weight sets for %d members" % (len(member_weights), self.members))
+        flat = np.zeros((self.members, self.n_params), np.float32)
+        for e, weights in enumerate(member_weights):
+            for i, w in enumerate(weights):
+                w = np.asarray(w, np.float32)
+                if w.shape != (self.sizes[i + 1], self.sizes[i]):
+                    raise ValueError("member %d layer %d weight shape %s" % (e, i, w.shape))
+                o = self.offsets[2 * i]
+                flat[e, o:o + w.size] = w.ravel()
+                if member_biases is not None:
+                    b = np.asarray(member_biases[e][i], np.float32)
+                    ob = self.offsets[2 * i + 1]
+                    flat[e, ob:ob + b.size] = b
+        self.params.upload(flat)
+        self.w_compute.upload(flat)       # the upload rounds to the storage type
+        return self
+
+    def forward(self, x, mask=None, stream=None):
+        """All members on the batch ``x`` [batch, features] (storage type); returns ``probs``."""
+        _lib.call("sb_mlp_forward_fused_ensemble", self.n_layers, self._sizes_c, self.batch, self.members,
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr,
+                  self.params.ptr if self.with_bias else None, self.head_flags, device_ptr(mask), self.probs.ptr,
+                  self.actions.ptr if self.actions is not None else None, stream_ptr(stream))
+        return self.probs

@@ -210,3 +210,33 @@ def test_backward_split_by_layer_equals_whole_pass(gpu):
         np.testing.assert_allclose(gb, wb, rtol=1e-4, atol=1e-7)
     assert abs(float(net.loss.numpy()[0]) - loss_whole) <= 1e-5 * abs(loss_whole)
     assert net.layer_segment(0)[0] == 0 and net.layer_segment(3)[1] == net.n_params
+
+
+@pytest.mark.parametrize("members,batch,in_dtype", [(4, 1000, "f16"), (16, 6144, "bf16"), (3, 128, "f16")])
+def test_ensemble_forward_in_one_launch_equals_the_members_one_by_one(gpu, members, batch, in_dtype):
+    """All members of an ensemble on one input batch in a single fused launch: every member's
+    probabilities and actions equal the single-net fused forward with that member's weights
+    bit for bit, and the oracle within the class tolerance."""
+    sizes = [32, 64, 64, 3]
+    head = ("masked_softmax", "regret_matching", "argmax")
+    x, mask = so.leduc_inputs(31, batch)
+    dx, dm = gpu.to_storage(x, in_dtype), gpu.DeviceArray.from_numpy(mask)
+    sets = [so.mlp_weights(100 + e, sizes) for e in range(members)]
+    biases = [[so.rng(200 + e).normal(size=b.shape).astype(np.float32) * 0.1 for b in bs] for e, (_, bs) in enumerate(sets)]
+    ens = gpu.EnsemblePolicyMLP(sizes, batch, members, in_dtype=in_dtype, head=head)
+    ens.load_weights([ws for ws, _ in sets], biases)
+    l0 = gpu.launch_count()
+    probs = ens.forward(dx, dm).numpy()
+    assert gpu.launch_count() - l0 == 1
+    actions = ens.actions.numpy()
+    single = gpu.PolicyMLP(sizes, batch, in_dtype=in_dtype, head=head)
+    for e in range(members):
+        single.load_weights(sets[e][0], biases[e])
+        want_probs = single.forward_fused(dx, dm).numpy()
+        np.testing.assert_array_equal(probs[e], want_probs)
+        np.testing.assert_array_equal(actions[e], single.actions.numpy())
+    oracle = so.mlp_forward(x, sets[members - 1][0], biases[members - 1], mask, in_dtype=in_dtype, act_dtype=in_dtype,
+                            head=("masked_softmax", "regret_matching"))
+    assert so.rel_frobenius(probs[members - 1], oracle) <= TOL
+    with pytest.raises(gpu.SpiralError):
+        gpu.EnsemblePolicyMLP([32, 96, 3], batch, 2).forward(dx, dm)        # hidden width not a multiple of 64
