@@ -2,7 +2,7 @@
 
 Mirrors the dense subset of ml/layers.spi: graph builders ``input``, ``matmul``,
 ``relu``, ``softmax``, ``masked_softmax``, ``regret_matching``,
-``masked_regret_matching``, ``argmax``, ``ln_l2`` (:347-420, 467, 482-484), the
+``masked_regret_matching``, ``argmax``, ``ln_l2``, ``matmul_ensemble`` (:347-420, 467-471, 482-484), the
 arena planner ``create_model`` (:127-172, 486-490), ``pass_init`` (:307, weights
 N(0, 0.1) as weight_init :460-463), ``key_extract`` (:321-325) and
 ``graph_run_host`` (:339-344).
@@ -56,6 +56,18 @@ def matmul(in_out, x):
     return Node("matmul", x, x.dims[:-1] + (fan_out,), fan_in=fan_in, fan_out=fan_out)
 
 
+def matmul_ensemble(ens_in_out, x):
+    """Dense layer with one weight matrix per ensemble member: ``ens_in_out`` = (members, in, out) as in
+    ``matmul_ensemble (c,b,a) x`` (ml/layers.spi:468-471: weights (c,a,b), the member picked by the
+    ``ensemble`` index the graph is run with)."""
+    members, fan_in, fan_out = (int(v) for v in ens_in_out)
+    if members < 1:
+        raise ValueError("matmul_ensemble: at least one member")
+    if x.cols != fan_in:
+        raise ValueError("matmul_ensemble: input has %d features, the layer expects %d" % (x.cols, fan_in))
+    return Node("matmul", x, x.dims[:-1] + (fan_out,), fan_in=fan_in, fan_out=fan_out, members=members)
+
+
 def relu(x):
     return Node("relu", x, x.dims)
 
@@ -103,7 +115,9 @@ class Model:
         for n in self.nodes:                      # pass_calculate_partitions, ml/layers.spi:127-172
             if n.op == "matmul":
                 n.weight_offset = sizes[WEIGHT_ID]
-                sizes[WEIGHT_ID] += _round_up(n.attrs["fan_in"] * n.attrs["fan_out"] * 4, _ALIGN)
+                member_bytes = _round_up(n.attrs["fan_in"] * n.attrs["fan_out"] * 4, _ALIGN)
+                n.attrs["member_bytes"] = member_bytes
+                sizes[WEIGHT_ID] += member_bytes * n.attrs.get("members", 1)
             n.offset = sizes[WORKSPACE_ID]
             sizes[WORKSPACE_ID] += _round_up(n.rows * (n.cols if n.op != "argmax" else 1) * 4, _ALIGN)
         self.partition_bytes = tuple(sizes)
@@ -120,8 +134,16 @@ class Model:
             return self.arenas[WORKSPACE_ID].view((node.rows,), "i32", node.offset)
         return self.arenas[WORKSPACE_ID].view((node.rows, node.cols), "f32", node.offset)
 
-    def weight(self, node):
-        return self.arenas[WEIGHT_ID].view((node.attrs["fan_out"], node.attrs["fan_in"]), "f32", node.weight_offset)
+    def weight(self, node, ensemble=0):
+        """The [out, in] weight matrix of a matmul node (of member ``ensemble`` for an ensemble layer)."""
+        members = node.attrs.get("members", 1)
+        if not 0 <= ensemble < members:
+            if members == 1:
+                ensemble = 0            # plain layers are shared by all members
+            else:
+                raise IndexError("ensemble member %d of %d" % (ensemble, members))
+        return self.arenas[WEIGHT_ID].view((node.attrs["fan_out"], node.attrs["fan_in"]), "f32",
+                                           node.weight_offset + ensemble * node.attrs["member_bytes"])
 
 
 def _round_up(x, a):
@@ -147,13 +169,14 @@ def pass_init(model, seed=CONSTANT_SEED, std=0.1):
     gen = np.random.Generator(np.random.Philox(seed))
     for n in model.nodes:
         if n.op == "matmul":
-            w = gen.normal(0.0, std, size=(n.attrs["fan_out"], n.attrs["fan_in"])).astype(np.float32)
-            model.weight(n).upload(w)
+            for e in range(n.attrs.get("members", 1)):
+                w = gen.normal(0.0, std, size=(n.attrs["fan_out"], n.attrs["fan_in"])).astype(np.float32)
+                model.weight(n, e).upload(w)
     return model
 
 
-def get_weights(model):
-    return [model.weight(n).numpy() for n in model.nodes if n.op == "matmul"]
+def get_weights(model, ensemble=0):
+    return [model.weight(n, ensemble).numpy() for n in model.nodes if n.op == "matmul"]
 
 
 def key_extract(model, key):
@@ -164,8 +187,10 @@ def key_extract(model, key):
     raise KeyError(key)
 
 
-def graph_run_host(model, stream=None):
-    """Runs the graph (ml/layers.spi:339-344) and returns the output tensor of the last node."""
+def graph_run_host(model, stream=None, ensemble=0):
+    """Runs the graph (ml/layers.spi:339-344) and returns the output tensor of the last node.
+    ``ensemble`` picks the member whose weights the ``matmul_ensemble`` layers use, as the reference's
+    ``graph_run_host model {ensemble}`` does (ml/layers.spi:623); plain layers are the same for all."""
     nodes = model.nodes
     i = 1
     while i < len(nodes):
@@ -195,7 +220,7 @@ def graph_run_host(model, stream=None):
                     m[:, :size] = 1
                     mask_dev = DeviceArray.from_numpy(m)
             out = model.tensor(last)
-            _matmul(False, True, 1.0, src, model.weight(n), 0.0, out, in_dtype=model.in_dtype,
+            _matmul(False, True, 1.0, src, model.weight(n, ensemble), 0.0, out, in_dtype=model.in_dtype,
                     epilogue=tuple(epilogue), mask=mask_dev, stream=stream)
             if mask_dev is not None:
                 _lib.call("sb_stream_sync", stream_ptr(stream))      # the mask buffer is released on return

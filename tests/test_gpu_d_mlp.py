@@ -240,3 +240,26 @@ def test_ensemble_forward_in_one_launch_equals_the_members_one_by_one(gpu, membe
     assert so.rel_frobenius(probs[members - 1], oracle) <= TOL
     with pytest.raises(gpu.SpiralError):
         gpu.EnsemblePolicyMLP([32, 96, 3], batch, 2).forward(dx, dm)        # hidden width not a multiple of 64
+
+
+def test_layer_graph_with_ensemble_layers(gpu):
+    """layers.matmul_ensemble (ml/layers.spi:468-471): one weight matrix per member, the graph run with
+    an ensemble index; every member's output follows the oracle with that member's weights."""
+    L = gpu.layers
+    members = 3
+    g = L.softmax(L.matmul_ensemble((members, 64, 8), L.relu(L.matmul_ensemble((members, 32, 64),
+                  L.input("input", (1, 256, 32))))))
+    model = L.pass_init(L.create_model(g))
+    x = so.round_tf32(so.rng(18).normal(size=(256, 32)).astype(np.float32))
+    L.key_extract(model, "input").upload(x)
+    outs = []
+    for e in range(members):
+        out = L.graph_run_host(model, ensemble=e).numpy().copy()
+        w0, w1 = [so.round_tf32(w) for w in L.get_weights(model, e)]
+        h = so.relu(so.matmul(False, True, 1.0, x, w0, 0.0, None, in_dtype="tf32"))
+        want = so.softmax(so.matmul(False, True, 1.0, h, w1, 0.0, None, in_dtype="tf32"))
+        assert so.rel_frobenius(out, want) <= TOL
+        outs.append(out)
+    assert so.rel_frobenius(outs[0], outs[1]) > 1e-2          # the members really differ
+    with pytest.raises(IndexError):
+        L.graph_run_host(model, ensemble=members)
