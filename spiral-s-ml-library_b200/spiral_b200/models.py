@@ -102,6 +102,23 @@ class PolicyMLP:
             bs.append(flat[ob:ob + self.sizes[i + 1]].copy())
         return ws, bs
 
+    def save(self, path):
+        """Checkpoint: the flat fp32 master parameter vector with the layer sizes (NumPy .npz)."""
+        np.savez(path, params=self.params.numpy(), sizes=np.asarray(self.sizes, np.int64))
+
+    def load(self, path):
+        """Restores a checkpoint written by ``save`` (same architecture) into the master parameters
+        and the compute copy."""
+        with np.load(path) as ck:
+            if [int(v) for v in ck["sizes"]] != self.sizes:
+                raise ValueError("checkpoint is for layer sizes %s, the model has %s" % (list(ck["sizes"]), self.sizes))
+            flat = np.asarray(ck["params"], np.float32)
+        if flat.shape != (self.n_params,):
+            raise ValueError("checkpoint holds %d parameters, the model %d" % (flat.size, self.n_params))
+        self.params.upload(flat)
+        self.w_compute.upload(flat)
+        return self
+
     def split_flat(self, flat):
         """Views of a flat host vector as [(W_i, b_i), ...]."""
         out = []

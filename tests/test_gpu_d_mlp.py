@@ -263,3 +263,20 @@ def test_layer_graph_with_ensemble_layers(gpu):
     assert so.rel_frobenius(outs[0], outs[1]) > 1e-2          # the members really differ
     with pytest.raises(IndexError):
         L.graph_run_host(model, ensemble=members)
+
+
+def test_checkpoint_round_trip(gpu, tmp_path):
+    sizes, batch = [32, 64, 3], 256
+    net, ws, bs = build(gpu, sizes, batch, "bf16", 77, bias_scale=0.1)
+    x, mask = so.leduc_inputs(78, batch)
+    dx, dm = gpu.to_storage(x, "bf16"), gpu.DeviceArray.from_numpy(mask)
+    want = net.forward(dx, dm).numpy().copy()
+    path = str(tmp_path / "policy.npz")
+    net.save(path)
+    other = gpu.PolicyMLP(sizes, batch, in_dtype="bf16")
+    other.load(path)
+    np.testing.assert_array_equal(other.forward(dx, dm).numpy(), want)
+    for a, b in zip(other.get_weights()[0], net.get_weights()[0]):
+        np.testing.assert_array_equal(a, b)
+    with pytest.raises(ValueError):
+        gpu.PolicyMLP([32, 128, 3], batch, in_dtype="bf16").load(path)
