@@ -151,6 +151,11 @@ int sb_row_regret_matching(const float* x, float* out, int rows, int cols, const
                            int prefix, void* stream);
 int sb_row_argmax(const float* x, int32_t* out, int rows, int cols, void* stream);
 int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream);  /* ml/primitives.spi:701-703 */
+/* Discrete sampling, local_discrete_sampling ml/primitives.spi:782-800 (the sampling heads of
+ * ml/layers.spi:422-431): out[r] = the first j with probs[r,j] > 0 and cdf[r,j] >= uniforms[r] *
+ * (cdf at the last positive entry), -1 for a row without a positive entry.  The uniform numbers in
+ * (0, 1] come from the caller (the reference draws them inside the kernel). */
+int sb_row_sample(const float* probs, const float* uniforms, int32_t* out, int rows, int cols, void* stream);
 /* Rounds fp32 to the storage type of a tensor-core input class (SB_BF16,
  * SB_F16 -> 16-bit; SB_TF32 -> fp32 with the low 13 mantissa bits cleared,
  * round-to-nearest-even). */

@@ -116,6 +116,20 @@ def argmax(x):
     return np.argmax(np.asarray(x), axis=-1).astype(np.int32)
 
 
+def discrete_sampling(x, u):
+    """local_discrete_sampling (ml/primitives.spi:782-800) with the uniform numbers u in (0, 1] given:
+    per row the first j with x[j] > 0 and cdf[j] >= u * (cdf at the last positive entry); -1 when the
+    row has no positive entry.  Sums in index order, float32."""
+    x = np.asarray(x, dtype=np.float32)
+    u = np.asarray(u, dtype=np.float32)
+    cdf = np.cumsum(x, axis=-1, dtype=np.float32)
+    pos = x > 0
+    top = np.max(np.where(pos, cdf, np.float32(0)), axis=-1).astype(np.float32)
+    ok = pos & ((cdf - (u * top)[..., None].astype(np.float32)) >= 0)
+    first = np.argmax(ok, axis=-1)
+    return np.where(ok.any(axis=-1), first, -1).astype(np.int32)
+
+
 def softmax(x):
     """local_softmax: exp(x - mean(x)) normalised  (ml/primitives.spi:711-716)."""
     x = np.asarray(x, dtype=np.float32)

@@ -216,6 +216,39 @@ encode_states_kernel(const uint8_t* __restrict__ fields, const T* __restrict__ d
   }
 }
 
+// Discrete sampling of one index per row from non-negative weights (probabilities), with the
+// caller's uniform number u in (0, 1] per row: local_discrete_sampling, ml/primitives.spi:782-800 --
+// cdf = running sum of the row, top = the cdf at the last positive entry, result = the first j
+// with x[j] > 0 and cdf[j] >= u * top; -1 for a row without a positive entry (the reference
+// returns its integer maximum there).  The reference draws u inside the kernel; here the random
+// stream stays with the caller, which makes the result a pure function of (row, u).  One thread per
+// row, sums in index order.
+__global__ void row_sample_kernel(const float* __restrict__ x, const float* __restrict__ u,
+                                  int32_t* __restrict__ out, int rows, int cols) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const float* row = x + r * cols;
+    float s = 0.f, top = 0.f;
+    for (int j = 0; j < cols; ++j) {
+      const float v = row[j];
+      s += v;
+      if (v > 0.f) top = s;
+    }
+    const float threshold = u[r] * top;
+    int pick = -1;
+    s = 0.f;
+    for (int j = 0; j < cols; ++j) {
+      const float v = row[j];
+      s += v;
+      if (v > 0.f && s - threshold >= 0.f) {
+        pick = j;
+        break;
+      }
+    }
+    out[r] = pick;
+  }
+}
+
 int grid_for(long long work_items, int per_block) {
   long long b = (work_items + per_block - 1) / per_block;
   if (b < 1) b = 1;
@@ -276,6 +309,16 @@ int sb_row_argmax(const float* x, int32_t* out, int rows, int cols, void* stream
   int rc = row_args_ok("sb_row_argmax", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   row_argmax_kernel<<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_row_sample(const float* probs, const float* uniforms, int32_t* out, int rows, int cols, void* stream) {
+  int rc = row_args_ok("sb_row_sample", probs, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  if (!uniforms) return sb_fail(SB_ERR_BAD_ARG, "sb_row_sample: uniforms is null");
+  row_sample_kernel<<<grid_for(rows, 256), 256, 0, (cudaStream_t)stream>>>(probs, uniforms, out, rows, cols);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;

@@ -98,6 +98,16 @@ def argmax(x):
     return Node("argmax", x, x.dims[:-1] + (1,))
 
 
+def masked_softmax_and_discrete_sample(size, x):
+    """Prefix-masked softmax followed by one sampled index per row (ml/layers.spi:422-431).  The node's
+    output is the int32 index tensor [..., 1]; its source node holds the probabilities.  The uniform
+    numbers come from the caller (``Model.uniforms(node).upload(u)``, one in (0, 1] per row) or, when
+    ``graph_run_host`` is given a seed, from a host Philox stream -- the reference draws them on the
+    device from its per-thread generator."""
+    probs = Node("softmax", x, x.dims, size=int(size))
+    return Node("sample", probs, x.dims[:-1] + (1,))
+
+
 class Model:
     """Planned graph + its three arenas (weights, workspace, weight adjoint), ml/layers.spi:486-502."""
 
@@ -119,7 +129,10 @@ class Model:
                 n.attrs["member_bytes"] = member_bytes
                 sizes[WEIGHT_ID] += member_bytes * n.attrs.get("members", 1)
             n.offset = sizes[WORKSPACE_ID]
-            sizes[WORKSPACE_ID] += _round_up(n.rows * (n.cols if n.op != "argmax" else 1) * 4, _ALIGN)
+            sizes[WORKSPACE_ID] += _round_up(n.rows * (n.cols if n.op not in ("argmax", "sample") else 1) * 4, _ALIGN)
+            if n.op == "sample":
+                n.attrs["uniform_offset"] = sizes[WORKSPACE_ID]
+                sizes[WORKSPACE_ID] += _round_up(n.rows * 4, _ALIGN)
         self.partition_bytes = tuple(sizes)
         self.arenas = None
 
@@ -130,9 +143,13 @@ class Model:
 
     def tensor(self, node):
         """Typed view of a node's output inside the workspace arena."""
-        if node.op == "argmax":
+        if node.op in ("argmax", "sample"):
             return self.arenas[WORKSPACE_ID].view((node.rows,), "i32", node.offset)
         return self.arenas[WORKSPACE_ID].view((node.rows, node.cols), "f32", node.offset)
+
+    def uniforms(self, node):
+        """The fp32 [rows] tensor of uniform numbers a sample node consumes."""
+        return self.arenas[WORKSPACE_ID].view((node.rows,), "f32", node.attrs["uniform_offset"])
 
     def weight(self, node, ensemble=0):
         """The [out, in] weight matrix of a matmul node (of member ``ensemble`` for an ensemble layer)."""
@@ -187,10 +204,12 @@ def key_extract(model, key):
     raise KeyError(key)
 
 
-def graph_run_host(model, stream=None, ensemble=0):
+def graph_run_host(model, stream=None, ensemble=0, seed=None):
     """Runs the graph (ml/layers.spi:339-344) and returns the output tensor of the last node.
     ``ensemble`` picks the member whose weights the ``matmul_ensemble`` layers use, as the reference's
-    ``graph_run_host model {ensemble}`` does (ml/layers.spi:623); plain layers are the same for all."""
+    ``graph_run_host model {ensemble}`` does (ml/layers.spi:623); plain layers are the same for all.
+    ``seed``: sample nodes get fresh uniform numbers from a host Philox stream of this seed (otherwise
+    they use what the caller uploaded into ``model.uniforms(node)``)."""
     nodes = model.nodes
     i = 1
     while i < len(nodes):
@@ -237,6 +256,11 @@ def graph_run_host(model, stream=None, ensemble=0):
             primitives.ln_l2(src, out, stream=stream)
         elif n.op == "argmax":
             primitives.argmax(src, out, stream=stream)
+        elif n.op == "sample":
+            if seed is not None:
+                gen = np.random.Generator(np.random.Philox(int(seed)))
+                model.uniforms(n).upload((1.0 - gen.random(n.rows, dtype=np.float32)).astype(np.float32))
+            primitives.sample(src, model.uniforms(n), out, stream=stream)
         else:
             raise ValueError("unknown node %r" % n.op)
         i += 1

@@ -53,6 +53,15 @@ def argmax(x, out, stream=None):
     return out
 
 
+def sample(probs, uniforms, out, stream=None):
+    """One index per row drawn from the row's non-negative weights with the caller's uniform numbers
+    in (0, 1] (one per row): the reference's discrete sampling head (ml/primitives.spi:782-800)."""
+    rows, cols = _rows_cols(probs)
+    _lib.call("sb_row_sample", device_ptr(probs), device_ptr(uniforms), device_ptr(out), rows, cols,
+              stream_ptr(stream))
+    return out
+
+
 def ln_l2(x, out=None, stream=None):
     out = x if out is None else out
     rows, cols = _rows_cols(x)

@@ -137,3 +137,23 @@ def test_encode_states_wide_dense_rows_and_many_rows(gpu):
     shifted = whole.view((rows, n_dense), "f32", 4)               # dense base 4 bytes off a 16-byte boundary
     P.encode_states(_dev(gpu, fields), (2,), shifted, out)
     np.testing.assert_array_equal(out.numpy(), so.encode_states(fields, (2,), dense))
+
+
+@pytest.mark.parametrize("rows,cols", [(1000, 3), (4097, 10), (64, 64)])
+def test_discrete_sampling_matches_oracle(gpu, rows, cols):
+    """sb_row_sample is a pure function of (row, u): bit-exact against the oracle, including masked
+    (zero) entries, rows of zeros and u = 1."""
+    g = so.rng(60 + cols)
+    mask = g.random((rows, cols)) < 0.7
+    mask[:, 0] |= ~mask.any(axis=1)
+    probs = so.masked_softmax(g.normal(size=(rows, cols)).astype(np.float32), mask.astype(np.uint8))
+    probs[5] = 0.0                                        # a row without a positive entry
+    u = (1.0 - g.random(rows, dtype=np.float32)).astype(np.float32)     # (0, 1]
+    u[7] = 1.0
+    out = gpu.DeviceArray((rows,), "i32")
+    gpu.primitives.sample(_dev(gpu, probs), _dev(gpu, u), out)
+    got = out.numpy()
+    np.testing.assert_array_equal(got, so.discrete_sampling(probs, u))
+    assert got[5] == -1
+    picked = got[got >= 0]
+    assert np.all(probs[got >= 0, picked] > 0)            # never an illegal (zero-weight) action

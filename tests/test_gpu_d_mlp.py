@@ -280,3 +280,25 @@ def test_checkpoint_round_trip(gpu, tmp_path):
         np.testing.assert_array_equal(a, b)
     with pytest.raises(ValueError):
         gpu.PolicyMLP([32, 128, 3], batch, in_dtype="bf16").load(path)
+
+
+def test_layer_graph_sampling_head(gpu):
+    """masked_softmax_and_discrete_sample (ml/layers.spi:422-431): indices are legal (below the prefix
+    size), follow the oracle for the uniforms in use, and change with the seed."""
+    L = gpu.layers
+    g = L.masked_softmax_and_discrete_sample(5, L.matmul((32, 8), L.input("input", (1, 512, 32))))
+    model = L.pass_init(L.create_model(g))
+    x = so.round_tf32(so.rng(28).normal(size=(512, 32)).astype(np.float32))
+    L.key_extract(model, "input").upload(x)
+    idx = L.graph_run_host(model, seed=7).numpy().copy()
+    probs = model.tensor(model.nodes[-2]).numpy()
+    u = model.uniforms(model.nodes[-1]).numpy()
+    np.testing.assert_array_equal(idx, so.discrete_sampling(probs, u))
+    assert idx.min() >= 0 and idx.max() < 5
+    w = so.round_tf32(L.get_weights(model)[0])
+    want = so.masked_softmax(so.matmul(False, True, 1.0, x, w, 0.0, None, in_dtype="tf32"), so.prefix_mask((512, 8), 5))
+    assert so.rel_frobenius(probs, want) <= TOL
+    assert (L.graph_run_host(model, seed=8).numpy() != idx).any()
+    u2 = np.full(512, 1.0, np.float32)
+    model.uniforms(model.nodes[-1]).upload(u2)                      # caller-provided uniforms: u = 1 picks the last legal action
+    np.testing.assert_array_equal(L.graph_run_host(model).numpy(), np.full(512, 4, np.int32))

@@ -134,3 +134,18 @@ def test_state_encoder_matches_the_dense_generators():
     assert np.array_equal(x2[:, 24:], (f2[:, 4:] == 0).astype(np.float32))
     tiny = so.encode_states(np.array([[1, 2], [3, 0]], np.uint8), (3, 2), np.array([[0.5], [0.25]], np.float32))
     assert np.array_equal(tiny, np.array([[0, 1, 0, 0, 0, 0.5], [0, 0, 0, 1, 0, 0.25]], np.float32))
+
+
+def test_discrete_sampling_oracle_follows_the_distribution():
+    """The sampling oracle (ml/primitives.spi:782-800) draws index j with probability x[j] / sum(x) and
+    never a zero-weight entry."""
+    p = np.array([0.1, 0.0, 0.6, 0.3, 0.0], np.float32)
+    g = so.rng(9)
+    n = 200000
+    u = (1.0 - g.random(n, dtype=np.float32)).astype(np.float32)
+    idx = so.discrete_sampling(np.tile(p, (n, 1)), u)
+    freq = np.bincount(idx, minlength=5) / n
+    assert freq[1] == 0 and freq[4] == 0
+    np.testing.assert_allclose(freq, p, atol=5e-3)
+    assert so.discrete_sampling(np.zeros((1, 4), np.float32), np.ones(1, np.float32))[0] == -1
+    assert so.discrete_sampling(p[None] * 3.0, np.array([1.0], np.float32))[0] == 3      # unnormalised weights, u = 1
