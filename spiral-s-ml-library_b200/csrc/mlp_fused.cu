@@ -233,6 +233,10 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
   const int L = p.n_layers;
+  // Set-up above touched only this CTA's shared and tensor memory; everything below reads or writes
+  // global memory and therefore waits for the kernel before it on the stream.
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -473,7 +477,7 @@ extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int
   double flops = 0.0;
   for (int l = 0; l < n_layers; ++l) flops += 2.0 * batch * (double)sizes[l] * sizes[l + 1] * members;
   sb_prof_before((cudaStream_t)stream);
-  mlp_fused_kernel<<<grid, FM_THREADS, smem, (cudaStream_t)stream>>>(maps, p);
+  SB_CUDA(sb_launch(mlp_fused_kernel, dim3(grid), dim3(FM_THREADS), smem, (cudaStream_t)stream, 1, maps, p));
   sb_prof_after((cudaStream_t)stream, flops);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
