@@ -88,6 +88,43 @@ RANK_SCRIPT = textwrap.dedent('''
     gathered = [torch.zeros_like(flat) for _ in range(world)]
     dist.all_gather(gathered, flat)
     assert all(torch.equal(gathered[0], t) for t in gathered), "replicas diverged"
+
+    # The peer-update protocol on the host: every rank reduces only its slice of the flat gradient vector
+    # (all ranks' gradients summed in rank order), updates that slice and hands it to every rank.
+    from spiral_b200.parallel import update_slice
+
+    class HostPeerUpdate:
+        overlap_layer = 0
+        def __init__(self, net): self.net = net
+        def step(self, lr, stream=None):
+            mine = self.net.grads.clone()
+            everyone = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(everyone, mine)
+            n = mine.numel()
+            n4 = (n + 3) // 4 * 4
+            b4, e4 = update_slice(n4, world, rank)
+            b4, e4 = min(b4, n), min(e4, n)
+            total = torch.zeros(e4 - b4)
+            for g in everyone:
+                total += g[b4:e4]
+            flat = np.concatenate([np.concatenate([w.ravel(), v]) for w, v in zip(self.net.w, self.net.b)])
+            new_slice = torch.from_numpy(flat[b4:e4] - lr * total.numpy())
+            sizes_ = [None] * world
+            dist.all_gather_object(sizes_, (b4, e4, new_slice))
+            for bb, ee, sl in sizes_:
+                flat[bb:ee] = sl.numpy()
+            o = 0
+            for i in range(len(self.net.w)):
+                k = self.net.w[i].size; self.net.w[i] = flat[o:o + k].reshape(self.net.w[i].shape).copy(); o += k
+                k = self.net.b[i].size; self.net.b[i] = flat[o:o + k].copy(); o += k
+
+    net2 = HostNet()
+    dp2 = DataParallel(net2, gbatch, world_size=world, rank=rank, peer_update=HostPeerUpdate(net2))
+    dp2.train_step(x[b:e], mask[b:e], target[b:e], lr)
+    for got, want in zip(net2.w + net2.b, want_w + want_b):
+        assert np.allclose(got, want, atol=1e-5), "rank %d: the sliced update disagrees with the single-process step" % rank
+    for got, ref in zip(net2.w + net2.b, net.w + net.b):
+        assert np.allclose(got, ref, atol=1e-6)
     dist.destroy_process_group()
     print("rank", rank, "ok")
 ''')
@@ -95,7 +132,8 @@ RANK_SCRIPT = textwrap.dedent('''
 
 def test_two_rank_gloo_data_parallel_step(tmp_path):
     """Sharded backward + all-reduce + SGD on 2 gloo ranks equals the single-process step, and the
-    replicas end bit-identical."""
+    replicas end bit-identical; the sliced reduce-update-redistribute protocol of the peer update
+    (every rank owns one slice, update_slice) gives the same weights."""
     script = tmp_path / "rank.py"
     script.write_text(RANK_SCRIPT)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
