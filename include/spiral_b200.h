@@ -156,6 +156,9 @@ int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream); 
  * (cdf at the last positive entry), -1 for a row without a positive entry.  The uniform numbers in
  * (0, 1] come from the caller (the reference draws them inside the kernel). */
 int sb_row_sample(const float* probs, const float* uniforms, int32_t* out, int rows, int cols, void* stream);
+/* Row hash, local_binarize ml/primitives.spi:816-821 (layers.binarize, ml/layers.spi:433-436): out[r] =
+ * (sum over j of (x[r,j] > 0) << j) mod modulo; cols <= 32. */
+int sb_row_binarize(const float* x, uint32_t* out, int rows, int cols, uint32_t modulo, void* stream);
 /* Rounds fp32 to the storage type of a tensor-core input class (SB_BF16,
  * SB_F16 -> 16-bit; SB_TF32 -> fp32 with the low 13 mantissa bits cleared,
  * round-to-nearest-even). */

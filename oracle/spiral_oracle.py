@@ -130,6 +130,14 @@ def discrete_sampling(x, u):
     return np.where(ok.any(axis=-1), first, -1).astype(np.int32)
 
 
+def binarize(x, modulo):
+    """local_binarize (ml/primitives.spi:816-821): per row the word with bit j = (x[j] > 0), modulo
+    `modulo`; rows of at most 32 values."""
+    x = np.asarray(x)
+    bits = (x > 0).astype(np.uint64) << np.arange(x.shape[-1], dtype=np.uint64)
+    return (np.sum(bits, axis=-1, dtype=np.uint64) % np.uint64(modulo)).astype(np.uint32)
+
+
 def softmax(x):
     """local_softmax: exp(x - mean(x)) normalised  (ml/primitives.spi:711-716)."""
     x = np.asarray(x, dtype=np.float32)

@@ -249,6 +249,19 @@ __global__ void row_sample_kernel(const float* __restrict__ x, const float* __re
   }
 }
 
+// Hash of a row: bit j = (x[r, j] > 0), the word taken modulo `modulo` (local_binarize,
+// ml/primitives.spi:816-821; rows of at most 32 values, where the shift is defined).
+__global__ void row_binarize_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, int rows, int cols,
+                                    uint32_t modulo) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const float* row = x + r * cols;
+    uint32_t bits = 0u;
+    for (int j = 0; j < cols; ++j) bits |= (row[j] > 0.f ? 1u : 0u) << j;
+    out[r] = bits % modulo;
+  }
+}
+
 int grid_for(long long work_items, int per_block) {
   long long b = (work_items + per_block - 1) / per_block;
   if (b < 1) b = 1;
@@ -319,6 +332,17 @@ int sb_row_sample(const float* probs, const float* uniforms, int32_t* out, int r
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   if (!uniforms) return sb_fail(SB_ERR_BAD_ARG, "sb_row_sample: uniforms is null");
   row_sample_kernel<<<grid_for(rows, 256), 256, 0, (cudaStream_t)stream>>>(probs, uniforms, out, rows, cols);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_row_binarize(const float* x, uint32_t* out, int rows, int cols, uint32_t modulo, void* stream) {
+  int rc = row_args_ok("sb_row_binarize", x, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  if (cols > 32) return sb_fail(SB_ERR_UNSUPPORTED, "sb_row_binarize: rows of at most 32 values (cols=%d)", cols);
+  if (modulo == 0u) return sb_fail(SB_ERR_BAD_ARG, "sb_row_binarize: modulo must be positive");
+  row_binarize_kernel<<<grid_for(rows, 256), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, modulo);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;

@@ -79,6 +79,7 @@ SIGNATURES = {
     "sb_row_regret_matching": (_I, [_P, _P, _I, _I, _P, _I, _P]),
     "sb_row_argmax": (_I, [_P, _P, _I, _I, _P]),
     "sb_row_sample": (_I, [_P, _P, _P, _I, _I, _P]),
+    "sb_row_binarize": (_I, [_P, _P, _I, _I, ctypes.c_uint, _P]),
     "sb_row_ln_l2": (_I, [_P, _P, _I, _I, _P]),
     "sb_convert": (_I, [_P, _P, _Z, _I, _P]),
     "sb_ipc_export": (_I, [_P, _P]),

@@ -2,7 +2,8 @@
 
 Mirrors the dense subset of ml/layers.spi: graph builders ``input``, ``matmul``,
 ``relu``, ``softmax``, ``masked_softmax``, ``regret_matching``,
-``masked_regret_matching``, ``argmax``, ``ln_l2``, ``matmul_ensemble`` (:347-420, 467-471, 482-484), the
+``masked_regret_matching``, ``argmax``, ``ln_l2``, ``matmul_ensemble``,
+``masked_softmax_and_discrete_sample``, ``binarize`` (:347-436, 467-471, 482-484), the
 arena planner ``create_model`` (:127-172, 486-490), ``pass_init`` (:307, weights
 N(0, 0.1) as weight_init :460-463), ``key_extract`` (:321-325) and
 ``graph_run_host`` (:339-344).
@@ -98,6 +99,14 @@ def argmax(x):
     return Node("argmax", x, x.dims[:-1] + (1,))
 
 
+def binarize(modulo, x):
+    """Row hash of the signs, modulo ``modulo`` (ml/layers.spi:433-436); the output keeps a trailing
+    dimension of 1 (one unsigned value per row, stored as int32)."""
+    if x.cols > 32:
+        raise ValueError("binarize: rows of at most 32 values")
+    return Node("binarize", x, x.dims[:-1] + (1,), modulo=int(modulo))
+
+
 def masked_softmax_and_discrete_sample(size, x):
     """Prefix-masked softmax followed by one sampled index per row (ml/layers.spi:422-431).  The node's
     output is the int32 index tensor [..., 1]; its source node holds the probabilities.  The uniform
@@ -129,7 +138,7 @@ class Model:
                 n.attrs["member_bytes"] = member_bytes
                 sizes[WEIGHT_ID] += member_bytes * n.attrs.get("members", 1)
             n.offset = sizes[WORKSPACE_ID]
-            sizes[WORKSPACE_ID] += _round_up(n.rows * (n.cols if n.op not in ("argmax", "sample") else 1) * 4, _ALIGN)
+            sizes[WORKSPACE_ID] += _round_up(n.rows * (n.cols if n.op not in ("argmax", "sample", "binarize") else 1) * 4, _ALIGN)
             if n.op == "sample":
                 n.attrs["uniform_offset"] = sizes[WORKSPACE_ID]
                 sizes[WORKSPACE_ID] += _round_up(n.rows * 4, _ALIGN)
@@ -143,7 +152,7 @@ class Model:
 
     def tensor(self, node):
         """Typed view of a node's output inside the workspace arena."""
-        if node.op in ("argmax", "sample"):
+        if node.op in ("argmax", "sample", "binarize"):
             return self.arenas[WORKSPACE_ID].view((node.rows,), "i32", node.offset)
         return self.arenas[WORKSPACE_ID].view((node.rows, node.cols), "f32", node.offset)
 
@@ -256,6 +265,8 @@ def graph_run_host(model, stream=None, ensemble=0, seed=None):
             primitives.ln_l2(src, out, stream=stream)
         elif n.op == "argmax":
             primitives.argmax(src, out, stream=stream)
+        elif n.op == "binarize":
+            primitives.binarize(n.attrs["modulo"], src, out, stream=stream)
         elif n.op == "sample":
             if seed is not None:
                 gen = np.random.Generator(np.random.Philox(int(seed)))

@@ -62,6 +62,16 @@ def sample(probs, uniforms, out, stream=None):
     return out
 
 
+def binarize(modulo, x, out, stream=None):
+    """Row hash: bit j = (x[r, j] > 0), modulo ``modulo`` (ml/primitives.spi:816-821); ``out`` is an int32
+    device array [rows] holding the unsigned values."""
+    import ctypes
+    rows, cols = _rows_cols(x)
+    _lib.call("sb_row_binarize", device_ptr(x), device_ptr(out), rows, cols, ctypes.c_uint(int(modulo)),
+              stream_ptr(stream))
+    return out
+
+
 def ln_l2(x, out=None, stream=None):
     out = x if out is None else out
     rows, cols = _rows_cols(x)

@@ -157,3 +157,14 @@ def test_discrete_sampling_matches_oracle(gpu, rows, cols):
     assert got[5] == -1
     picked = got[got >= 0]
     assert np.all(probs[got >= 0, picked] > 0)            # never an illegal (zero-weight) action
+
+
+@pytest.mark.parametrize("cols,modulo", [(8, 256), (20, 1000003), (32, 4294967295)])
+def test_binarize_row_hash(gpu, cols, modulo):
+    x = so.rng(70 + cols).normal(size=(777, cols)).astype(np.float32)
+    x[3] = 0.0
+    out = gpu.DeviceArray((777,), "i32")
+    gpu.primitives.binarize(modulo, _dev(gpu, x), out)
+    np.testing.assert_array_equal(out.numpy().view(np.uint32), so.binarize(x, modulo))
+    with pytest.raises(gpu.SpiralError):
+        gpu.primitives.binarize(7, gpu.DeviceArray((4, 33), "f32"), gpu.DeviceArray((4,), "i32"))

@@ -302,3 +302,18 @@ def test_layer_graph_sampling_head(gpu):
     u2 = np.full(512, 1.0, np.float32)
     model.uniforms(model.nodes[-1]).upload(u2)                      # caller-provided uniforms: u = 1 picks the last legal action
     np.testing.assert_array_equal(L.graph_run_host(model).numpy(), np.full(512, 4, np.int32))
+
+
+def test_layer_graph_binarize_head(gpu):
+    L = gpu.layers
+    g = L.binarize(1000003, L.matmul((32, 24), L.input("input", (1, 300, 32))))
+    model = L.pass_init(L.create_model(g))
+    x = so.round_tf32(so.rng(38).normal(size=(300, 32)).astype(np.float32))
+    L.key_extract(model, "input").upload(x)
+    got = L.graph_run_host(model).numpy().view(np.uint32)
+    logits = model.tensor(model.nodes[-2]).numpy()
+    np.testing.assert_array_equal(got, so.binarize(logits, 1000003))
+    w = so.round_tf32(L.get_weights(model)[0])
+    ref = so.matmul(False, True, 1.0, x, w, 0.0, None, in_dtype="tf32")
+    decided = np.all(np.abs(ref) > 5e-3, axis=1)              # rows whose signs do not hinge on TF32 rounding
+    np.testing.assert_array_equal(got[decided], so.binarize(ref, 1000003)[decided])

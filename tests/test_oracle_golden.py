@@ -149,3 +149,9 @@ def test_discrete_sampling_oracle_follows_the_distribution():
     np.testing.assert_allclose(freq, p, atol=5e-3)
     assert so.discrete_sampling(np.zeros((1, 4), np.float32), np.ones(1, np.float32))[0] == -1
     assert so.discrete_sampling(p[None] * 3.0, np.array([1.0], np.float32))[0] == 3      # unnormalised weights, u = 1
+
+
+def test_binarize_oracle():
+    x = np.array([[1.0, -1.0, 0.0, 2.0], [0.0, 0.0, 0.0, 0.0], [5.0, 5.0, 5.0, 5.0]], np.float32)
+    np.testing.assert_array_equal(so.binarize(x, 1 << 20), np.array([0b1001, 0, 0b1111], np.uint32))
+    np.testing.assert_array_equal(so.binarize(x, 7), np.array([9 % 7, 0, 15 % 7], np.uint32))
