@@ -217,15 +217,37 @@ int blocks_for(long long n, int per_block, int cap = 148 * 8) {
   return (int)(b > cap ? cap : b);
 }
 
-// Split factor of a wgrad GEMM [out, in] with inner dimension = batch.
+// Split factor of a wgrad GEMM [out, in] with inner dimension = batch.  A GEMM with more than
+// 128 output rows runs on CTA pairs (256 x 256 tiles, 74 pairs): the factor that minimises
+// (waves of work items over the pairs) / splits, plus a charge per split for the partials' write
+// and reduction -- for a 1024 x 1024 layer at a batch of 262144, 9 splits (144 items, two full
+// waves) instead of 4 (64 items on 74 pairs, 14 % of the GPU idle); at 32768 rows still 4.  Narrow outputs run on single CTAs, one item each.
 int wgrad_splits(int out, int in, int batch, int in_dtype) {
   const int es = sb_dtype_size(in_dtype);
   const int block_k = 128 / es;
   const int k_blocks = (batch + block_k - 1) / block_k;
+  const int max_by_k = k_blocks / 8 > 0 ? k_blocks / 8 : 1;  // keep >= 8 k-blocks per split
+  if (out > 128) {
+    const int tiles = ((out + 255) / 256) * ((in + 255) / 256);
+    const int workers = 148 / 2;
+    // One more split costs one more partial tile written and reduced (a few microseconds), against a
+    // full-K tile time that grows with the batch: about 4 k-blocks' worth.
+    const double per_split = 4.0 / (double)k_blocks;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 32 && s <= max_by_k; ++s) {
+      const int waves = (tiles * s + workers - 1) / workers;
+      const double cost = (double)waves / s + per_split * s;
+      if (cost < best_cost - 1e-12) {
+        best_cost = cost;
+        best = s;
+      }
+    }
+    return best;
+  }
   const int tiles = ((out + 127) / 128) * ((in + 255) / 256);
   int s = 148 / (tiles > 0 ? tiles : 1);
   if (s < 1) s = 1;
-  const int max_by_k = k_blocks / 8 > 0 ? k_blocks / 8 : 1;  // keep >= 8 k-blocks per split
   if (s > max_by_k) s = max_by_k;
   if (s > 128) s = 128;
   return s;
