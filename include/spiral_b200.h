@@ -91,6 +91,15 @@ int sb_event_destroy(void* event);
 int sb_event_record(void* event, void* stream);
 int sb_event_elapsed_ms(void* start, void* stop, float* ms);  /* syncs on stop */
 int sb_stream_wait_event(void* stream, void* event);        /* later work on stream waits for event */
+/* Host-side check of the bounded device waits: synchronises `stream`, then returns
+ * SB_ERR_DEVICE_TIMEOUT when any kernel of this library gave up a wait since the status word
+ * was last cleared (the outputs of those kernels are then incomplete), else SB_OK.  Stands
+ * where the reference learns of a failed device assert at its next synchronisation
+ * (ml/matmul/run.py:1240).  The Python host calls it at its read-back points. */
+int sb_check_device(void* stream);
+/* Free and total bytes of device memory (cudaMemGetInfo); corecuda/cupy.spi:20-58 leaves this
+ * to CuPy's memory pool. */
+int sb_mem_info(size_t* free_bytes, size_t* total_bytes);
 /* Reads (and optionally clears) the device status word written by bounded
  * waits: status[0] = first wait site that expired (0 = healthy), status[1] =
  * count of expired waits.  Synchronises the device. */
@@ -262,6 +271,14 @@ int sb_mlp_backward(int n_layers, const int* sizes, int batch, float inv_global_
                     float* grads, int with_bias, void* scratch, size_t scratch_bytes, float* loss,
                     void* stream);
 
+/* Where the backward pass keeps d(loss)/d(output of layer `layer`) inside `scratch`: byte offset
+ * of a [batch, round_up(sizes[layer+1], 8)] matrix in the storage type.  The two dY buffers
+ * alternate from layer to layer, so the matrix is intact from the moment layer `layer` has been
+ * processed until layer `layer - 2` is; a caller that runs sb_mlp_backward_range one layer at a
+ * time can inspect every layer's dY (the counterpart of reading the reference's adjoint arena,
+ * ml/layers.spi:6-12).  Used by the full-size parity tests. */
+int sb_mlp_backward_dy_offset(int n_layers, const int* sizes, int batch, int in_dtype, int layer, size_t* offset);
+
 /* The same pass restricted to layers first_layer, first_layer-1, ..., last_layer
  * (first_layer = n_layers-1 zeroes grads and computes d logits and the loss
  * first).  Successive calls that together cover n_layers-1 .. 0 equal one
@@ -316,9 +333,11 @@ int sb_dp_slice(long long begin, long long end, int world_size, int rank, long l
  * bytes leave the GPU, and a rank's master vector is current only in its own
  * slice until SB_DP_GATHER_MASTER (no gradients, no step: every owner's slice
  * is copied to all ranks) is called.  Every wait is bounded by timeout_ms; when
- * one expires the update is skipped, sb_dp_status reports 0x100 + the rank
- * that did not arrive, and the flag block must be zeroed before it is used
- * again.  barriers = 0 runs the update without either barrier (single rank, or
+ * one expires the waiting CTAs return without updating, sb_dp_status reports
+ * 0x100 + the rank that did not arrive, and the flag block must be zeroed
+ * before it is used again.  The update of that step may then be PARTIAL (a CTA
+ * that still saw the late flag has stored its part): restore the weights from a
+ * checkpoint.  barriers = 0 runs the update without either barrier (single rank, or
  * ranks ordered by the caller).  A step may be split into several calls over
  * disjoint ranges; calls that can be in flight at the same time need flag
  * blocks of their own.  max_blocks caps the grid (0 = no cap). */

@@ -2,6 +2,9 @@
 
     python oracle/build_ref.py [<reference checkout>]
 
+The checkout is named by the argument, else by the environment variable SPIRAL_REFERENCE_ROOT, else a
+directory called `reference` beside this repository is tried.
+
 The reference has no CPU implementation of this path and no hand-written CUDA: its kernels are
 Spiral-generated CUDA C++ embedded as a string in generated Python files, compiled at run time by
 CuPy.  The grid-level TF32 WMMA GEMM of tests/matmul/test1_run.py (NT layout, alpha = beta = 1,
@@ -27,8 +30,17 @@ NVCC_OPTIONS = ["-std=c++20", "-DNDEBUG", "--restrict", "--maxrregcount=255", "-
                 "--diag-suppress=550,20012,68,39,177"]
 
 
-def build(ref_root="/root/reference", force=False):
+def default_ref_root():
+    env = os.environ.get("SPIRAL_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root=None, force=False):
     """Returns the cubin path, or None when the reference checkout is absent (the GPU box)."""
+    if ref_root is None:
+        ref_root = default_ref_root()
     src_py = os.path.join(ref_root, GENERATED)
     if not os.path.exists(src_py):
         return CUBIN if os.path.exists(CUBIN) else None
@@ -54,4 +66,4 @@ def build(ref_root="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, force=True))

@@ -118,7 +118,7 @@ int sb_matmul_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, 
   if (M <= 0 || N <= 0 || K <= 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_plan: dimensions must be positive");
   if (in_dtype != SB_TF32 && in_dtype != SB_BF16 && in_dtype != SB_F16)
     return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_plan: tensor-core input classes only");
-  return sb_umma_plan(a_trans, b_trans, M, N, K, in_dtype, 148, plan5);
+  return sb_umma_plan(a_trans, b_trans, M, N, K, in_dtype, sb_sm_count(), plan5);
 }
 
 }  // extern "C"

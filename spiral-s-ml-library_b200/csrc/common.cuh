@@ -15,6 +15,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "../../include/spiral_b200.h"
 
 // ---------------------------------------------------------------------------
@@ -48,8 +50,13 @@ enum SbWaitSite : int {
 
 // Launch accounting: every kernel launch of the library goes through
 // SB_COUNT_LAUNCH so that a host can report how many kernels a region issued.
-extern unsigned long long g_sb_launch_count;
-#define SB_COUNT_LAUNCH() (++g_sb_launch_count)
+// The counter is atomic: entry points may be called from several host threads.
+void sb_count_launch();
+#define SB_COUNT_LAUNCH() sb_count_launch()
+
+// Multiprocessor count of the current device (cached per device); SB_NUM_SMS_FALLBACK when no
+// device can be asked (planning calls on a host without a GPU).
+int sb_sm_count();
 
 // Optional GEMM profiling: when enabled, the tensor-core GEMM launcher records
 // a CUDA event pair around each launch on the launching stream.
@@ -63,6 +70,8 @@ static inline int sb_dtype_size(int dt) {
     default: return 0;
   }
 }
+
+constexpr int SB_NUM_SMS_FALLBACK = 148;
 
 #ifdef __CUDACC__
 
@@ -108,7 +117,6 @@ cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-constexpr int SB_NUM_SMS_FALLBACK = 148;
 // Wall-clock limit of one device-side wait (nanoseconds of %globaltimer).
 constexpr unsigned long long SB_WAIT_LIMIT_NS = 400ull * 1000ull * 1000ull;
 

@@ -298,7 +298,7 @@ int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float*
   const long long slice_vecs = (((end - begin) >> 2) + world_size - 1) / world_size;
   long long blocks = (slice_vecs + DP_THREADS - 1) / DP_THREADS;
   if (blocks < 1) blocks = 1;
-  const long long cap = max_blocks > 0 ? max_blocks : 148 * 8;
+  const long long cap = max_blocks > 0 ? max_blocks : (long long)sb_sm_count() * 8;
   if (blocks > cap) blocks = cap;
   // A plain launch (no programmatic dependent launch): the first thing this kernel does is to tell
   // its peers that the gradients of this rank -- the work of the kernels before it -- are complete.

@@ -2,20 +2,23 @@
 // fused epilogue.  Replaces matmul_tf32_template (ml/matmul/kernel.spi:25-240,
 // nvcuda::wmma m16n16k8 TF32 with one-deep cuda::memcpy_async prefetch).
 //
-// Structure of one CTA (192 threads, persistent over output tiles):
+// Structure of one CTA (320 threads = 10 warps, persistent over output tiles):
 //   warp 0, lane 0 : TMA producer.  Per k-block it arms full[stage] with the
 //                    stage's byte count and issues plain 2-D tiled TMA loads
-//                    (128-byte swizzle) of the A and B tiles.
-//   warp 1, lane 0 : MMA issuer.  Waits full[stage], issues 4 tcgen05.mma
-//                    (M=128, N=block_n, 32 bytes of K each) on shared-memory
-//                    descriptors, commits to empty[stage]; after the last
-//                    k-block commits to tmem_full[acc].  Warp 1 also owns the
-//                    TMEM allocation.
-//   warps 2..5     : epilogue.  Wait tmem_full[acc], read the fp32 accumulator
-//                    from TMEM (tcgen05.ld, one output row per thread), apply
-//                    alpha/beta/bias/ReLU/row head, store, arrive on
-//                    tmem_empty[acc].  Two accumulators in TMEM let the
-//                    epilogue of tile i overlap the main loop of tile i+1.
+//                    (128-byte swizzle) of the A and B tiles; a stage holds one
+//                    or two 128-byte sub-blocks of K per operand.
+//   warp 1, lane 0 : MMA issuer.  Waits full[stage], issues 4 or 8 tcgen05.mma
+//                    (M=128, or 256 for a CTA pair; N=block_n; 32 bytes of K
+//                    each) on shared-memory descriptors, commits to
+//                    empty[stage]; after the last k-block commits to
+//                    tmem_full[acc].  Warp 1 also owns the TMEM allocation.
+//   warps 2..9     : epilogue, two warps per TMEM lane quadrant taking alternate
+//                    32-column chunks (or chunk pairs).  Wait tmem_full[acc],
+//                    read the fp32 accumulator from TMEM (tcgen05.ld, one output
+//                    row per thread), apply alpha/beta/bias/ReLU/row head, store
+//                    through a swizzled shared-memory box and a TMA store,
+//                    arrive on tmem_empty[acc].  Two accumulators in TMEM let
+//                    the epilogue of tile i overlap the main loop of tile i+1.
 //
 // Operand layouts.  "K-major" = the K index is contiguous in global memory
 // (A stored [M,K]; B stored [N,K]); "MN-major" = the M or N index is contiguous
@@ -28,6 +31,8 @@
 
 #include <stdlib.h>
 #include <string.h>
+
+#include <atomic>
 
 namespace {
 
@@ -1099,18 +1104,7 @@ int next_pow2(int x) {
   return p;
 }
 
-int cached_sm_count() {
-  static int sms[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SB_NUM_SMS_FALLBACK;
-  if (sms[dev] == 0) {
-    int v = 0;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-      v = SB_NUM_SMS_FALLBACK;
-    sms[dev] = v;
-  }
-  return sms[dev];
-}
+int cached_sm_count() { return sb_sm_count(); }
 
 // Chooses block_n / stages / grid for a problem; `sms` = SM count to plan for.
 // `allow_pair`: CTA pairs may be used (needs at least two 128-row blocks and a
@@ -1295,15 +1289,15 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     p.tma_store = 1;
   }
   const size_t smem = umma_dyn_smem(p);
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {   // setting it twice is harmless
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   sb_prof_before(stream);
   if (!p.pair) {
@@ -1340,7 +1334,8 @@ int sb_umma_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, in
 int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStream_t stream) {
   if (total <= 0) return SB_OK;
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long long cap = (long long)sb_sm_count() * 8;
+  if (blocks > cap) blocks = cap;
   scale_rows_kernel<<<(int)blocks, 256, 0, stream>>>(C, total, beta, out_dtype);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());

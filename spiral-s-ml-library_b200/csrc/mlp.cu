@@ -211,7 +211,8 @@ __global__ void sgd_kernel(float* __restrict__ params, const float* __restrict__
   }
 }
 
-int blocks_for(long long n, int per_block, int cap = 148 * 8) {
+int blocks_for(long long n, int per_block, int cap = 0) {
+  if (cap <= 0) cap = sb_sm_count() * 8;
   long long b = (n + per_block - 1) / per_block;
   if (b < 1) b = 1;
   return (int)(b > cap ? cap : b);
@@ -229,7 +230,7 @@ int wgrad_splits(int out, int in, int batch, int in_dtype) {
   const int max_by_k = k_blocks / 8 > 0 ? k_blocks / 8 : 1;  // keep >= 8 k-blocks per split
   if (out > 128) {
     const int tiles = ((out + 255) / 256) * ((in + 255) / 256);
-    const int workers = 148 / 2;
+    const int workers = sb_sm_count() / 2;
     // One more split costs one more partial tile written and reduced (a few microseconds), against a
     // full-K tile time that grows with the batch: about 4 k-blocks' worth.
     const double per_split = 4.0 / (double)k_blocks;
@@ -246,7 +247,7 @@ int wgrad_splits(int out, int in, int batch, int in_dtype) {
     return best;
   }
   const int tiles = ((out + 127) / 128) * ((in + 255) / 256);
-  int s = 148 / (tiles > 0 ? tiles : 1);
+  int s = sb_sm_count() / (tiles > 0 ? tiles : 1);
   if (s < 1) s = 1;
   if (s > max_by_k) s = max_by_k;
   if (s > 128) s = 128;
@@ -397,6 +398,18 @@ int sb_mlp_backward_scratch_bytes(int n_layers, const int* sizes, int batch, int
   return SB_OK;
 }
 
+int sb_mlp_backward_dy_offset(int n_layers, const int* sizes, int batch, int in_dtype, int layer, size_t* offset) {
+  if (!offset) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward_dy_offset: null output");
+  int rc = check_layout("sb_mlp_backward_dy_offset", n_layers, sizes, batch, in_dtype);
+  if (rc != SB_OK) return rc;
+  if (layer < 0 || layer >= n_layers) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward_dy_offset: layer %d of %d", layer, n_layers);
+  int max_w = 0;
+  for (int i = 0; i < n_layers; ++i) max_w = max(max_w, padded_out(sizes[i + 1]));
+  const size_t dy_bytes = (size_t)align_up((long long)batch * max_w * sb_dtype_size(in_dtype), 256);
+  *offset = ((n_layers - 1 - layer) & 1) ? dy_bytes : 0;
+  return SB_OK;
+}
+
 int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
                           const void* x, const void* w_compute, void* const* activations,
                           void* const* relu_bits, const float* probs, const uint8_t* mask,
@@ -481,7 +494,7 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
       // Enough blocks to fill the GPU a few times over, each with a long row slab.
       const int strip = 32 * (16 / es);
       const int strips = (fan_out + strip - 1) / strip;
-      int slabs = (148 * 4 + strips - 1) / strips;
+      int slabs = (sb_sm_count() * 4 + strips - 1) / strips;
       int rows_per_block = (batch + slabs - 1) / slabs;
       if (rows_per_block < 64) rows_per_block = 64;
       dim3 grid(strips, (batch + rows_per_block - 1) / rows_per_block);

@@ -463,16 +463,15 @@ extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int
   p.out = out; p.mask = mask; p.actions = actions; p.head = head;
   const size_t smem = (size_t)p.w_offset + (size_t)FM_W_STAGES * FM_STAGE_BYTES + 1024;
 
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   SB_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     SB_CUDA(cudaFuncSetAttribute(mlp_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   if (smem > 225 * 1024) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: %zu bytes of shared memory needed", smem);
-  int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sb_sm_count();
   const int grid = p.num_items < sms ? p.num_items : sms;
   double flops = 0.0;
   for (int l = 0; l < n_layers; ++l) flops += 2.0 * batch * (double)sizes[l] * sizes[l + 1] * members;

@@ -265,7 +265,7 @@ __global__ void row_binarize_kernel(const float* __restrict__ x, uint32_t* __res
 int grid_for(long long work_items, int per_block) {
   long long b = (work_items + per_block - 1) / per_block;
   if (b < 1) b = 1;
-  const long long cap = 148LL * 16;
+  const long long cap = (long long)sb_sm_count() * 16;
   return (int)(b > cap ? cap : b);
 }
 

@@ -8,12 +8,32 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+
 static thread_local char t_error[512] = "";
 
-unsigned long long g_sb_launch_count = 0;
+static std::atomic<unsigned long long> g_sb_launch_count{0};
+void sb_count_launch() { g_sb_launch_count.fetch_add(1, std::memory_order_relaxed); }
+
+int sb_sm_count() {
+  static std::atomic<int> sms[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SB_NUM_SMS_FALLBACK;
+  int v = sms[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      v = SB_NUM_SMS_FALLBACK;
+    sms[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
 
 namespace {
 constexpr int PROF_MAX = 4096;
+// The GEMM profile is one process-wide recording: begin/end and the per-launch hooks take this lock,
+// so launches from several host threads are recorded whole (in the order the lock is won).
+std::mutex g_prof_lock;
 bool g_prof_on = false;
 int g_prof_n = 0;
 cudaEvent_t g_prof_ev[2 * PROF_MAX];
@@ -32,16 +52,28 @@ bool sb_pdl_enabled() {
   return v == 1;
 }
 
+// before/after bracket one launch: `before` takes the lock when a profile is being recorded and
+// `after` releases it, so two threads' event pairs cannot interleave.
+static thread_local bool t_prof_held = false;
+
 void sb_prof_before(cudaStream_t s) {
-  if (!g_prof_on || g_prof_n >= PROF_MAX) return;
+  if (!g_prof_on) return;
+  g_prof_lock.lock();
+  if (!g_prof_on || g_prof_n >= PROF_MAX) {
+    g_prof_lock.unlock();
+    return;
+  }
+  t_prof_held = true;
   cudaEventRecord(g_prof_ev[2 * g_prof_n], s);
 }
 
 void sb_prof_after(cudaStream_t s, double flops) {
-  if (!g_prof_on || g_prof_n >= PROF_MAX) return;
+  if (!t_prof_held) return;
   cudaEventRecord(g_prof_ev[2 * g_prof_n + 1], s);
   g_prof_flops[g_prof_n] = flops;
   ++g_prof_n;
+  t_prof_held = false;
+  g_prof_lock.unlock();
 }
 
 void sb_set_error(const char* fmt, ...) {
@@ -209,9 +241,16 @@ int sb_event_elapsed_ms(void* start, void* stop, float* ms) {
   return SB_OK;
 }
 
-unsigned long long sb_launch_count(void) { return g_sb_launch_count; }
+unsigned long long sb_launch_count(void) { return g_sb_launch_count.load(std::memory_order_relaxed); }
+
+int sb_mem_info(size_t* free_bytes, size_t* total_bytes) {
+  if (!free_bytes || !total_bytes) return sb_fail(SB_ERR_BAD_ARG, "sb_mem_info: null output");
+  SB_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+  return SB_OK;
+}
 
 int sb_gemm_profile_begin(void) {
+  std::lock_guard<std::mutex> hold(g_prof_lock);
   if (!g_prof_ev_made) {
     for (int i = 0; i < 2 * PROF_MAX; ++i) SB_CUDA(cudaEventCreate(&g_prof_ev[i]));
     g_prof_ev_made = true;
@@ -222,6 +261,7 @@ int sb_gemm_profile_begin(void) {
 }
 
 int sb_gemm_profile_end(int* launches, double* total_ms, double* total_flops) {
+  std::lock_guard<std::mutex> hold(g_prof_lock);
   g_prof_on = false;
   double ms = 0.0, fl = 0.0;
   for (int i = 0; i < g_prof_n; ++i) {
@@ -241,6 +281,7 @@ int sb_gemm_profile_end(int* launches, double* total_ms, double* total_flops) {
 }
 
 int sb_gemm_profile_entry(int index, double* ms, double* flops) {
+  std::lock_guard<std::mutex> hold(g_prof_lock);
   if (index < 0 || index >= g_prof_last_n || !ms || !flops)
     return sb_fail(SB_ERR_BAD_ARG, "sb_gemm_profile_entry: index %d outside the last profile of %d launches", index, g_prof_last_n);
   *ms = g_prof_ms[index];
@@ -259,6 +300,18 @@ int sb_device_status(int* status2, int clear) {
     int zero[4] = {0, 0, 0, 0};
     SB_CUDA(cudaMemcpyToSymbol(g_sb_status, zero, sizeof(zero)));
   }
+  return SB_OK;
+}
+
+int sb_check_device(void* stream) {
+  SB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  int host[4] = {0, 0, 0, 0};
+  SB_CUDA(cudaMemcpyFromSymbol(host, g_sb_status, sizeof(host)));
+  if (host[0] != 0 || host[1] != 0)
+    return sb_fail(SB_ERR_DEVICE_TIMEOUT,
+                   "a bounded device-side wait expired (first wait site %d, %d waits in all): the kernels that were "
+                   "running gave up and their outputs are incomplete; read the details with sb_device_status",
+                   host[0], host[1]);
   return SB_OK;
 }
 

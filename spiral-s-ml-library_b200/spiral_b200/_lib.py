@@ -66,6 +66,8 @@ SIGNATURES = {
     "sb_stream_wait_event": (_I, [_P, _P]),
     "sb_event_elapsed_ms": (_I, [_P, _P, POINTER(c_float)]),
     "sb_device_status": (_I, [_IP, _I]),
+    "sb_check_device": (_I, [_P]),
+    "sb_mem_info": (_I, [POINTER(c_size_t), POINTER(c_size_t)]),
     "sb_selftest_bounded_wait": (_I, [_IP]),
     "sb_launch_count": (ctypes.c_ulonglong, []),
     "sb_gemm_profile_begin": (_I, []),
@@ -98,6 +100,7 @@ SIGNATURES = {
     "sb_mlp_forward_static": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_backward_scratch_bytes": (_I, [_I, _IP, _I, _I, POINTER(c_size_t)]),
     "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),
+    "sb_mlp_backward_dy_offset": (_I, [_I, _IP, _I, _I, _I, POINTER(c_size_t)]),
     "sb_mlp_backward_range": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _I, _I, _P]),
     "sb_sgd_update": (_I, [_P, _P, _P, ctypes.c_longlong, _F, _I, _P]),
     "sb_mlp_train_step": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _F, _P, _Z, _P, _P]),

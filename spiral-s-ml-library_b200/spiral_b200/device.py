@@ -33,6 +33,19 @@ def synchronize():
     _lib.call("sb_device_sync")
 
 
+def mem_info():
+    """(free, total) bytes of device memory on the current device."""
+    free, total = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    _lib.call("sb_mem_info", ctypes.byref(free), ctypes.byref(total))
+    return free.value, total.value
+
+
+def check_device(stream=None):
+    """Synchronises ``stream`` and raises SpiralError (SB_ERR_DEVICE_TIMEOUT) if a bounded device-side
+    wait expired since the status word was last cleared."""
+    _lib.call("sb_check_device", stream_ptr(stream))
+
+
 def device_status(clear=True):
     """(first expired wait site, number of expired waits); (0, 0) when healthy."""
     st = (ctypes.c_int * 2)()
@@ -90,8 +103,8 @@ class DeviceArray:
         host = self._host_storage(array)
         if host.size != self.size:
             raise ValueError("upload of %d elements into a buffer of %d" % (host.size, self.size))
-        _lib.call("sb_memcpy_h2d", self.ptr, host.ctypes.data, host.nbytes, stream)
-        _lib.call("sb_stream_sync", stream)
+        _lib.call("sb_memcpy_h2d", self.ptr, host.ctypes.data, host.nbytes, stream_ptr(stream))
+        _lib.call("sb_stream_sync", stream_ptr(stream))
         return self
 
     def fill_zero(self, stream=None):
@@ -102,8 +115,10 @@ class DeviceArray:
     def numpy(self, stream=None):
         """Downloads; 16-bit float storage comes back widened to fp32."""
         host = np.empty(self.shape, dtype=_NP_STORAGE[self.dtype])
-        _lib.call("sb_memcpy_d2h", host.ctypes.data, self.ptr, host.nbytes, stream)
-        _lib.call("sb_stream_sync", stream)
+        _lib.call("sb_memcpy_d2h", host.ctypes.data, self.ptr, host.nbytes, stream_ptr(stream))
+        # Synchronises, and raises SpiralError(SB_ERR_DEVICE_TIMEOUT) when a kernel gave up a bounded
+        # wait: what was just read may then be incomplete.
+        _lib.call("sb_check_device", stream_ptr(stream))
         if self.dtype == "bf16":
             return dtypes.bf16_bits_to_f32(host).reshape(self.shape)
         if self.dtype == "f16":

@@ -55,7 +55,7 @@ class PolicyMLP:
         self.probs = DeviceArray((self.batch, self.sizes[-1]), "f32")
         self.actions = DeviceArray((self.batch,), "i32") if "argmax" in self.head else None
         self.training = bool(training)
-        # ReLU sign bits of every hidden layer (uint32 [batch, width / 32]): recorded by the
+        # ReLU sign bits of every hidden layer (uint32 [width / 32, batch], column-block-major): recorded by the
         # forward pass when training so that backward gates by bits instead of re-reading H.
         self.relu_bits = []
         self._bits_c = None
@@ -185,6 +185,16 @@ class PolicyMLP:
                   self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, int(first_layer), int(last_layer),
                   stream_ptr(stream))
         return self.grads
+
+    def layer_dy(self, layer):
+        """View of d(loss)/d(output of layer ``layer``) inside the backward scratch: [batch, width padded
+        to 8] in the storage type.  Valid after ``backward_layers`` has processed ``layer`` and until it
+        processes ``layer - 2`` (the two dY buffers alternate)."""
+        off = ctypes.c_size_t(0)
+        _lib.call("sb_mlp_backward_dy_offset", self.n_layers, self._sizes_c, self.batch,
+                  _lib.DTYPE_CODES[self.in_dtype], int(layer), ctypes.byref(off))
+        width = (self.sizes[layer + 1] + 7) // 8 * 8
+        return self.scratch.view((self.batch, width), self.storage, off.value)
 
     def layer_segment(self, layer):
         """[begin, end) of layer `layer`'s weights and bias inside the flat parameter / gradient vectors."""

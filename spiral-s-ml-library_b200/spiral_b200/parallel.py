@@ -114,6 +114,16 @@ class PeerUpdate:
         _lib.call("sb_dp_status", self.flags.ptr, ctypes.byref(out))
         return out.value
 
+    def check(self):
+        """Raises SpiralError (SB_ERR_DEVICE_TIMEOUT) when a flag wait of this rank's update kernel gave
+        up.  The update of that step may then be partial (some CTAs may have seen the late flag and
+        stored their part): restore the weights from a checkpoint and zero the flag block before the
+        next step.  Synchronises the device."""
+        code = self.status()
+        if code != 0:
+            raise _lib.SpiralError(-5, "the peer update gave up waiting for rank %d (status 0x%x); the weights of "
+                                   "this step may be partly updated" % (code - 0x100, code))
+
     def close(self):
         for ptr in self._opened:
             _lib.call("sb_ipc_close", ptr)

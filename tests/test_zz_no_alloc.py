@@ -31,7 +31,14 @@ def test_no_alloc_forward_matches_workspace_forward_twice(gpu):
         want = net.forward(dx, dm).numpy()
         want_actions = net.actions.numpy()
         out.fill_zero()
-        got = net.forward_no_alloc(dx, out, dm, actions=actions).numpy()
+        gpu.synchronize()
+        free_before = gpu.mem_info()[0]
+        net.forward_no_alloc(dx, out, dm, actions=actions)
+        gpu.synchronize()
+        # The call took no device memory: the free-memory reading is the same before and after
+        # (the first call's one-time set-up -- symbol address, kernel attributes -- allocates nothing either).
+        assert gpu.mem_info()[0] == free_before
+        got = out.numpy()
         assert so.rel_frobenius(got, want) <= TOL
         np.testing.assert_array_equal(actions.numpy(), want_actions)
         oracle = so.mlp_forward(x, ws, bs, mask, in_dtype="f16", act_dtype="f16",
