@@ -40,8 +40,9 @@ typedef enum sb_dtype { SB_F32 = 0, SB_TF32 = 1, SB_BF16 = 2, SB_F16 = 3, SB_I32
  *   v = alpha * acc + beta * C_old ; v += bias[col] ; v = relu(v) ;
  *   v = (aux_in[row,col] > 0) ? v : 0   (RELU_GRAD) ;
  *   row head: masked softmax, then regret matching, then argmax.
- * Row heads are fused into the GEMM for N <= 32 and run as a second kernel on
- * C for wider rows. */
+ *   row head: sign hash, masked softmax, then regret matching, then argmax and sampling.
+ * Row heads are fused into the GEMM for N <= 64 (and for N <= 256 under a prefix mask of at
+ * most 64 columns) and run as further kernels on C for wider rows. */
 enum {
   SB_EPI_NONE = 0,
   SB_EPI_BIAS = 1,            /* bias: fp32[N] */
@@ -62,8 +63,36 @@ enum {
    * alpha == 1, beta == 0, tensor-core classes; combines only with
    * SB_EPI_RELU_GRAD_MASK.  The additions are atomic: their order, hence the
    * last bits of the sums, can differ between runs. */
-  SB_EPI_COLSUM_OUT = 256
+  SB_EPI_COLSUM_OUT = 256,
+  /* The next three are given through sb_matmul_head / sb_head_spec. */
+  SB_EPI_SAMPLE = 512,        /* ml/primitives.spi:782-800: one index per row drawn from the finished row */
+  SB_EPI_BINARIZE = 1024,     /* ml/primitives.spi:816-821: sign hash of the logits (N <= 32) */
+  /* x / sum(x^2) over the whole row (local_ln_l2, ml/primitives.spi:701-703), applied before the
+   * ReLU: the reference's test nets put ln_l2 between every matmul and relu
+   * (ml/layers.spi:562-568).  N <= 256, alpha == 1, beta == 0, no bias, tensor-core classes. */
+  SB_EPI_LN_L2 = 2048
 };
+
+/* A row head with everything it may need.  `flags`: SB_EPI_MASKED_SOFTMAX, SB_EPI_REGRET_MATCHING,
+ * SB_EPI_ARGMAX, SB_EPI_SAMPLE, SB_EPI_BINARIZE.  Legal columns: j < prefix when prefix >= 0 (the way
+ * layers.masked_softmax / masked_regret_matching / masked_softmax_and_discrete_sample instantiate
+ * their mask, ml/layers.spi:409,416,426), else mask[row, j] != 0, else all.  Sampling draws, for row
+ * r, output number `position` of the Philox4x32-10 stream (key = seed, subsequence = row_offset + r)
+ * -- the generator the reference initialises per thread with curand_init(seed, thread index, 0)
+ * (corecuda/random.spi:22-24) -- as a uniform number in (0, 1] (corecuda/random.spi:84), and takes the
+ * first j with a positive weight and cdf[j] >= u * total; -1 for a row without a positive weight. */
+typedef struct sb_head_spec {
+  int flags;
+  int prefix;                    /* -1: no prefix mask */
+  const uint8_t* mask;           /* uint8 [rows, N] or NULL */
+  int32_t* argmax_out;           /* int32 [rows], SB_EPI_ARGMAX */
+  int32_t* sample_out;           /* int32 [rows], SB_EPI_SAMPLE */
+  uint32_t* hash_out;            /* uint32 [rows], SB_EPI_BINARIZE */
+  uint32_t modulo;               /* SB_EPI_BINARIZE: the hash is taken modulo this (> 0) */
+  unsigned long long seed;
+  unsigned long long row_offset;
+  unsigned long long position;
+} sb_head_spec;
 
 /* ---- runtime ------------------------------------------------------------ */
 const char* sb_last_error_string(void);
@@ -142,6 +171,16 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
                  const float* bias, const uint8_t* mask, const void* aux_in, void* aux_out,
                  void* stream);
 
+/* The dense layer with a row head described by `head` (ml/layers.spi:408-436 on top of :227-240):
+ * C <- head(alpha * op(A) * op(B) + beta * C (+ bias) (ReLU)), fp32 output.  `epilogue` may hold
+ * SB_EPI_BIAS, SB_EPI_RELU and SB_EPI_LN_L2; the head flags come from head->flags.  One launch when
+ * N <= 64, or N <= 256 with 0 <= prefix <= 64 (the reference's policy nets end in 64 columns of
+ * which the first few are legal, game/leduc/model_cem.spi:37,52-60); wider rows run the head as
+ * further kernels on C.  Nothing is allocated and no mask matrix is needed for a prefix. */
+int sb_matmul_head(int a_trans, int b_trans, float alpha, const void* A, const void* B, float beta,
+                   float* C, int M, int N, int K, int in_dtype, int epilogue, const float* bias,
+                   const sb_head_spec* head, void* stream);
+
 /* Tile-shape heuristic of the tensor-core path, exposed for tests: the
  * counterpart of matmul_config_tf32 (ml/matmul/run.spi:8-19).  Writes
  * {block_m, block_n, block_k_elems, stages, grid}. */
@@ -165,6 +204,14 @@ int sb_row_ln_l2(const float* x, float* out, int rows, int cols, void* stream); 
  * (cdf at the last positive entry), -1 for a row without a positive entry.  The uniform numbers in
  * (0, 1] come from the caller (the reference draws them inside the kernel). */
 int sb_row_sample(const float* probs, const float* uniforms, int32_t* out, int rows, int cols, void* stream);
+/* The same with the uniform numbers drawn on the device, as the reference does: row r uses output
+ * number `position` of the Philox4x32-10 stream (seed, row_offset + r), see sb_head_spec. */
+int sb_row_sample_seeded(const float* probs, int32_t* out, int rows, int cols, unsigned long long seed,
+                         unsigned long long row_offset, unsigned long long position, void* stream);
+/* The uniform numbers themselves (fp32 [n], each in (0, 1]): element i = output `position` of stream
+ * (seed, row_offset + i).  For callers and tests that want to see what a sampling head drew. */
+int sb_philox_uniform(float* out, long long n, unsigned long long seed, unsigned long long row_offset,
+                      unsigned long long position, void* stream);
 /* Row hash, local_binarize ml/primitives.spi:816-821 (layers.binarize, ml/layers.spi:433-436): out[r] =
  * (sum over j of (x[r,j] > 0) << j) mod modulo; cols <= 32. */
 int sb_row_binarize(const float* x, uint32_t* out, int rows, int cols, uint32_t modulo, void* stream);
@@ -221,7 +268,7 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
  * policy MLP): hidden activations stay in shared memory / TMEM, so no activations
  * buffer is needed.  Replaces the same reference chain (ml/layers.py:4500-4546).
  * Limits: in_dtype SB_F16 or SB_BF16; sizes[0] in 8..256 and a multiple of 8;
- * hidden widths multiples of 64 up to 256; sizes[n_layers] <= 32; n_layers <= 8;
+ * hidden widths multiples of 64 up to 256; sizes[n_layers] <= 64; n_layers <= 8;
  * otherwise SB_ERR_UNSUPPORTED (use sb_mlp_forward). */
 int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
                          const void* w_compute, const float* params, int head, const uint8_t* mask,
@@ -236,6 +283,61 @@ int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype
 int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
                                   const void* x, const void* w_compute, const float* params, int head,
                                   const uint8_t* mask, float* out, int32_t* actions, void* stream);
+
+/* The fused ensemble forward with the head given as an sb_head_spec and the reference's other
+ * graph pieces: hidden_norm = 1 puts ln_l2 (x / sum(x^2) over the row, ml/primitives.spi:701-703)
+ * before every ReLU as the reference's nets do (ml/layers.spi:594-603; then params must be NULL:
+ * those nets have no bias); the head may be prefix-masked (ml/layers.spi:409,416) and may sample
+ * (SB_EPI_SAMPLE, ml/layers.spi:422-431): member e draws output number head->position + e of the row's
+ * stream, the way the reference's per-thread generator advances from one member's run to the next
+ * (ml/models.spi:47-49).  Output widths up to 64, or up to 256 under a prefix of at most 64 columns
+ * (game/leduc/model_cem.spi:37,52-60: 64 columns, 3 legal).  head->argmax_out / sample_out are
+ * int32 [members, batch]; out is fp32 [members, batch, n_out].  No sign hash here. */
+int sb_mlp_forward_fused_head(int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                              const void* x, const void* w_compute, const float* params, int hidden_norm,
+                              const sb_head_spec* head, float* out, void* stream);
+
+/* One policy decision per game state, the whole of models.noinline_run (ml/models.spi:9-76): the states
+ * are serialised into the input tensor on the device (sb_encode_states; fields == NULL: x already holds
+ * the input), every ensemble member's net runs on them, each member samples an action per state from
+ * its head, a member is drawn per state, and the call reports that member's action together with the
+ * probability the drawn member gave it (sampling_prob_selected) and the probability EVERY member gave
+ * it (sampling_prob_ensemble) -- what the reference returns as {action, sampling_prob_selected,
+ * sampling_prob_ensemble} and leaves in its output_probs / output_indices tensors.  Two launches:
+ * the encoder and one fused kernel (nets within the limits of sb_mlp_forward_fused_head).
+ * Random stream of state r: Philox4x32-10 (seed, row_offset + r); outputs 0 .. members-1 are the
+ * members' sampling draws, the outputs from `members` on pick the member (unbiased rejection,
+ * corecuda/random.spi:53-59).  tile_counters: int32 [ceil(rows / 128)] that the caller zeroes once;
+ * every call leaves it zero again.  Calls that overlap on the GPU need counters of their own. */
+typedef struct sb_decide_args {
+  int n_layers;
+  const int* sizes;              /* HOST: n_layers + 1 widths */
+  int members;
+  int in_dtype;                  /* SB_F16 or SB_BF16 */
+  const void* w_compute;         /* members' flat parameter vectors, one after the other */
+  const float* params;           /* fp32 copies for the biases, or NULL: no bias */
+  int hidden_norm;               /* 1: ln_l2 before every ReLU (params must be NULL) */
+  long long rows;
+  const uint8_t* fields;         /* uint8 [rows, n_fields] or NULL */
+  int n_fields;
+  const int* widths;             /* HOST */
+  const void* dense;             /* [rows, n_dense] in the storage type, or NULL */
+  int n_dense;
+  void* x;                       /* [rows, sizes[0]] storage type: the network input (written when fields != NULL) */
+  int head_flags;                /* SB_EPI_MASKED_SOFTMAX and / or SB_EPI_REGRET_MATCHING */
+  int prefix;                    /* legal iff column < prefix; -1: use mask (or all) */
+  const uint8_t* mask;           /* uint8 [rows, n_out] or NULL */
+  unsigned long long seed;
+  unsigned long long row_offset;
+  float* output_probs;           /* fp32 [members, rows, n_out] */
+  int32_t* output_indices;       /* int32 [members, rows] */
+  int32_t* ensemble_id;          /* int32 [rows]: the member drawn for each state */
+  int32_t* action;               /* int32 [rows] */
+  float* sampling_prob_selected; /* fp32 [rows] */
+  float* sampling_prob_ensemble; /* fp32 [rows, members] */
+  int32_t* tile_counters;        /* int32 [ceil(rows / 128)], zero */
+} sb_decide_args;
+int sb_policy_decide(const sb_decide_args* args, void* stream);
 
 /* The same forward pass for callers that cannot allocate device memory (a host
  * that owns no allocator, a plugin in a context where allocation is forbidden,

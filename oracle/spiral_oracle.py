@@ -130,6 +130,70 @@ def discrete_sampling(x, u):
     return np.where(ok.any(axis=-1), first, -1).astype(np.int32)
 
 
+# Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC 2011), the
+# generator behind the reference's per-thread cuRAND state (curandStatePhilox4_32_10_t,
+# corecuda/random.spi:9-24).  Pinned by the paper's known-answer vectors in tests/test_oracle_golden.py.
+_PHILOX_M0, _PHILOX_M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+_PHILOX_W0, _PHILOX_W1 = 0x9E3779B9, 0xBB67AE85
+_U32 = np.uint64(0xFFFFFFFF)
+
+
+def philox4x32_10(counter, key):
+    """One block per element: `counter` = four arrays (or ints) of 32-bit words, `key` = two ints.
+    Returns four uint32 arrays."""
+    c = [np.asarray(x, dtype=np.uint64) & _U32 for x in counter]
+    k0, k1 = int(key[0]) & 0xFFFFFFFF, int(key[1]) & 0xFFFFFFFF
+    for _ in range(10):
+        p0, p1 = _PHILOX_M0 * c[0], _PHILOX_M1 * c[2]
+        hi0, lo0 = p0 >> np.uint64(32), p0 & _U32
+        hi1, lo1 = p1 >> np.uint64(32), p1 & _U32
+        c = [hi1 ^ c[1] ^ np.uint64(k0), lo1, hi0 ^ c[3] ^ np.uint64(k1), lo0]
+        k0, k1 = (k0 + _PHILOX_W0) & 0xFFFFFFFF, (k1 + _PHILOX_W1) & 0xFFFFFFFF
+    return [x.astype(np.uint32) for x in c]
+
+
+def philox_u32(seed, subsequence, position):
+    """32-bit output number `position` of the stream (seed, subsequence): key = the 64-bit seed, counter =
+    (position // 4 as 64 bits, subsequence as 64 bits), word position % 4 of the block -- the layout of
+    curand_init(seed, subsequence, offset) followed by `position - offset` draws.  `subsequence` may be
+    an array (one stream per row)."""
+    sub = np.asarray(subsequence, dtype=np.uint64)
+    pos = np.broadcast_to(np.asarray(position, dtype=np.uint64), sub.shape)
+    block = pos >> np.uint64(2)
+    words = philox4x32_10([block & _U32, block >> np.uint64(32), sub & _U32, sub >> np.uint64(32)],
+                          [int(seed) & 0xFFFFFFFF, (int(seed) >> 32) & 0xFFFFFFFF])
+    which = (pos & np.uint64(3)).astype(np.int64)
+    return np.choose(which, words).astype(np.uint32)
+
+
+def uniform_open_closed(x):
+    """A 32-bit draw as a float32 in (0, 1]: x * 2^-32 + 2^-33 rounded once, the mapping of
+    curand_uniform (corecuda/random.spi:84: "an uniform value in the (0,1] range")."""
+    xf = np.asarray(x, dtype=np.uint32).astype(np.float32).astype(np.float64)
+    return (xf * 2.0 ** -32 + 2.0 ** -33).astype(np.float32)
+
+
+def philox_uniform(seed, subsequence, position):
+    return uniform_open_closed(philox_u32(seed, subsequence, position))
+
+
+def philox_below(seed, subsequence, position, bound):
+    """Unbiased integers in [0, bound) by rejection (corecuda/random.spi:53-59: draw r, x = r mod bound,
+    accept when r - x <= 2^32 - bound), draws taken at position, position + 1, ...; at most 8 tries."""
+    sub = np.asarray(subsequence, dtype=np.uint64)
+    out = np.zeros(sub.shape, dtype=np.uint32)
+    done = np.zeros(sub.shape, dtype=bool)
+    for attempt in range(8):
+        r = philox_u32(seed, sub, np.uint64(position + attempt)).astype(np.uint64)
+        x = r % np.uint64(bound)
+        ok = (r - x) <= np.uint64(2 ** 32 - bound)
+        out = np.where(done, out, x.astype(np.uint32))
+        done = done | ok
+        if done.all():
+            break
+    return out.astype(np.int32)
+
+
 def binarize(x, modulo):
     """local_binarize (ml/primitives.spi:816-821): per row the word with bit j = (x[j] > 0), modulo
     `modulo`; rows of at most 32 values."""
@@ -232,6 +296,48 @@ def mlp_forward(x, weights, biases=None, mask=None, in_dtype="f32", head=("maske
     if return_activations:
         return out, acts
     return out
+
+
+def ensemble_forward(x, member_weights, member_biases=None, mask=None, in_dtype="f32", head=("masked_softmax",),
+                     hidden_norm=False):
+    """Every ensemble member's net on the same input (layers.matmul_ensemble, ml/layers.spi:468-471, run once
+    per member, ml/models.spi:47-49): hidden layers dense [+ ln_l2] + ReLU rounded to the storage type, the
+    last layer dense + row head.  Returns probabilities [members, rows, n_out]."""
+    outs = []
+    for e, ws in enumerate(member_weights):
+        bs = None if member_biases is None else member_biases[e]
+        h = np.asarray(x, dtype=np.float32)
+        for i, w in enumerate(ws):
+            h = dense(h, w, None if bs is None else bs[i], in_dtype=in_dtype)
+            if i < len(ws) - 1:
+                if hidden_norm:
+                    h = ln_l2(h)
+                h = round_input(relu(h), in_dtype)
+        m = np.ones(h.shape, dtype=bool) if mask is None else np.asarray(mask, dtype=bool)
+        if "masked_softmax" in head:
+            h = masked_softmax(h, m)
+        if "regret_matching" in head:
+            h = masked_regret_matching(h, m)
+        outs.append(h)
+    return np.stack(outs)
+
+
+def policy_decide(output_probs, seed, row_offset=0):
+    """The per-decision tail of models.noinline_run (ml/models.spi:51-76) on the members' probabilities
+    [members, rows, n_out]: member e samples an index per row with output e of the row's Philox stream
+    (seed, row_offset + row) (local_discrete_sampling, ml/primitives.spi:782-800), a member is drawn per
+    row with the outputs from `members` on (random.int_range, corecuda/random.spi:53-71), and the result is
+    (action, ensemble_id, sampling_prob_selected, sampling_prob_ensemble [rows, members], output_indices)."""
+    probs = np.asarray(output_probs, dtype=np.float32)
+    members, rows, _ = probs.shape
+    streams = np.uint64(row_offset) + np.arange(rows, dtype=np.uint64)
+    indices = np.stack([discrete_sampling(probs[e], philox_uniform(seed, streams, e)) for e in range(members)])
+    ensemble_id = philox_below(seed, streams, members, members)
+    r = np.arange(rows)
+    action = indices[ensemble_id, r]
+    safe = np.maximum(action, 0)
+    by_member = np.where(action[None, :] >= 0, probs[:, r, safe], np.float32(0))       # [members, rows]
+    return action, ensemble_id, by_member[ensemble_id, r], np.ascontiguousarray(by_member.T), indices
 
 
 def cross_entropy_loss(probs, target, mask=None):

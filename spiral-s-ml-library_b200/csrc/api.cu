@@ -4,35 +4,61 @@
 // (ml/matmul/run.spi:21-26): C's shape gives M and N, A gives K, all tensors
 // row-major and written in place.
 #include "common.cuh"
+#include "row_head.cuh"
 
-int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
-                        float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
-                        int epi, const float* bias, const uint8_t* mask, const void* aux_in,
-                        void* aux_out, cudaStream_t stream, int splits = 1, int* splits_used = nullptr);
 int sb_umma_plan(int a_trans, int b_trans, int M, int N, int K, int in_dtype, int sms, int* plan5);
 int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStream_t stream);
-int sb_umma_head_max_n();
 int sb_sgemm_launch(int a_trans, int b_trans, float alpha, const float* A, const float* B, float beta,
                     float* C, int M, int N, int K, int epi, const float* bias, cudaStream_t stream);
 
 namespace {
-constexpr int HEAD_FLAGS = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
+constexpr int HEAD_FLAGS = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;   // heads sb_matmul_ex accepts
+constexpr int SPEC_HEAD_FLAGS = HEAD_FLAGS | SB_EPI_SAMPLE | SB_EPI_BINARIZE;                  // heads sb_matmul_head accepts
 constexpr int GATE_FLAGS = SB_EPI_RELU_MASK_OUT | SB_EPI_RELU_GRAD_MASK;
-constexpr int ALL_FLAGS = SB_EPI_BIAS | SB_EPI_RELU | SB_EPI_RELU_GRAD | HEAD_FLAGS | GATE_FLAGS | SB_EPI_COLSUM_OUT;
+constexpr int ALL_FLAGS = SB_EPI_BIAS | SB_EPI_RELU | SB_EPI_RELU_GRAD | HEAD_FLAGS | GATE_FLAGS | SB_EPI_COLSUM_OUT |
+                          SB_EPI_LN_L2;
 
-int run_heads_unfused(float* C, int M, int N, int epi, const uint8_t* mask, void* aux_out,
-                      void* stream) {
+// The head as kernels of its own on the finished C (rows too wide for the fused head).
+int run_heads_unfused(float* C, int M, int N, const SbRowHead& h, void* stream) {
   int rc = SB_OK;
-  if (epi & SB_EPI_MASKED_SOFTMAX) {
-    rc = sb_row_softmax(C, C, M, N, mask, -1, stream);
+  if (h.flags & SB_EPI_BINARIZE) {
+    rc = sb_row_binarize(C, h.hash_out, M, N, h.modulo, stream);
     if (rc != SB_OK) return rc;
   }
-  if (epi & SB_EPI_REGRET_MATCHING) {
-    rc = sb_row_regret_matching(C, C, M, N, mask, -1, stream);
+  if (h.flags & SB_EPI_MASKED_SOFTMAX) {
+    rc = sb_row_softmax(C, C, M, N, h.mask, h.prefix, stream);
     if (rc != SB_OK) return rc;
   }
-  if (epi & SB_EPI_ARGMAX) rc = sb_row_argmax(C, reinterpret_cast<int32_t*>(aux_out), M, N, stream);
+  if (h.flags & SB_EPI_REGRET_MATCHING) {
+    rc = sb_row_regret_matching(C, C, M, N, h.mask, h.prefix, stream);
+    if (rc != SB_OK) return rc;
+  }
+  if (h.flags & SB_EPI_ARGMAX) {
+    rc = sb_row_argmax(C, h.argmax_out, M, N, stream);
+    if (rc != SB_OK) return rc;
+  }
+  if (h.flags & SB_EPI_SAMPLE) rc = sb_row_sample_seeded(C, h.sample_out, M, N, h.seed, h.row_offset, h.position, stream);
   return rc;
+}
+
+SbRowHead legacy_head(int epilogue, int N, const uint8_t* mask, void* aux_out) {
+  SbRowHead h;
+  memset(&h, 0, sizeof(h));
+  h.n = N; h.flags = epilogue & HEAD_FLAGS; h.prefix = -1; h.mask = mask;
+  h.argmax_out = reinterpret_cast<int32_t*>(aux_out);
+  return h;
+}
+
+int check_head(const char* who, const SbRowHead& h, int N) {
+  if (h.flags & ~SPEC_HEAD_FLAGS) return sb_fail(SB_ERR_BAD_ARG, "%s: head flags 0x%x hold something that is not a row head", who, h.flags);
+  if ((h.flags & SB_EPI_ARGMAX) && !h.argmax_out) return sb_fail(SB_ERR_BAD_ARG, "%s: SB_EPI_ARGMAX without argmax_out", who);
+  if ((h.flags & SB_EPI_SAMPLE) && !h.sample_out) return sb_fail(SB_ERR_BAD_ARG, "%s: SB_EPI_SAMPLE without sample_out", who);
+  if (h.flags & SB_EPI_BINARIZE) {
+    if (!h.hash_out || h.modulo == 0) return sb_fail(SB_ERR_BAD_ARG, "%s: SB_EPI_BINARIZE needs hash_out and a non-zero modulo", who);
+    if (N > 32) return sb_fail(SB_ERR_UNSUPPORTED, "%s: the sign hash is defined for rows of at most 32 values (N=%d)", who, N);
+  }
+  if (h.prefix > N) return sb_fail(SB_ERR_BAD_ARG, "%s: prefix %d beyond the %d columns", who, h.prefix, N);
+  return SB_OK;
 }
 }  // namespace
 
@@ -71,6 +97,11 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
     if (beta != 0.0f || alpha != 1.0f)
       return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_COLSUM_OUT needs alpha == 1 and beta == 0");
   }
+  if (epilogue & SB_EPI_LN_L2) {
+    if (in_dtype == SB_F32) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_LN_L2 needs a tensor-core input class");
+    if (alpha != 1.0f || beta != 0.0f || (epilogue & ~(SB_EPI_LN_L2 | SB_EPI_RELU)))
+      return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: SB_EPI_LN_L2 needs alpha == 1, beta == 0 and combines only with SB_EPI_RELU");
+  }
   if (in_dtype == SB_F32 && out_dtype == SB_TF32) out_dtype = SB_F32;
   if ((epilogue & HEAD_FLAGS) && out_dtype != SB_F32)
     return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul: row heads write fp32 output only");
@@ -91,18 +122,53 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
     int rc = sb_sgemm_launch(a_trans, b_trans, alpha, (const float*)A, (const float*)B, beta, (float*)C,
                              M, N, K, epilogue & (SB_EPI_BIAS | SB_EPI_RELU), bias, s);
     if (rc != SB_OK) return rc;
-    if (epilogue & HEAD_FLAGS) return run_heads_unfused((float*)C, M, N, epilogue, mask, aux_out, stream);
+    if (epilogue & HEAD_FLAGS) return run_heads_unfused((float*)C, M, N, legacy_head(epilogue, N, mask, aux_out), stream);
     return SB_OK;
   }
 
-  if ((epilogue & HEAD_FLAGS) && N > sb_umma_head_max_n()) {
+  if ((epilogue & HEAD_FLAGS) && !sb_umma_head_fits(N, -1)) {
     int rc = sb_umma_gemm_launch(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, in_dtype, out_dtype,
                                  epilogue & ~HEAD_FLAGS, bias, nullptr, aux_in, nullptr, s);
     if (rc != SB_OK) return rc;
-    return run_heads_unfused((float*)C, M, N, epilogue, mask, aux_out, stream);
+    return run_heads_unfused((float*)C, M, N, legacy_head(epilogue, N, mask, aux_out), stream);
   }
   return sb_umma_gemm_launch(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, in_dtype, out_dtype,
                              epilogue, bias, mask, aux_in, aux_out, s);
+}
+
+int sb_matmul_head(int a_trans, int b_trans, float alpha, const void* A, const void* B, float beta,
+                   float* C, int M, int N, int K, int in_dtype, int epilogue, const float* bias,
+                   const sb_head_spec* head, void* stream) {
+  if (!head) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_head: head is null");
+  if (M < 0 || N < 0 || K <= 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_head: dimensions M=%d N=%d K=%d", M, N, K);
+  if (epilogue & ~(SB_EPI_BIAS | SB_EPI_RELU))
+    return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_head: epilogue may hold SB_EPI_BIAS and SB_EPI_RELU (the head comes through head->flags)");
+  if ((epilogue & SB_EPI_BIAS) && !bias) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_head: SB_EPI_BIAS without a bias pointer");
+  if (in_dtype != SB_F32 && in_dtype != SB_TF32 && in_dtype != SB_BF16 && in_dtype != SB_F16)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_head: unknown input dtype %d", in_dtype);
+  if (M == 0 || N == 0) return SB_OK;
+  if (!A || !B || !C) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_head: null pointer");
+  if (reinterpret_cast<uintptr_t>(C) & 15) return sb_fail(SB_ERR_MISALIGNED, "sb_matmul_head: C must be 16-byte aligned");
+  SbRowHead h;
+  h.n = N; h.flags = head->flags; h.prefix = head->prefix < 0 ? -1 : head->prefix; h.mask = head->mask;
+  h.argmax_out = head->argmax_out; h.sample_out = head->sample_out; h.hash_out = head->hash_out;
+  h.modulo = head->modulo; h.seed = head->seed; h.row_offset = head->row_offset; h.position = head->position;
+  int rc = check_head("sb_matmul_head", h, N);
+  if (rc != SB_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (in_dtype == SB_F32) {
+    rc = sb_sgemm_launch(a_trans, b_trans, alpha, (const float*)A, (const float*)B, beta, C, M, N, K, epilogue, bias, s);
+    if (rc != SB_OK) return rc;
+    return run_heads_unfused(C, M, N, h, stream);
+  }
+  if (h.flags == 0 || !sb_umma_head_fits(N, h.prefix)) {
+    rc = sb_umma_gemm_launch(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, in_dtype, SB_F32, epilogue, bias, nullptr,
+                             nullptr, nullptr, s);
+    if (rc != SB_OK) return rc;
+    return run_heads_unfused(C, M, N, h, stream);
+  }
+  return sb_umma_gemm_launch(a_trans, b_trans, alpha, A, B, beta, C, M, N, K, in_dtype, SB_F32, epilogue | h.flags, bias,
+                             nullptr, nullptr, nullptr, s, 1, nullptr, &h);
 }
 
 int sb_matmul_tf32(int a_trans, int b_trans, float alpha, const float* A, const float* B,

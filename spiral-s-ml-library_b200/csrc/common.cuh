@@ -63,6 +63,18 @@ int sb_sm_count();
 void sb_prof_before(cudaStream_t s);
 void sb_prof_after(cudaStream_t s, double flops);
 
+// The tensor-core GEMM launcher (gemm_umma.cu); every argument is validated there.  `head`
+// describes the row head when `epi` holds a head flag (null: the legacy form -- byte mask in
+// `mask`, arg-max indices to `aux_out`).
+struct SbRowHead;
+int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
+                        float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
+                        int epi, const float* bias, const uint8_t* mask, const void* aux_in,
+                        void* aux_out, cudaStream_t stream, int splits = 1, int* splits_used = nullptr,
+                        const SbRowHead* head = nullptr);
+// True when a row head over N columns (legal columns j < prefix when prefix >= 0) runs inside the GEMM.
+bool sb_umma_head_fits(int N, int prefix);
+
 static inline int sb_dtype_size(int dt) {
   switch (dt) {
     case SB_F32: case SB_TF32: return 4;

@@ -28,6 +28,7 @@
 // UMMA layout that TMA produces, so no operand is transposed or re-tiled in
 // shared memory.
 #include "common.cuh"
+#include "row_head.cuh"
 
 #include <stdlib.h>
 #include <string.h>
@@ -42,7 +43,8 @@ constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;   // a warp takes every UG_EPI_S
 constexpr int UG_THREADS = 64 + 32 * UG_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
-constexpr int UG_HEAD_MAX_N = 32;  // widest row a fused head keeps in registers
+constexpr int UG_HEAD_MAX_N = 64;       // widest row a fused head keeps in registers
+constexpr int UG_HEAD_MAX_TILE_N = 256; // widest row a fused head may belong to when a prefix mask confines it to UG_HEAD_MAX_N columns
 constexpr int UG_EPI_STAGING = UG_EPI_WARPS * 4096;  // one 32-row x 128-byte box per epilogue warp
 
 struct UmmaGemmParams {
@@ -85,6 +87,7 @@ struct UmmaGemmParams {
   int tma_store;       // 1: and the finished boxes are written by TMA stores
   int wide;            // 1: 16-bit output boxes span two chunks (64 columns, 128-byte rows)
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
+  SbRowHead head;      // the row head, when epi holds a head flag
 };
 
 __device__ __forceinline__ void tile_coords(const UmmaGemmParams& p, int tile, int& m_blk, int& n_blk) {
@@ -239,6 +242,7 @@ struct EpiShared {
   int block_n;
   float alpha, beta;
   int has_bias, relu, relu_grad, coalesced;
+  int ln_l2;                // divide every row by its sum of squares before the ReLU (SB_EPI_LN_L2; the tile spans the row)
   uint32_t box_base;        // shared-memory address of the first epilogue warp's 4 KB box
 };
 __shared__ EpiShared g_epi;
@@ -524,10 +528,27 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
 
   uint32_t raw_a[32];
   uint32_t box_sel = 0u;
+  // Row normalisation (local_ln_l2, ml/primitives.spi:701-703): a first pass over the whole
+  // accumulator row sums the squares (both warps of a quadrant do it, each for itself); the tile
+  // spans the row (one column tile, N a multiple of 32), columns beyond N are zero.
+  float sumsq = 0.f;
+  const bool ln_l2 = MODE == -1 && g_epi.ln_l2 != 0;
+  if (ln_l2) {
+    for (int cc = 0; cc < nfull; ++cc) {
+      tmem_ld32(t_row + (uint32_t)(cc * 32), raw_a);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sumsq = fmaf(__uint_as_float(raw_a[j]), __uint_as_float(raw_a[j]), sumsq);
+    }
+  }
   for (; c < nfull; c += UG_EPI_STRIDE) {
     tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
     fetch(c + UG_EPI_STRIDE, bias_nxt, gate_nxt);    // in flight while this chunk is finished
     tmem_ld_wait();
+    if (ln_l2) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) raw_a[j] = __float_as_uint(sumsq != 0.f ? __uint_as_float(raw_a[j]) / sumsq : 0.f);
+    }
     const int col0 = n0 + c * 32;
     if (rows_live && col0 < N) {
       const uint32_t box = sbuf + ((MODE != -2 && sizeof(OutT) == 2 && g_epi.tma_c) ? box_sel : 0u);
@@ -621,106 +642,53 @@ __device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, i
   return true;
 }
 
-struct HeadArgs {
-  void* C;
+// What the row-head epilogue needs, in shared memory like EpiShared (written once by thread 0).
+struct HeadShared {
+  float* C;
   const float* bias;
-  const uint8_t* mask;
-  void* aux_out;
   long long ldc;
-  int N, epi;
+  int epi;                 // SB_EPI_BIAS / SB_EPI_RELU applied before the head
   float alpha, beta;
+  SbRowHead rh;
 };
+__shared__ HeadShared g_head;
 
-// Row head on a full row (N <= 32) held by one thread; fp32 output.
-// Follows local_masked_softmax / local_masked_regret_matching / local_argmax
-// (ml/primitives.spi:748-780, 705-708); the softmax subtracts the masked
-// maximum, which equals the reference's masked-mean form exactly in exact
-// arithmetic and cannot overflow.
-template <int UG_HEAD_W>
-__device__ __forceinline__ void finish_head(const HeadArgs& p, float* v, long long row) {
-  const int n = p.N;
-  float* crow = reinterpret_cast<float*>(p.C) + row * p.ldc;
-  const uint8_t* mrow = p.mask ? p.mask + row * (long long)n : nullptr;
-  const bool has_beta = p.beta != 0.0f;
-  uint32_t legal = 0;
-#pragma unroll
-  for (int j = 0; j < UG_HEAD_W; ++j) {
-    if (j < n) {
-      float x = p.alpha * v[j];
-      if (has_beta) x += p.beta * crow[j];
-      if (p.epi & SB_EPI_BIAS) x += __ldg(p.bias + j);
-      if (p.epi & SB_EPI_RELU) x = fmaxf(x, 0.f);
-      v[j] = x;
-      if (!mrow || mrow[j] != 0) legal |= (1u << j);
-    }
-  }
-  const int count = __popc(legal);
-  if (p.epi & SB_EPI_MASKED_SOFTMAX) {
-    float mx = -3.402823466e38f;
-#pragma unroll
-    for (int j = 0; j < UG_HEAD_W; ++j)
-      if (j < n && ((legal >> j) & 1u)) mx = fmaxf(mx, v[j]);
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < UG_HEAD_W; ++j) {
-      if (j < n) {
-        float e = ((legal >> j) & 1u) ? __expf(v[j] - mx) : 0.f;
-        v[j] = e;
-        s += e;
-      }
-    }
-    const float inv = s > 0.f ? 1.f / s : 0.f;
-#pragma unroll
-    for (int j = 0; j < UG_HEAD_W; ++j)
-      if (j < n) v[j] *= inv;
-  }
-  if (p.epi & SB_EPI_REGRET_MATCHING) {
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < UG_HEAD_W; ++j) {
-      if (j < n) {
-        float q = ((legal >> j) & 1u) ? fmaxf(v[j], 0.f) : 0.f;
-        v[j] = q;
-        s += q;
-      }
-    }
-    const float inv_len = count > 0 ? 1.f / (float)count : 0.f;
-#pragma unroll
-    for (int j = 0; j < UG_HEAD_W; ++j) {
-      if (j < n) {
-        const bool lg = (legal >> j) & 1u;
-        v[j] = !lg ? 0.f : (s != 0.f ? v[j] / s : inv_len);
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < UG_HEAD_W; ++j)
-    if (j < n) crow[j] = v[j];
-  if (p.epi & SB_EPI_ARGMAX) {
-    int best = 0;
-    float bv = v[0];
-#pragma unroll
-    for (int j = 1; j < UG_HEAD_W; ++j) {
-      if (j < n && v[j] > bv) {
-        bv = v[j];
-        best = j;
-      }
-    }
-    reinterpret_cast<int32_t*>(p.aux_out)[row] = best;
-  }
-}
-
-// One warp finishes the head rows of its TMEM lane quadrant; out of line for the
-// same reason as epilogue_tile.
+// One warp finishes the head rows of its TMEM lane quadrant: a thread holds the first W values of
+// its row (the whole row when N <= W), applies scale / old C / bias / ReLU and hands over to the
+// shared row head.  Out of line for the same reason as epilogue_tile.
 template <int W>
-__device__ __noinline__ void epilogue_head(HeadArgs h, uint32_t t_row, long long row, int M) {
+__device__ __noinline__ void epilogue_head(uint32_t t_row, long long row, int M) {
   uint32_t raw[W];
-  if (W == 32) tmem_ld32(t_row, raw); else tmem_ld16(t_row, raw);
+  if (W == 64) {
+    tmem_ld32(t_row, raw);
+    tmem_ld32(t_row + 32u, raw + 32);
+  } else if (W == 32) {
+    tmem_ld32(t_row, raw);
+  } else {
+    tmem_ld16(t_row, raw);
+  }
   tmem_ld_wait();
-  if (row < M) finish_head<W>(h, reinterpret_cast<float*>(raw), row);
+  if (row >= M) return;
+  float* v = reinterpret_cast<float*>(raw);
+  const int n = g_head.rh.n;
+  float* crow = g_head.C + row * g_head.ldc;
+  const float alpha = g_head.alpha, beta = g_head.beta;
+  const bool has_beta = beta != 0.0f, has_bias = (g_head.epi & SB_EPI_BIAS) != 0, relu = (g_head.epi & SB_EPI_RELU) != 0;
+  const float* bias = g_head.bias;
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    if (j < n) {
+      float x = alpha * v[j];
+      if (has_beta) x += beta * crow[j];
+      if (has_bias) x += __ldg(bias + j);
+      if (relu) x = fmaxf(x, 0.f);
+      v[j] = x;
+    }
+  }
+  sb_row_head_finish<W>(g_head.rh, v, row, crow);
 }
 
-constexpr int EPI_HEAD_MASK = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX;
+constexpr int EPI_HEAD_MASK = SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX | SB_EPI_SAMPLE | SB_EPI_BINARIZE;
 constexpr int EPI_GATE_MASK = SB_EPI_RELU_MASK_OUT | SB_EPI_RELU_GRAD_MASK;
 
 // PAIR = false: one CTA per 128 x block_n tile (cta_group::1).
@@ -781,7 +749,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     g_epi.alpha = p.alpha; g_epi.beta = p.beta;
     g_epi.has_bias = (p.epi & SB_EPI_BIAS) ? 1 : 0; g_epi.relu = (p.epi & SB_EPI_RELU) ? 1 : 0;
     g_epi.relu_grad = (p.epi & SB_EPI_RELU_GRAD) ? 1 : 0; g_epi.coalesced = p.coalesced;
+    g_epi.ln_l2 = (p.epi & SB_EPI_LN_L2) ? 1 : 0;
     g_epi.box_base = stage_base + p.epi_offset;
+    g_head.C = reinterpret_cast<float*>(p.C); g_head.bias = p.bias; g_head.ldc = p.ldc; g_head.epi = p.epi;
+    g_head.alpha = p.alpha; g_head.beta = p.beta; g_head.rh = p.head;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -955,7 +926,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const bool head = (p.epi & EPI_HEAD_MASK) != 0;
     // Which compile-time variant of the epilogue serves this launch (see coalesced_chunk).
     int epi_mode = (p.beta != 0.0f || (p.epi & SB_EPI_RELU_GRAD)) ? -2 : -1;
-    if (epi_mode == -1 && p.alpha == 1.0f) {
+    if (epi_mode == -1 && p.alpha == 1.0f && !(p.epi & SB_EPI_LN_L2)) {
       const int flags = ((p.epi & SB_EPI_BIAS) ? 1 : 0) | ((p.epi & SB_EPI_RELU) ? 2 : 0) |
                         ((p.epi & SB_EPI_RELU_MASK_OUT) ? 4 : 0) | ((p.epi & SB_EPI_RELU_GRAD_MASK) ? 8 : 0) |
                         ((p.epi & SB_EPI_COLSUM_OUT) ? 16 : 0);
@@ -971,12 +942,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (head) {
         if (!mbar_wait(full_bar, acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
         tc_fence_after_sync();
-        if (half == 0) {               // a head row is one chunk: the second warp of the quadrant idles
-          HeadArgs h;
-          h.C = p.C; h.bias = p.bias; h.mask = p.mask; h.aux_out = p.aux_out; h.ldc = p.ldc;
-          h.N = p.N; h.epi = p.epi; h.alpha = p.alpha; h.beta = p.beta;
-          if (p.block_n >= 32) epilogue_head<32>(h, t_row, (long long)row0_warp + lane, p.M);
-          else epilogue_head<16>(h, t_row, (long long)row0_warp + lane, p.M);
+        if (half == 0) {               // a thread finishes a whole head row: the second warp of the quadrant idles
+          if (p.block_n > 32) epilogue_head<64>(t_row, (long long)row0_warp + lane, p.M);
+          else if (p.block_n > 16) epilogue_head<32>(t_row, (long long)row0_warp + lane, p.M);
+          else epilogue_head<16>(t_row, (long long)row0_warp + lane, p.M);
         }
       } else {
         const int n0 = n_blk * p.block_n;
@@ -1222,7 +1191,7 @@ __global__ void scale_rows_kernel(void* C, long long total, float beta, int out_
 int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
-                        void* aux_out, cudaStream_t stream, int splits, int* splits_used) {
+                        void* aux_out, cudaStream_t stream, int splits, int* splits_used, const SbRowHead* head) {
   const int es = sb_dtype_size(in_dtype);
   UmmaGemmParams p;
   memset(&p, 0, sizeof(p));
@@ -1234,6 +1203,20 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.alpha = alpha; p.beta = beta;
   p.C = C; p.ldc = N; p.out_dtype = out_dtype;
   p.epi = epi; p.bias = bias; p.mask = mask; p.aux_in = aux_in; p.aux_out = aux_out;
+  if (epi & EPI_HEAD_MASK) {
+    if (head) {
+      p.head = *head;
+    } else {
+      p.head.prefix = -1;
+      p.head.mask = mask;
+      p.head.argmax_out = reinterpret_cast<int32_t*>(aux_out);
+    }
+    p.head.n = N;
+    p.head.flags = epi & EPI_HEAD_MASK;
+    if (!sb_umma_head_fits(N, p.head.prefix))
+      return sb_fail(SB_ERR_UNSUPPORTED, "a fused row head holds %d columns (%d under a prefix mask of at most %d)",
+                     UG_HEAD_MAX_N, UG_HEAD_MAX_TILE_N, UG_HEAD_MAX_N);
+  }
 
   // TMA needs 16-byte aligned bases and row pitches.
   const long long lda = a_trans ? M : K;
@@ -1274,6 +1257,11 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
 
   if (!p.coalesced && (epi & (EPI_GATE_MASK | SB_EPI_COLSUM_OUT)))
     return sb_fail(SB_ERR_MISALIGNED, "the sign-bit and column-sum epilogues need a 16-byte aligned C");
+  if (epi & SB_EPI_LN_L2) {
+    if (epi & EPI_HEAD_MASK) return sb_fail(SB_ERR_UNSUPPORTED, "SB_EPI_LN_L2 cannot be combined with a row head");
+    if (p.tiles_n != 1 || N % 32 != 0 || !p.coalesced)
+      return sb_fail(SB_ERR_UNSUPPORTED, "SB_EPI_LN_L2 needs N <= 256, N %% 32 == 0 and a 16-byte aligned C (N=%d)", N);
+  }
 
   // TMA stores of the finished boxes: no second tile is read (beta, activation gate), and with
   // split-K -- the partials form one [splits * M, N] tensor -- no 32-row box may straddle two partials.
@@ -1282,7 +1270,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.tma_store = 0;
   if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || M % 32 == 0)) {
     const int cdt = es_out == 4 ? SB_F32 : out_dtype;
-    p.wide = (es_out == 2 && p.block_n % 64 == 0) ? 1 : 0;
+    p.wide = (es_out == 2 && p.block_n % 64 == 0 && !(epi & SB_EPI_LN_L2)) ? 1 : 0;
     rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, p.wide ? 64 : 32,
                       (es_out == 4 || p.wide) ? SWZ_128 : SWZ_64);
     if (rc != SB_OK) return rc;
@@ -1342,4 +1330,6 @@ int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStr
   return SB_OK;
 }
 
-int sb_umma_head_max_n() { return UG_HEAD_MAX_N; }
+bool sb_umma_head_fits(int N, int prefix) {
+  return N <= UG_HEAD_MAX_N || (N <= UG_HEAD_MAX_TILE_N && prefix >= 0 && prefix <= UG_HEAD_MAX_N);
+}

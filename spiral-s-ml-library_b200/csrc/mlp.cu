@@ -18,11 +18,6 @@
 // all-reduce), per-layer activation buffers and one scratch buffer.
 #include "common.cuh"
 
-int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
-                        float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
-                        int epi, const float* bias, const uint8_t* mask, const void* aux_in,
-                        void* aux_out, cudaStream_t stream, int splits, int* splits_used);
-int sb_umma_head_max_n();
 
 namespace {
 

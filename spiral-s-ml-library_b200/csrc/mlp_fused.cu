@@ -17,8 +17,17 @@
 //                    the next layer's MMAs read; the last layer ends in the row head
 //                    (masked softmax / regret matching / argmax) written to global.
 // 16-bit arithmetic classes only (SB_F16, SB_BF16); widths: input <= 256 and a
-// multiple of 8, hidden layers multiples of 64 up to 256, output <= 32.
+// multiple of 8, hidden layers multiples of 64 up to 256, output <= 64 (<= 256 when a
+// prefix mask confines the head to its first 64 columns, the shape of the reference's
+// own policy nets, game/leduc/model_cem.spi:37,52-60).
+//
+// Optional, for the reference's graphs: ln_l2 before every ReLU (ml/layers.spi:562-568), a
+// sampling head that draws from a Philox stream per row (ml/layers.spi:422-431), and the
+// per-decision tail of ml/models.spi:51-76 (pick a member per row, report its action and the
+// probabilities every member gave that action), done by whichever CTA finishes the last member
+// of a row tile.
 #include "common.cuh"
+#include "row_head.cuh"
 
 namespace {
 
@@ -53,92 +62,40 @@ struct FusedParams {
   uint32_t act_offset, w_offset;      // byte offsets of the activation tile and the weight ring
   // head
   float* out;
-  const uint8_t* mask;
-  int32_t* actions;
-  int head;
+  SbRowHead head;                     // n, flags, prefix, mask, seed, ...; argmax_out / sample_out are [members, batch]
+  int hidden_norm;                    // 1: x / sum(x^2) over the row before every ReLU
+  // decision tail (null counters = off)
+  int members;
+  int* tile_counters;                 // int32 [num_tiles], zero between calls
+  int32_t* ensemble_id;               // [batch]
+  int32_t* action;                    // [batch]
+  float* prob_selected;               // [batch]
+  float* prob_ensemble;               // [batch, members]
 };
 
-struct HeadArgsF {
-  float* out;
-  const float* bias;
-  const uint8_t* mask;
-  int32_t* actions;
-  int N, epi;
-};
-
-// Row head on one full row held by a thread (same math as the GEMM's fused head;
-// ml/primitives.spi:705-708, 748-780).
+// The last layer: a thread takes the first W values of its row out of tensor memory, adds the bias and
+// hands over to the shared row head.
 template <int W>
-__device__ __forceinline__ void fused_head_row(const HeadArgsF& h, float* v, long long row) {
-  const int n = h.N;
-  float* crow = h.out + row * n;
-  const uint8_t* mrow = h.mask ? h.mask + row * (long long)n : nullptr;
-  uint32_t legal = 0;
-#pragma unroll
-  for (int j = 0; j < W; ++j) {
-    if (j < n) {
-      if (h.bias) v[j] += __ldg(h.bias + j);
-      if (!mrow || mrow[j] != 0) legal |= (1u << j);
-    }
-  }
-  const int count = __popc(legal);
-  if (h.epi & SB_EPI_MASKED_SOFTMAX) {
-    float mx = -3.402823466e38f;
-#pragma unroll
-    for (int j = 0; j < W; ++j)
-      if (j < n && ((legal >> j) & 1u)) mx = fmaxf(mx, v[j]);
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < W; ++j) {
-      if (j < n) {
-        const float e = ((legal >> j) & 1u) ? __expf(v[j] - mx) : 0.f;
-        v[j] = e;
-        s += e;
-      }
-    }
-    const float inv = s > 0.f ? 1.f / s : 0.f;
-#pragma unroll
-    for (int j = 0; j < W; ++j)
-      if (j < n) v[j] *= inv;
-  }
-  if (h.epi & SB_EPI_REGRET_MATCHING) {
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < W; ++j) {
-      if (j < n) {
-        const float q = ((legal >> j) & 1u) ? fmaxf(v[j], 0.f) : 0.f;
-        v[j] = q;
-        s += q;
-      }
-    }
-    const float inv_len = count > 0 ? 1.f / (float)count : 0.f;
-#pragma unroll
-    for (int j = 0; j < W; ++j)
-      if (j < n) v[j] = !((legal >> j) & 1u) ? 0.f : (s != 0.f ? v[j] / s : inv_len);
-  }
-#pragma unroll
-  for (int j = 0; j < W; ++j)
-    if (j < n) crow[j] = v[j];
-  if (h.epi & SB_EPI_ARGMAX) {
-    int best = 0;
-    float bv = v[0];
-#pragma unroll
-    for (int j = 1; j < W; ++j) {
-      if (j < n && v[j] > bv) {
-        bv = v[j];
-        best = j;
-      }
-    }
-    h.actions[row] = best;
-  }
-}
-
-template <int W>
-__device__ __noinline__ void fused_head(HeadArgsF h, uint32_t t_row, long long row, int batch) {
+__device__ __noinline__ void fused_head(const SbRowHead& h, const float* bias, float* out, uint32_t t_row, long long row,
+                                        int batch) {
   uint32_t raw[W];
-  if (W == 32) tmem_ld32(t_row, raw); else tmem_ld16(t_row, raw);
+  if (W == 64) {
+    tmem_ld32(t_row, raw);
+    tmem_ld32(t_row + 32u, raw + 32);
+  } else if (W == 32) {
+    tmem_ld32(t_row, raw);
+  } else {
+    tmem_ld16(t_row, raw);
+  }
   tmem_ld_wait();
-  if (row < batch) fused_head_row<W>(h, reinterpret_cast<float*>(raw), row);
+  if (row >= batch) return;
+  float* v = reinterpret_cast<float*>(raw);
+  if (bias) {
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+      if (j < h.n) v[j] += __ldg(bias + j);
+  }
+  sb_row_head_finish<W>(h, v, row, out + row * h.n);
 }
 
 // One warp's share of a hidden layer: chunks `half`, half+2, ... of 32 columns.
@@ -147,8 +104,20 @@ __device__ __noinline__ void fused_head(HeadArgsF h, uint32_t t_row, long long r
 // element (row, j) -> chunk j / 64, byte row * 128 + (((j % 64) / 8) ^ (row % 8)) * 16 + (j % 8) * 2.
 template <bool BF16>
 __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const float* bias, uint32_t act_base,
-                                          uint32_t bias_smem, int row_in_tile, int lane, int half) {
+                                          uint32_t bias_smem, int row_in_tile, int lane, int half, int norm) {
   const int nchunks = n_cols >> 5;
+  // Row normalisation (local_ln_l2, ml/primitives.spi:701-703; no bias in this mode): a first pass
+  // over the whole accumulator row sums the squares; both warps of a quadrant do it for themselves.
+  float sumsq = 0.f;
+  if (norm) {
+    for (int c = 0; c < nchunks; ++c) {
+      uint32_t raw[32];
+      tmem_ld32(t_row + (uint32_t)(c * 32), raw);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sumsq = fmaf(__uint_as_float(raw[j]), __uint_as_float(raw[j]), sumsq);
+    }
+  }
   float bias_cur = 0.f, bias_nxt = 0.f;
   if (bias && half < nchunks) bias_cur = __ldg(bias + half * 32 + lane);
   for (int c = half; c < nchunks; c += 2) {
@@ -157,6 +126,10 @@ __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const floa
     if (bias && c + 2 < nchunks) bias_nxt = __ldg(bias + (c + 2) * 32 + lane);
     tmem_ld_wait();
     float* v = reinterpret_cast<float*>(raw);
+    if (norm) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = sumsq != 0.f ? v[j] / sumsq : 0.f;
+    }
     if (bias) {
       asm volatile("st.shared.f32 [%0], %1;" ::"r"(bias_smem + 4u * (uint32_t)lane), "f"(bias_cur) : "memory");
       __syncwarp();
@@ -196,13 +169,34 @@ __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const floa
   }
 }
 
+// The per-decision tail for one state, once every member's probabilities and sampled index are in
+// global memory: draw a member, report its action, the probability it gave the action and the
+// probability every member gave it (ml/models.spi:51-76).
+__device__ __noinline__ void decide_row(const FusedParams& p, long long row) {
+  if (row >= p.batch) return;
+  const int n = p.head.n;
+  const unsigned long long stream = p.head.row_offset + (unsigned long long)row;
+  // drawn after the members' sampling draws (outputs position .. position + members - 1 of the stream)
+  const int e_id = (int)sb_philox_below(p.head.seed, stream, p.head.position + (unsigned long long)p.members,
+                                        (uint32_t)p.members);
+  const int a = __ldcg(p.head.sample_out + (long long)e_id * p.batch + row);
+  p.ensemble_id[row] = e_id;
+  p.action[row] = a;
+  const float* prow = p.out + row * n;
+  p.prob_selected[row] = a >= 0 ? __ldcg(prow + (long long)e_id * p.out_stride + a) : 0.f;
+  for (int e = 0; e < p.members; ++e)
+    p.prob_ensemble[row * p.members + e] = a >= 0 ? __ldcg(prow + (long long)e * p.out_stride + a) : 0.f;
+}
+
 __global__ void __launch_bounds__(FM_THREADS, 1)
 mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__ FusedParams p) {
   extern __shared__ uint8_t fm_smem_raw[];
-  __shared__ __align__(8) uint64_t bar_x_full, bar_x_empty, bar_acc_full, bar_act_ready;
+  __shared__ __align__(8) uint64_t bar_x_full, bar_x_empty, bar_acc_full, bar_act_ready, bar_tail_in, bar_tail_out;
   __shared__ __align__(8) uint64_t bar_w_full[FM_W_STAGES], bar_w_empty[FM_W_STAGES];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int tile_is_complete;
+  __shared__ SbRowHead head_slot[FM_EPI_WARPS];
   __shared__ __align__(16) float bias_spread[FM_EPI_WARPS][32];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -216,6 +210,8 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
     mbar_init(smem_u32(&bar_x_empty), 1);
     mbar_init(smem_u32(&bar_acc_full), 1);
     mbar_init(smem_u32(&bar_act_ready), FM_EPI_WARPS);
+    mbar_init(smem_u32(&bar_tail_in), 4);       // the four warps that finish head rows
+    mbar_init(smem_u32(&bar_tail_out), 1);
     for (int s = 0; s < FM_W_STAGES; ++s) {
       mbar_init(smem_u32(&bar_w_full[s]), 1);
       mbar_init(smem_u32(&bar_w_empty[s]), 1);
@@ -319,35 +315,70 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
     const int row_in_tile = quad * 32 + lane;
     const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t bias_smem = smem_u32(&bias_spread[warp - 2][0]);
-    uint32_t acc_phase = 0;
-    HeadArgsF h;
-    h.out = p.out; h.bias = p.bias[L - 1]; h.mask = p.mask; h.actions = p.actions;
-    h.N = p.width[L]; h.epi = p.head;
+    uint32_t acc_phase = 0, tail_phase = 0;
+    // This warp's copy of the head description (in shared memory: the head code reads a field where it
+    // needs it instead of holding the whole structure in registers); member-specific fields are set per item.
+    SbRowHead& h = head_slot[warp - 2];
+    if (lane == 0) h = p.head;
+    __syncwarp();
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       const int member = item / p.num_tiles, tile = item - member * p.num_tiles;
       const long long pofs = (long long)member * p.member_stride;
-      h.out = p.out + (long long)member * p.out_stride;
-      h.actions = p.actions ? p.actions + (long long)member * p.batch : nullptr;
-      h.bias = p.bias[L - 1] ? p.bias[L - 1] + pofs : nullptr;
+      float* out_m = p.out + (long long)member * p.out_stride;
+      if (lane == 0) {
+        h.argmax_out = p.head.argmax_out ? p.head.argmax_out + (long long)member * p.batch : nullptr;
+        h.sample_out = p.head.sample_out ? p.head.sample_out + (long long)member * p.batch : nullptr;
+        h.position = p.head.position + (unsigned long long)member;      // one draw per member from the row's stream
+      }
+      __syncwarp();
+      const float* head_bias = p.bias[L - 1] ? p.bias[L - 1] + pofs : nullptr;
       for (int l = 0; l < L; ++l) {
         if (!mbar_wait(smem_u32(&bar_acc_full), acc_phase, abortp, SB_SITE_MLP_ACC)) { ok = false; break; }
         acc_phase ^= 1u;
         tc_fence_after_sync();
         if (l < L - 1) {
           const float* bias_l = p.bias[l] ? p.bias[l] + pofs : nullptr;
-          if (p.is_bf16) fused_hidden<true>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half);
-          else fused_hidden<false>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half);
+          if (p.is_bf16) fused_hidden<true>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm);
+          else fused_hidden<false>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm);
           // generic-proxy writes of the activation tile must be visible to the MMA's async-proxy reads
           fence_proxy_async_smem();
         } else if (half == 0) {
           const long long row = (long long)tile * 128 + row_in_tile;
-          if (p.n_pad[l] >= 32) fused_head<32>(h, t_row, row, p.batch);
-          else fused_head<16>(h, t_row, row, p.batch);
+          if (p.n_pad[l] > 32) fused_head<64>(h, head_bias, out_m, t_row, row, p.batch);
+          else if (p.n_pad[l] > 16) fused_head<32>(h, head_bias, out_m, t_row, row, p.batch);
+          else fused_head<16>(h, head_bias, out_m, t_row, row, p.batch);
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_act_ready));
+      }
+      if (ok && p.tile_counters && half == 0) {
+        // Decision tail (ml/models.spi:51-76).  The four head warps publish their rows of this member, count
+        // the member in; the CTA that counts the last member of the tile in sees every member's results.
+        // The two meeting points are mbarriers with bounded waits, like every other wait of the kernel.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tail_in));
+        if (warp == 2 && lane == 0) {
+          if (mbar_wait(smem_u32(&bar_tail_in), tail_phase, abortp, SB_SITE_MLP_ACT)) {
+            __threadfence();
+            const int before = atomicAdd(p.tile_counters + tile, 1);
+            __threadfence();
+            tile_is_complete = before == p.members - 1 ? 1 : 0;
+          } else {
+            tile_is_complete = 0;
+          }
+          mbar_arrive(smem_u32(&bar_tail_out));
+        }
+        if (!mbar_wait(smem_u32(&bar_tail_out), tail_phase, abortp, SB_SITE_MLP_ACT)) break;
+        tail_phase ^= 1u;
+        if (tile_is_complete) {
+          __threadfence();
+          decide_row(p, (long long)tile * 128 + row_in_tile);
+          if (warp == 2 && lane == 0) p.tile_counters[tile] = 0;        // ready for the next call
+        }
+        // tile_is_complete is rewritten only after all four warps have arrived for the next item.
       }
     }
   }
@@ -389,38 +420,43 @@ static int make_tmap_members(CUtensorMap* map, const void* base, int in_dtype, i
   return SB_OK;
 }
 
-extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
-                                             const void* x, const void* w_compute, const float* params, int head,
-                                             const uint8_t* mask, float* out, int32_t* actions, void* stream);
+// What the per-decision tail writes (all null = no tail).
+struct FusedDecide {
+  int* tile_counters;
+  int32_t* ensemble_id;
+  int32_t* action;
+  float* prob_selected;
+  float* prob_ensemble;
+};
 
-extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
-                                    const void* w_compute, const float* params, int head, const uint8_t* mask,
-                                    float* out, int32_t* actions, void* stream) {
-  return sb_mlp_forward_fused_ensemble(n_layers, sizes, batch, 1, in_dtype, x, w_compute, params, head, mask, out,
-                                       actions, stream);
-}
-
-extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
-                                             const void* x, const void* w_compute, const float* params, int head,
-                                             const uint8_t* mask, float* out, int32_t* actions, void* stream) {
-  if (members < 1 || members > 1024) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: 1..1024 ensemble members");
-  if (n_layers < 1 || n_layers > FM_MAX_LAYERS) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: 1..%d layers", FM_MAX_LAYERS);
-  if (!sizes) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: sizes is null");
+// Validates and launches the fused kernel.  `head`: n is set here; argmax_out / sample_out are
+// [members, batch].  `who` names the entry point in error texts.
+static int fused_launch(const char* who, int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                        const void* x, const void* w_compute, const float* params, SbRowHead head, int hidden_norm,
+                        float* out, const FusedDecide* decide, void* stream) {
+  if (members < 1 || members > 1024) return sb_fail(SB_ERR_BAD_ARG, "%s: 1..1024 ensemble members", who);
+  if (n_layers < 1 || n_layers > FM_MAX_LAYERS) return sb_fail(SB_ERR_UNSUPPORTED, "%s: 1..%d layers", who, FM_MAX_LAYERS);
+  if (!sizes) return sb_fail(SB_ERR_BAD_ARG, "%s: sizes is null", who);
   if (in_dtype != SB_F16 && in_dtype != SB_BF16)
-    return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: 16-bit arithmetic classes only (SB_F16, SB_BF16)");
-  if (batch < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: negative batch");
-  if (head & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX))
-    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: head may hold only row-head flags");
-  if (sizes[0] < 8 || sizes[0] > 256 || sizes[0] % 8) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: input width %d (8..256, multiple of 8)", sizes[0]);
+    return sb_fail(SB_ERR_UNSUPPORTED, "%s: 16-bit arithmetic classes only (SB_F16, SB_BF16)", who);
+  if (batch < 0) return sb_fail(SB_ERR_BAD_ARG, "%s: negative batch", who);
+  if (head.flags & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX | SB_EPI_SAMPLE))
+    return sb_fail(SB_ERR_BAD_ARG, "%s: the head may hold softmax, regret matching, arg-max and sampling", who);
+  if (sizes[0] < 8 || sizes[0] > 256 || sizes[0] % 8) return sb_fail(SB_ERR_UNSUPPORTED, "%s: input width %d (8..256, multiple of 8)", who, sizes[0]);
   for (int i = 1; i < n_layers; ++i)
     if (sizes[i] < 64 || sizes[i] > 256 || sizes[i] % 64)
-      return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: hidden width %d (64..256, multiple of 64)", sizes[i]);
-  if (sizes[n_layers] < 1 || sizes[n_layers] > 32) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: output width %d (1..32)", sizes[n_layers]);
+      return sb_fail(SB_ERR_UNSUPPORTED, "%s: hidden width %d (64..256, multiple of 64)", who, sizes[i]);
+  const int n_out = sizes[n_layers];
+  if (head.prefix > n_out) return sb_fail(SB_ERR_BAD_ARG, "%s: prefix %d beyond the %d output columns", who, head.prefix, n_out);
+  if (n_out < 1 || !(n_out <= 64 || (n_out <= 256 && head.prefix >= 0 && head.prefix <= 64)))
+    return sb_fail(SB_ERR_UNSUPPORTED, "%s: output width %d (1..64, or up to 256 under a prefix mask of at most 64 columns)", who, n_out);
+  if (hidden_norm && params) return sb_fail(SB_ERR_UNSUPPORTED, "%s: row-normalised hidden layers take no bias (params must be null)", who);
   if (batch == 0) return SB_OK;
-  if (!x || !w_compute || !out) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: null pointer");
-  if ((head & SB_EPI_ARGMAX) && !actions) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: SB_EPI_ARGMAX without an actions buffer");
+  if (!x || !w_compute || !out) return sb_fail(SB_ERR_BAD_ARG, "%s: null pointer", who);
+  if ((head.flags & SB_EPI_ARGMAX) && !head.argmax_out) return sb_fail(SB_ERR_BAD_ARG, "%s: SB_EPI_ARGMAX without an actions buffer", who);
+  if ((head.flags & SB_EPI_SAMPLE) && !head.sample_out) return sb_fail(SB_ERR_BAD_ARG, "%s: SB_EPI_SAMPLE without an indices buffer", who);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_compute)) & 15)
-    return sb_fail(SB_ERR_MISALIGNED, "sb_mlp_forward_fused: x and w_compute must be 16-byte aligned");
+    return sb_fail(SB_ERR_MISALIGNED, "%s: x and w_compute must be 16-byte aligned", who);
 
   long long off[2 * FM_MAX_LAYERS + 1];
   int rc = sb_mlp_param_offsets(n_layers, sizes, off);
@@ -435,13 +471,13 @@ extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int
   p.num_tiles = (batch + 127) / 128;
   p.num_items = p.num_tiles * members;
   p.member_stride = off[2 * n_layers];
-  p.out_stride = (long long)batch * sizes[n_layers];
+  p.out_stride = (long long)batch * n_out;
   int max_n = 32;
   uint32_t max_act_chunks = 1;
   for (int l = 0; l <= n_layers; ++l) p.width[l] = sizes[l];
   for (int l = 0; l < n_layers; ++l) {
     const bool last = l == n_layers - 1;
-    p.n_pad[l] = last ? (sizes[l + 1] <= 16 ? 16 : 32) : sizes[l + 1];
+    p.n_pad[l] = last ? (sizes[l + 1] + 15) / 16 * 16 : sizes[l + 1];
     p.k_chunks[l] = (sizes[l] + 63) / 64;
     p.idesc[l] = sb_umma_idesc(in_dtype, 0, 0, 128, p.n_pad[l]);
     p.w_bytes[l] = (uint32_t)p.n_pad[l] * 128u;
@@ -460,7 +496,13 @@ extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int
   p.w_offset = p.act_offset + max_act_chunks * FM_CHUNK_BYTES;
   p.tmem_cols = 32;
   while (p.tmem_cols < max_n) p.tmem_cols <<= 1;
-  p.out = out; p.mask = mask; p.actions = actions; p.head = head;
+  head.n = n_out;
+  p.out = out; p.head = head; p.hidden_norm = hidden_norm ? 1 : 0;
+  p.members = members;
+  if (decide) {
+    p.tile_counters = decide->tile_counters; p.ensemble_id = decide->ensemble_id; p.action = decide->action;
+    p.prob_selected = decide->prob_selected; p.prob_ensemble = decide->prob_ensemble;
+  }
   const size_t smem = (size_t)p.w_offset + (size_t)FM_W_STAGES * FM_STAGE_BYTES + 1024;
 
   static std::atomic<bool> attr_set[64];
@@ -470,7 +512,7 @@ extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int
     SB_CUDA(cudaFuncSetAttribute(mlp_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
     attr_set[dev].store(true, std::memory_order_release);
   }
-  if (smem > 225 * 1024) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused: %zu bytes of shared memory needed", smem);
+  if (smem > 225 * 1024) return sb_fail(SB_ERR_UNSUPPORTED, "%s: %zu bytes of shared memory needed", who, smem);
   const int sms = sb_sm_count();
   const int grid = p.num_items < sms ? p.num_items : sms;
   double flops = 0.0;
@@ -481,4 +523,74 @@ extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
+}
+
+static SbRowHead fused_head_from_spec(const sb_head_spec* spec) {
+  SbRowHead h;
+  memset(&h, 0, sizeof(h));
+  h.flags = spec->flags; h.prefix = spec->prefix < 0 ? -1 : spec->prefix; h.mask = spec->mask;
+  h.argmax_out = spec->argmax_out; h.sample_out = spec->sample_out;
+  h.seed = spec->seed; h.row_offset = spec->row_offset; h.position = spec->position;
+  return h;
+}
+
+extern "C" int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                                             const void* x, const void* w_compute, const float* params, int head,
+                                             const uint8_t* mask, float* out, int32_t* actions, void* stream) {
+  if (head & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX))
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused: head may hold only row-head flags");
+  SbRowHead h;
+  memset(&h, 0, sizeof(h));
+  h.flags = head; h.prefix = -1; h.mask = mask; h.argmax_out = actions;
+  return fused_launch("sb_mlp_forward_fused", n_layers, sizes, batch, members, in_dtype, x, w_compute, params, h, 0, out,
+                      nullptr, stream);
+}
+
+extern "C" int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                                    const void* w_compute, const float* params, int head, const uint8_t* mask,
+                                    float* out, int32_t* actions, void* stream) {
+  return sb_mlp_forward_fused_ensemble(n_layers, sizes, batch, 1, in_dtype, x, w_compute, params, head, mask, out,
+                                       actions, stream);
+}
+
+extern "C" int sb_mlp_forward_fused_head(int n_layers, const int* sizes, int batch, int members, int in_dtype,
+                                         const void* x, const void* w_compute, const float* params, int hidden_norm,
+                                         const sb_head_spec* head, float* out, void* stream) {
+  if (!head) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused_head: head is null");
+  if (head->flags & SB_EPI_BINARIZE) return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused_head: no sign hash in the fused kernel");
+  return fused_launch("sb_mlp_forward_fused_head", n_layers, sizes, batch, members, in_dtype, x, w_compute, params,
+                      fused_head_from_spec(head), hidden_norm, out, nullptr, stream);
+}
+
+extern "C" int sb_policy_decide(const sb_decide_args* a, void* stream) {
+  if (!a) return sb_fail(SB_ERR_BAD_ARG, "sb_policy_decide: null arguments");
+  if (a->rows < 0 || a->rows > 0x7fffffffLL) return sb_fail(SB_ERR_BAD_ARG, "sb_policy_decide: rows out of range");
+  if (a->rows == 0) return SB_OK;
+  if (!a->sizes || a->n_layers < 1) return sb_fail(SB_ERR_BAD_ARG, "sb_policy_decide: no network");
+  if (!a->output_probs || !a->output_indices || !a->ensemble_id || !a->action || !a->sampling_prob_selected ||
+      !a->sampling_prob_ensemble || !a->tile_counters || !a->x)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_policy_decide: every output buffer, the input workspace x and tile_counters are required");
+  if (a->head_flags & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING))
+    return sb_fail(SB_ERR_BAD_ARG, "sb_policy_decide: head_flags may hold SB_EPI_MASKED_SOFTMAX and SB_EPI_REGRET_MATCHING");
+  int rc;
+  if (a->fields) {
+    int features = a->n_dense;
+    for (int j = 0; j < a->n_fields; ++j) features += a->widths ? a->widths[j] : 0;
+    if (features != a->sizes[0])
+      return sb_fail(SB_ERR_BAD_ARG, "sb_policy_decide: the state layout describes %d features, the net takes %d", features, a->sizes[0]);
+    rc = sb_encode_states(a->fields, a->n_fields, a->widths, a->dense, a->n_dense, a->x, a->rows, a->in_dtype, stream);
+    if (rc != SB_OK) return rc;
+  }
+  SbRowHead h;
+  memset(&h, 0, sizeof(h));
+  h.flags = a->head_flags | SB_EPI_SAMPLE;
+  h.prefix = a->prefix < 0 ? -1 : a->prefix;
+  h.mask = a->mask;
+  h.sample_out = a->output_indices;
+  h.seed = a->seed; h.row_offset = a->row_offset; h.position = 0;
+  FusedDecide d;
+  d.tile_counters = a->tile_counters; d.ensemble_id = a->ensemble_id; d.action = a->action;
+  d.prob_selected = a->sampling_prob_selected; d.prob_ensemble = a->sampling_prob_ensemble;
+  return fused_launch("sb_policy_decide", a->n_layers, a->sizes, (int)a->rows, a->members, a->in_dtype, a->x, a->w_compute,
+                      a->params, h, a->hidden_norm, a->output_probs, &d, stream);
 }

@@ -7,6 +7,7 @@
 // One warp owns one row; lanes stride over the columns with warp-shuffle
 // reductions, so any column count works.
 #include "common.cuh"
+#include "row_head.cuh"
 
 namespace {
 
@@ -249,6 +250,42 @@ __global__ void row_sample_kernel(const float* __restrict__ x, const float* __re
   }
 }
 
+// The same with the uniform number drawn on the device: row r uses output `position` of the Philox
+// stream (seed, row_offset + r), the draw the fused sampling heads make (row_head.cuh).
+__global__ void row_sample_seeded_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int rows, int cols,
+                                         unsigned long long seed, unsigned long long row_offset,
+                                         unsigned long long position) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const float* row = x + r * cols;
+    const float u = sb_uniform_open_closed(sb_philox_u32(seed, row_offset + (unsigned long long)r, position));
+    float s = 0.f, top = 0.f;
+    for (int j = 0; j < cols; ++j) {
+      const float v = row[j];
+      s = __fadd_rn(s, v);
+      if (v > 0.f) top = s;
+    }
+    const float threshold = __fmul_rn(u, top);
+    int pick = -1;
+    s = 0.f;
+    for (int j = 0; j < cols; ++j) {
+      const float v = row[j];
+      s = __fadd_rn(s, v);
+      if (v > 0.f && __fsub_rn(s, threshold) >= 0.f) {
+        pick = j;
+        break;
+      }
+    }
+    out[r] = pick;
+  }
+}
+
+__global__ void philox_uniform_kernel(float* __restrict__ out, long long n, unsigned long long seed,
+                                      unsigned long long row_offset, unsigned long long position) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = sb_uniform_open_closed(sb_philox_u32(seed, row_offset + (unsigned long long)i, position));
+}
+
 // Hash of a row: bit j = (x[r, j] > 0), the word taken modulo `modulo` (local_binarize,
 // ml/primitives.spi:816-821; rows of at most 32 values, where the shift is defined).
 __global__ void row_binarize_kernel(const float* __restrict__ x, uint32_t* __restrict__ out, int rows, int cols,
@@ -332,6 +369,28 @@ int sb_row_sample(const float* probs, const float* uniforms, int32_t* out, int r
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
   if (!uniforms) return sb_fail(SB_ERR_BAD_ARG, "sb_row_sample: uniforms is null");
   row_sample_kernel<<<grid_for(rows, 256), 256, 0, (cudaStream_t)stream>>>(probs, uniforms, out, rows, cols);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_row_sample_seeded(const float* probs, int32_t* out, int rows, int cols, unsigned long long seed,
+                         unsigned long long row_offset, unsigned long long position, void* stream) {
+  int rc = row_args_ok("sb_row_sample_seeded", probs, out, rows, cols);
+  if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  row_sample_seeded_kernel<<<grid_for(rows, 256), 256, 0, (cudaStream_t)stream>>>(probs, out, rows, cols, seed, row_offset,
+                                                                                  position);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+int sb_philox_uniform(float* out, long long n, unsigned long long seed, unsigned long long row_offset,
+                      unsigned long long position, void* stream) {
+  if (n < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_philox_uniform: negative length");
+  if (n == 0) return SB_OK;
+  if (!out) return sb_fail(SB_ERR_BAD_ARG, "sb_philox_uniform: null output");
+  philox_uniform_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(out, n, seed, row_offset, position);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;

@@ -7,7 +7,7 @@ library every operation raises.
 from ._lib import SpiralError, LIB_PATH  # noqa: F401
 from .device import (DeviceArray, Event, Stream, wait_event, GemmProfile, launch_count, device_count, device_ptr, device_status, check_device, mem_info, set_device,  # noqa: F401
                      synchronize)
-from .matmul import matmul, matmul_plan, matmul_tf32  # noqa: F401
+from .matmul import head_spec, matmul, matmul_head, matmul_plan, matmul_tf32  # noqa: F401
 from . import primitives  # noqa: F401
 from .models import EnsemblePolicyMLP, PolicyMLP, param_offsets, to_storage  # noqa: F401
 from . import layers  # noqa: F401

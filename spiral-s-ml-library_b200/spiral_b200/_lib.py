@@ -24,6 +24,14 @@ DTYPE_CODES = {"f32": F32, "tf32": TF32, "bf16": BF16, "f16": F16, "i32": I32, "
 EPI_NONE, EPI_BIAS, EPI_RELU, EPI_RELU_GRAD = 0, 1, 2, 4
 EPI_MASKED_SOFTMAX, EPI_REGRET_MATCHING, EPI_ARGMAX = 8, 16, 32
 EPI_RELU_MASK_OUT, EPI_RELU_GRAD_MASK, EPI_COLSUM_OUT = 64, 128, 256
+EPI_SAMPLE, EPI_BINARIZE, EPI_LN_L2 = 512, 1024, 2048
+
+
+class HeadSpec(ctypes.Structure):
+    """sb_head_spec of include/spiral_b200.h."""
+    _fields_ = [("flags", c_int), ("prefix", c_int), ("mask", c_void_p), ("argmax_out", c_void_p),
+                ("sample_out", c_void_p), ("hash_out", c_void_p), ("modulo", ctypes.c_uint32),
+                ("seed", ctypes.c_ulonglong), ("row_offset", ctypes.c_ulonglong), ("position", ctypes.c_ulonglong)]
 
 
 class SpiralError(RuntimeError):
@@ -40,6 +48,18 @@ _F = c_float
 _Z = c_size_t
 _PP = POINTER(c_void_p)
 _IP = POINTER(c_int)
+
+class DecideArgs(ctypes.Structure):
+    """sb_decide_args of include/spiral_b200.h."""
+    _fields_ = [("n_layers", c_int), ("sizes", POINTER(c_int)), ("members", c_int), ("in_dtype", c_int),
+                ("w_compute", c_void_p), ("params", c_void_p), ("hidden_norm", c_int), ("rows", ctypes.c_longlong),
+                ("fields", c_void_p), ("n_fields", c_int), ("widths", POINTER(c_int)), ("dense", c_void_p),
+                ("n_dense", c_int), ("x", c_void_p), ("head_flags", c_int), ("prefix", c_int), ("mask", c_void_p),
+                ("seed", ctypes.c_ulonglong), ("row_offset", ctypes.c_ulonglong), ("output_probs", c_void_p),
+                ("output_indices", c_void_p), ("ensemble_id", c_void_p), ("action", c_void_p),
+                ("sampling_prob_selected", c_void_p), ("sampling_prob_ensemble", c_void_p),
+                ("tile_counters", c_void_p)]
+
 
 # name -> (restype, argtypes); every symbol include/spiral_b200.h declares.
 SIGNATURES = {
@@ -75,12 +95,15 @@ SIGNATURES = {
     "sb_gemm_profile_entry": (_I, [_I, POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "sb_matmul_tf32": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _P]),
     "sb_matmul_ex": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "sb_matmul_head": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P, POINTER(HeadSpec), _P]),
     "sb_matmul_plan": (_I, [_I, _I, _I, _I, _I, _I, _I, _IP]),
     "sb_relu": (_I, [_P, _P, _Z, _P]),
     "sb_row_softmax": (_I, [_P, _P, _I, _I, _P, _I, _P]),
     "sb_row_regret_matching": (_I, [_P, _P, _I, _I, _P, _I, _P]),
     "sb_row_argmax": (_I, [_P, _P, _I, _I, _P]),
     "sb_row_sample": (_I, [_P, _P, _P, _I, _I, _P]),
+    "sb_row_sample_seeded": (_I, [_P, _P, _I, _I, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, _P]),
+    "sb_philox_uniform": (_I, [_P, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, _P]),
     "sb_row_binarize": (_I, [_P, _P, _I, _I, ctypes.c_uint, _P]),
     "sb_row_ln_l2": (_I, [_P, _P, _I, _I, _P]),
     "sb_convert": (_I, [_P, _P, _Z, _I, _P]),
@@ -97,6 +120,8 @@ SIGNATURES = {
     "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused_ensemble": (_I, [_I, _IP, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "sb_mlp_forward_fused_head": (_I, [_I, _IP, _I, _I, _I, _P, _P, _P, _I, POINTER(HeadSpec), _P, _P]),
+    "sb_policy_decide": (_I, [POINTER(DecideArgs), _P]),
     "sb_mlp_forward_static": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_backward_scratch_bytes": (_I, [_I, _IP, _I, _I, POINTER(c_size_t)]),
     "sb_mlp_backward": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _P, _I, _P, _Z, _P, _P]),

@@ -16,9 +16,8 @@ the reference (blocks, rows, features); the leading dimensions are the batch.
 """
 import numpy as np
 
-from . import _lib
 from . import primitives
-from .device import DeviceArray, stream_ptr
+from .device import DeviceArray
 from .matmul import matmul as _matmul
 
 WEIGHT_ID, WORKSPACE_ID, WEIGHT_ADJOINT_ID = 0, 1, 2     # ml/layers.spi:6-12
@@ -111,8 +110,8 @@ def masked_softmax_and_discrete_sample(size, x):
     """Prefix-masked softmax followed by one sampled index per row (ml/layers.spi:422-431).  The node's
     output is the int32 index tensor [..., 1]; its source node holds the probabilities.  The uniform
     numbers come from the caller (``Model.uniforms(node).upload(u)``, one in (0, 1] per row) or, when
-    ``graph_run_host`` is given a seed, from a host Philox stream -- the reference draws them on the
-    device from its per-thread generator."""
+    ``graph_run_host`` is given a seed, are drawn on the device inside the head from a Philox4x32-10
+    stream per row, as the reference draws them from its per-thread generator."""
     probs = Node("softmax", x, x.dims, size=int(size))
     return Node("sample", probs, x.dims[:-1] + (1,))
 
@@ -150,11 +149,13 @@ class Model:
             self.arenas = [DeviceArray.zeros((max(b, 16),), "u8") for b in self.partition_bytes]
         return self
 
-    def tensor(self, node):
-        """Typed view of a node's output inside the workspace arena."""
+    def tensor(self, node, rounded=False):
+        """Typed view of a node's output inside the workspace arena.  ``rounded``: tagged 'tf32' so that the
+        GEMM that writes it rounds the values to TF32 (the input of the next tensor-core layer)."""
         if node.op in ("argmax", "sample", "binarize"):
             return self.arenas[WORKSPACE_ID].view((node.rows,), "i32", node.offset)
-        return self.arenas[WORKSPACE_ID].view((node.rows, node.cols), "f32", node.offset)
+        return self.arenas[WORKSPACE_ID].view((node.rows, node.cols),
+                                              "tf32" if rounded and self.in_dtype == "tf32" else "f32", node.offset)
 
     def uniforms(self, node):
         """The fp32 [rows] tensor of uniform numbers a sample node consumes."""
@@ -168,7 +169,11 @@ class Model:
                 ensemble = 0            # plain layers are shared by all members
             else:
                 raise IndexError("ensemble member %d of %d" % (ensemble, members))
-        return self.arenas[WEIGHT_ID].view((node.attrs["fan_out"], node.attrs["fan_in"]), "f32",
+        # In the TF32 class the view is tagged 'tf32': an upload rounds the weights to TF32 (nearest even)
+        # once, as the reference rounds every operand element when it loads a fragment
+        # (ml/matmul/kernel.spi:197,212); the tensor core itself would truncate unrounded fp32.
+        return self.arenas[WEIGHT_ID].view((node.attrs["fan_out"], node.attrs["fan_in"]),
+                                           "tf32" if self.in_dtype == "tf32" else "f32",
                                            node.weight_offset + ensemble * node.attrs["member_bytes"])
 
 
@@ -213,45 +218,72 @@ def key_extract(model, key):
     raise KeyError(key)
 
 
-def graph_run_host(model, stream=None, ensemble=0, seed=None):
+def graph_run_host(model, stream=None, ensemble=0, seed=None, row_offset=0):
     """Runs the graph (ml/layers.spi:339-344) and returns the output tensor of the last node.
     ``ensemble`` picks the member whose weights the ``matmul_ensemble`` layers use, as the reference's
     ``graph_run_host model {ensemble}`` does (ml/layers.spi:623); plain layers are the same for all.
-    ``seed``: sample nodes get fresh uniform numbers from a host Philox stream of this seed (otherwise
-    they use what the caller uploaded into ``model.uniforms(node)``)."""
+    ``seed``: sample nodes draw on the device, row r from output ``ensemble`` of the Philox stream
+    (seed, row_offset + r) -- one draw per member and row, like the reference's per-thread generator
+    that every member's run advances (ml/models.spi:47-49); without a seed they use the uniform numbers
+    the caller uploaded into ``model.uniforms(node)``.
+
+    Fusion: ``matmul [-> ln_l2] -> relu`` is one GEMM launch, and so is ``matmul -> softmax /
+    regret_matching [-> sample] | argmax | binarize`` (a prefix mask is an argument of the head: no mask
+    matrix, no allocation, no synchronisation); everything else runs as a stand-alone kernel."""
     nodes = model.nodes
+    tc = model.in_dtype == "tf32"
     i = 1
     while i < len(nodes):
         n = nodes[i]
         src = model.tensor(n.src)
         if n.op == "matmul":
-            epilogue, last, j, mask_dev = [], n, i + 1, None
-            if j < len(nodes) and nodes[j].op == "relu":
-                epilogue.append("relu")
-                last, j = nodes[j], j + 1
-            elif model.in_dtype == "tf32":
-                # softmax and regret matching fuse (in that order) when they share one prefix mask
-                k, size, mask_needed = j, None, False
-                while k < len(nodes) and nodes[k].op in ("softmax", "regret_matching"):
-                    want = "masked_softmax" if nodes[k].op == "softmax" else "regret_matching"
-                    if want in epilogue or (want == "masked_softmax" and "regret_matching" in epilogue):
-                        break
-                    if size is not None and nodes[k].attrs["size"] != size:
-                        break
-                    size = nodes[k].attrs["size"]
-                    epilogue.append(want)
-                    last, k = nodes[k], k + 1
-                j = k
-                mask_needed = size is not None and size >= 0
-                if mask_needed:
-                    m = np.zeros((n.rows, n.cols), np.uint8)
-                    m[:, :size] = 1
-                    mask_dev = DeviceArray.from_numpy(m)
-            out = model.tensor(last)
-            _matmul(False, True, 1.0, src, model.weight(n, ensemble), 0.0, out, in_dtype=model.in_dtype,
-                    epilogue=tuple(epilogue), mask=mask_dev, stream=stream)
-            if mask_dev is not None:
-                _lib.call("sb_stream_sync", stream_ptr(stream))      # the mask buffer is released on return
+            j = i + 1
+            w = model.weight(n, ensemble)
+            # hidden layer: [ln_l2 ->] relu
+            k, epilogue = j, []
+            if tc and k + 1 < len(nodes) and nodes[k].op == "ln_l2" and nodes[k + 1].op == "relu" \
+                    and n.cols % 32 == 0 and n.cols <= 256:
+                epilogue, k = ["ln_l2", "relu"], k + 2
+            elif k < len(nodes) and nodes[k].op == "relu":
+                epilogue, k = ["relu"], k + 1
+            if epilogue:
+                feeds_matmul = k < len(nodes) and nodes[k].op == "matmul"
+                _matmul(False, True, 1.0, src, w, 0.0, model.tensor(nodes[k - 1], rounded=feeds_matmul),
+                        in_dtype=model.in_dtype, epilogue=tuple(epilogue), stream=stream)
+                i = k
+                continue
+            # row head: softmax and regret matching fuse (in that order) when they share one prefix,
+            # then one of sample / argmax; or the sign hash by itself
+            head, size, last, k = [], None, n, j
+            while k < len(nodes) and nodes[k].op in ("softmax", "regret_matching"):
+                want = "masked_softmax" if nodes[k].op == "softmax" else "regret_matching"
+                if want in head or (want == "masked_softmax" and "regret_matching" in head):
+                    break
+                if size is not None and nodes[k].attrs["size"] != size:
+                    break
+                size = nodes[k].attrs["size"]
+                head.append(want)
+                last, k = nodes[k], k + 1
+            kw = {}
+            if head and k < len(nodes) and nodes[k].op == "sample" and seed is not None:
+                head.append("sample")
+                kw = dict(sample_out=model.tensor(nodes[k]), seed=int(seed), row_offset=int(row_offset), position=int(ensemble))
+                k += 1
+            elif head and k < len(nodes) and nodes[k].op == "argmax":
+                head.append("argmax")
+                kw = dict(argmax_out=model.tensor(nodes[k]))
+                k += 1
+            elif not head and k < len(nodes) and nodes[k].op == "binarize" and n.cols <= 32:
+                head.append("binarize")
+                kw = dict(hash_out=model.tensor(nodes[k]), modulo=nodes[k].attrs["modulo"])
+                k += 1
+            if head:
+                from .matmul import head_spec, matmul_head
+                spec = head_spec(tuple(head), prefix=-1 if size is None else size, **kw)
+                matmul_head(False, True, 1.0, src, w, 0.0, model.tensor(last), spec, in_dtype=model.in_dtype, stream=stream)
+                i = k
+                continue
+            _matmul(False, True, 1.0, src, w, 0.0, model.tensor(n), in_dtype=model.in_dtype, stream=stream)
             i = j
             continue
         out = model.tensor(n)
@@ -269,9 +301,9 @@ def graph_run_host(model, stream=None, ensemble=0, seed=None):
             primitives.binarize(n.attrs["modulo"], src, out, stream=stream)
         elif n.op == "sample":
             if seed is not None:
-                gen = np.random.Generator(np.random.Philox(int(seed)))
-                model.uniforms(n).upload((1.0 - gen.random(n.rows, dtype=np.float32)).astype(np.float32))
-            primitives.sample(src, model.uniforms(n), out, stream=stream)
+                primitives.sample_seeded(src, out, seed, row_offset=row_offset, position=ensemble, stream=stream)
+            else:
+                primitives.sample(src, model.uniforms(n), out, stream=stream)
         else:
             raise ValueError("unknown node %r" % n.op)
         i += 1

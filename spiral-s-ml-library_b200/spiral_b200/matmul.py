@@ -13,7 +13,7 @@ EPILOGUE_FLAGS = {
     "bias": _lib.EPI_BIAS, "relu": _lib.EPI_RELU, "relu_grad": _lib.EPI_RELU_GRAD,
     "masked_softmax": _lib.EPI_MASKED_SOFTMAX, "regret_matching": _lib.EPI_REGRET_MATCHING,
     "argmax": _lib.EPI_ARGMAX, "relu_mask_out": _lib.EPI_RELU_MASK_OUT, "relu_grad_mask": _lib.EPI_RELU_GRAD_MASK,
-    "colsum_out": _lib.EPI_COLSUM_OUT,
+    "colsum_out": _lib.EPI_COLSUM_OUT, "ln_l2": _lib.EPI_LN_L2,
 }
 
 
@@ -45,7 +45,8 @@ def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype=None, epilogue=(), b
     """
     m, n, k = _dims(bool(a_trans), bool(b_trans), a, b, c)
     storage = dtype_tag(a)
-    if storage != dtype_tag(b):
+    fp32_storage = ("f32", "tf32")                 # 'tf32' tags fp32 storage whose values are TF32-rounded
+    if storage != dtype_tag(b) and not (storage in fp32_storage and dtype_tag(b) in fp32_storage):
         raise TypeError("a and b must share a storage dtype (%s vs %s)" % (storage, dtype_tag(b)))
     if in_dtype is None:
         in_dtype = "tf32" if storage in ("f32", "tf32") else storage
@@ -60,6 +61,40 @@ def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype=None, epilogue=(), b
               device_ptr(a), device_ptr(b), ctypes.c_float(beta), device_ptr(c), m, n, k,
               _lib.DTYPE_CODES[in_dtype], _lib.DTYPE_CODES[out_dtype], epi, device_ptr(bias),
               device_ptr(mask), device_ptr(aux_in), device_ptr(aux_out), stream_ptr(stream))
+    return c
+
+
+HEAD_FLAGS = {"masked_softmax": _lib.EPI_MASKED_SOFTMAX, "softmax": _lib.EPI_MASKED_SOFTMAX,
+              "regret_matching": _lib.EPI_REGRET_MATCHING, "argmax": _lib.EPI_ARGMAX, "sample": _lib.EPI_SAMPLE,
+              "binarize": _lib.EPI_BINARIZE}
+
+
+def head_spec(head=(), prefix=-1, mask=None, argmax_out=None, sample_out=None, hash_out=None, modulo=0,
+              seed=0, row_offset=0, position=0):
+    """The ctypes ``sb_head_spec`` of a row head: ``head`` names from HEAD_FLAGS; legal columns are
+    ``j < prefix`` when ``prefix >= 0`` (the reference's ``masked_softmax size`` etc.), else ``mask``,
+    else all; a sampling head draws output ``position`` of the Philox stream (seed, row_offset + row)."""
+    flags = 0
+    for name in head:
+        flags |= HEAD_FLAGS[name]
+    return _lib.HeadSpec(flags, int(prefix), device_ptr(mask), device_ptr(argmax_out), device_ptr(sample_out),
+                         device_ptr(hash_out), int(modulo), int(seed), int(row_offset), int(position))
+
+
+def matmul_head(a_trans, b_trans, alpha, a, b, beta, c, spec, in_dtype=None, epilogue=(), bias=None, stream=None):
+    """``c <- head(alpha * op(a) @ op(b) + beta * c (+ bias) (relu))`` with the row head ``spec``
+    (``head_spec(...)``); fp32 output.  One launch for rows of up to 64 columns, or up to 256 under a
+    prefix mask of at most 64 columns; nothing is allocated."""
+    m, n, k = _dims(bool(a_trans), bool(b_trans), a, b, c)
+    storage = dtype_tag(a)
+    if in_dtype is None:
+        in_dtype = "tf32" if storage in ("f32", "tf32") else storage
+    epi = 0
+    for name in epilogue:
+        epi |= EPILOGUE_FLAGS[name]
+    _lib.call("sb_matmul_head", int(bool(a_trans)), int(bool(b_trans)), ctypes.c_float(alpha), device_ptr(a),
+              device_ptr(b), ctypes.c_float(beta), device_ptr(c), m, n, k, _lib.DTYPE_CODES[in_dtype], epi,
+              device_ptr(bias), ctypes.byref(spec), stream_ptr(stream))
     return c
 
 

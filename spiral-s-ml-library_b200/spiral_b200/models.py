@@ -231,11 +231,16 @@ class EnsemblePolicyMLP:
     ml/layers.spi:468-471, and runs the graph once per member, ml/models.spi:47-49).
 
     16-bit arithmetic classes and the fused kernel's width limits only (input <= 256, hidden layers
-    multiples of 64 up to 256, at most 32 outputs).  Outputs: ``probs`` fp32 [members, batch, n_out]
-    and, with an argmax head, ``actions`` int32 [members, batch].
+    multiples of 64 up to 256, at most 64 outputs -- or 256 under a prefix mask of at most 64 columns).
+    Outputs: ``probs`` fp32 [members, batch, n_out] and, with an argmax head, ``actions`` int32
+    [members, batch].
+
+    ``hidden_norm``: ln_l2 before every ReLU, as in the reference's nets (ml/layers.spi:594-603; no bias
+    then).  ``decide`` (below) is the reference's per-decision call ml/models.spi:9-76.
     """
 
-    def __init__(self, sizes, batch, members, in_dtype="f16", head=("masked_softmax",), with_bias=True):
+    def __init__(self, sizes, batch, members, in_dtype="f16", head=("masked_softmax",), with_bias=True,
+                 hidden_norm=False):
         if in_dtype not in ("bf16", "f16"):
             raise ValueError("the fused ensemble forward runs in 'bf16' or 'f16'")
         self.sizes = [int(s) for s in sizes]
@@ -246,10 +251,12 @@ class EnsemblePolicyMLP:
         self.head_flags = 0
         for h in self.head:
             self.head_flags |= HEAD_FLAGS[h]
-        self.with_bias = bool(with_bias)
+        self.hidden_norm = bool(hidden_norm)
+        self.with_bias = bool(with_bias) and not self.hidden_norm
         self.offsets = param_offsets(self.sizes)
         self.n_params = self.offsets[-1]
         self._sizes_c = (ctypes.c_int * len(self.sizes))(*self.sizes)
+        self._decide = None
         self.params = DeviceArray.zeros((self.members, self.n_params), "f32")
         self.w_compute = DeviceArray.zeros((self.members, self.n_params), self.storage)
         self.probs = DeviceArray((self.members, self.batch, self.sizes[-1]), "f32")
@@ -282,3 +289,72 @@ class EnsemblePolicyMLP:
                   self.params.ptr if self.with_bias else None, self.head_flags, device_ptr(mask), self.probs.ptr,
                   self.actions.ptr if self.actions is not None else None, stream_ptr(stream))
         return self.probs
+
+    def forward_head(self, x, head=("masked_softmax",), prefix=-1, mask=None, seed=0, row_offset=0, position=0,
+                     stream=None):
+        """All members with the head given in full: ``head`` names from ``matmul.HEAD_FLAGS`` (softmax,
+        regret matching, argmax, sample), legal columns ``j < prefix`` (or ``mask``), sampling from the
+        Philox stream (seed, row_offset + row), member e using output ``position + e``.  Fills ``probs``,
+        ``actions`` (argmax) and ``indices`` (sample)."""
+        from .matmul import head_spec
+        if "sample" in head and getattr(self, "indices", None) is None:
+            self.indices = DeviceArray((self.members, self.batch), "i32")
+        if "argmax" in head and self.actions is None:
+            self.actions = DeviceArray((self.members, self.batch), "i32")
+        spec = head_spec(tuple(head), prefix=prefix, mask=mask, argmax_out=self.actions if "argmax" in head else None,
+                         sample_out=self.indices if "sample" in head else None, seed=seed, row_offset=row_offset,
+                         position=position)
+        _lib.call("sb_mlp_forward_fused_head", self.n_layers, self._sizes_c, self.batch, self.members,
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr,
+                  self.params.ptr if self.with_bias else None, int(self.hidden_norm), ctypes.byref(spec),
+                  self.probs.ptr, stream_ptr(stream))
+        return self.probs
+
+    def decide(self, seed, fields=None, widths=None, dense=None, x=None, head=("masked_softmax",), prefix=-1,
+               mask=None, row_offset=0, stream=None):
+        """One decision per game state: the reference's ``models.run`` (ml/models.spi:9-76).
+
+        The states come either as compact records (``fields`` uint8 [batch, len(widths)] and optional
+        ``dense`` values, serialised into the network input on the device) or as a ready input ``x``.
+        Every member samples an action per state from its head, a member is drawn per state, and the
+        result is a dict of device arrays: ``action`` int32 [batch], ``ensemble_id`` int32 [batch],
+        ``sampling_prob_selected`` fp32 [batch], ``sampling_prob_ensemble`` fp32 [batch, members],
+        plus the reference's tensors ``output_probs`` [members, batch, n_out] and ``output_indices``
+        [members, batch].  Two kernel launches (one when ``x`` is given).  Buffers are created on the
+        first call and reused."""
+        if self._decide is None:
+            b, e = self.batch, self.members
+            self._decide = dict(
+                x=DeviceArray((b, self.sizes[0]), self.storage), output_indices=DeviceArray((e, b), "i32"),
+                ensemble_id=DeviceArray((b,), "i32"), action=DeviceArray((b,), "i32"),
+                sampling_prob_selected=DeviceArray((b,), "f32"), sampling_prob_ensemble=DeviceArray((b, e), "f32"),
+                tile_counters=DeviceArray.zeros(((b + 127) // 128,), "i32"))
+        d = self._decide
+        flags = 0
+        for name in head:
+            flags |= HEAD_FLAGS[name]
+        a = _lib.DecideArgs()
+        a.n_layers, a.sizes, a.members = self.n_layers, self._sizes_c, self.members
+        a.in_dtype = _lib.DTYPE_CODES[self.in_dtype]
+        a.w_compute, a.params = self.w_compute.ptr, (self.params.ptr if self.with_bias else None)
+        a.hidden_norm, a.rows = int(self.hidden_norm), self.batch
+        if fields is not None:
+            widths = [int(w) for w in widths]
+            self._widths_c = (ctypes.c_int * len(widths))(*widths)
+            a.fields, a.n_fields, a.widths = device_ptr(fields), len(widths), self._widths_c
+            a.dense, a.n_dense = device_ptr(dense), (0 if dense is None else int(dense.shape[1]))
+            a.x = d["x"].ptr
+        else:
+            a.fields, a.n_fields, a.dense, a.n_dense = None, 0, None, 0
+            a.x = device_ptr(x)
+        a.head_flags, a.prefix, a.mask = flags, int(prefix), device_ptr(mask)
+        a.seed, a.row_offset = int(seed), int(row_offset)
+        a.output_probs, a.output_indices = self.probs.ptr, d["output_indices"].ptr
+        a.ensemble_id, a.action = d["ensemble_id"].ptr, d["action"].ptr
+        a.sampling_prob_selected, a.sampling_prob_ensemble = d["sampling_prob_selected"].ptr, d["sampling_prob_ensemble"].ptr
+        a.tile_counters = d["tile_counters"].ptr
+        _lib.call("sb_policy_decide", ctypes.byref(a), stream_ptr(stream))
+        out = {k: d[k] for k in ("action", "ensemble_id", "sampling_prob_selected", "sampling_prob_ensemble",
+                                 "output_indices")}
+        out["output_probs"] = self.probs
+        return out

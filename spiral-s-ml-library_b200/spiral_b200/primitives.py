@@ -62,6 +62,25 @@ def sample(probs, uniforms, out, stream=None):
     return out
 
 
+def sample_seeded(probs, out, seed, row_offset=0, position=0, stream=None):
+    """The same with the uniform numbers drawn on the device as the reference does: row r uses output
+    ``position`` of the Philox4x32-10 stream (seed, row_offset + r)."""
+    import ctypes
+    rows, cols = _rows_cols(probs)
+    _lib.call("sb_row_sample_seeded", device_ptr(probs), device_ptr(out), rows, cols, ctypes.c_ulonglong(int(seed)),
+              ctypes.c_ulonglong(int(row_offset)), ctypes.c_ulonglong(int(position)), stream_ptr(stream))
+    return out
+
+
+def philox_uniform(out, seed, row_offset=0, position=0, stream=None):
+    """Fills the fp32 device array ``out`` with the uniform numbers in (0, 1] a sampling head draws:
+    element i = output ``position`` of the stream (seed, row_offset + i)."""
+    import ctypes
+    _lib.call("sb_philox_uniform", device_ptr(out), ctypes.c_longlong(int(out.size)), ctypes.c_ulonglong(int(seed)),
+              ctypes.c_ulonglong(int(row_offset)), ctypes.c_ulonglong(int(position)), stream_ptr(stream))
+    return out
+
+
 def binarize(modulo, x, out, stream=None):
     """Row hash: bit j = (x[r, j] > 0), modulo ``modulo`` (ml/primitives.spi:816-821); ``out`` is an int32
     device array [rows] holding the unsigned values."""

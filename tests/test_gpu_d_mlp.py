@@ -290,9 +290,11 @@ def test_layer_graph_sampling_head(gpu):
     model = L.pass_init(L.create_model(g))
     x = so.round_tf32(so.rng(28).normal(size=(512, 32)).astype(np.float32))
     L.key_extract(model, "input").upload(x)
+    l0 = gpu.launch_count()
     idx = L.graph_run_host(model, seed=7).numpy().copy()
+    assert gpu.launch_count() - l0 == 1                     # matmul + masked softmax + sampling: one launch
     probs = model.tensor(model.nodes[-2]).numpy()
-    u = model.uniforms(model.nodes[-1]).numpy()
+    u = so.philox_uniform(7, np.arange(512), 0)             # the draw the head made: stream (seed, row), output 0
     np.testing.assert_array_equal(idx, so.discrete_sampling(probs, u))
     assert idx.min() >= 0 and idx.max() < 5
     w = so.round_tf32(L.get_weights(model)[0])

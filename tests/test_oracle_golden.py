@@ -155,3 +155,37 @@ def test_binarize_oracle():
     x = np.array([[1.0, -1.0, 0.0, 2.0], [0.0, 0.0, 0.0, 0.0], [5.0, 5.0, 5.0, 5.0]], np.float32)
     np.testing.assert_array_equal(so.binarize(x, 1 << 20), np.array([0b1001, 0, 0b1111], np.uint32))
     np.testing.assert_array_equal(so.binarize(x, 7), np.array([9 % 7, 0, 15 % 7], np.uint32))
+
+
+def test_philox4x32_10_known_answers():
+    """The oracle's Philox4x32-10 against the known-answer vectors published with the algorithm
+    (Salmon et al., SC 2011: counter and key all zero, all ones, and the digits of pi)."""
+    cases = [
+        ([0, 0, 0, 0], [0, 0], [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]),
+        ([0xffffffff] * 4, [0xffffffff] * 2, [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]),
+        ([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0],
+         [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]),
+    ]
+    for counter, key, want in cases:
+        got = [int(w) for w in so.philox4x32_10(counter, key)]
+        assert got == want
+
+
+def test_philox_stream_layout_and_uniform_range():
+    """Output n of a stream is word n % 4 of block n // 4; uniforms lie in (0, 1] (2^-33 for a zero draw,
+    exactly 1 for the largest); the bounded draw is below its bound."""
+    sub = np.arange(7, dtype=np.uint64) + np.uint64(2 ** 33)
+    block1 = so.philox4x32_10([1, 0, sub & np.uint64(0xFFFFFFFF), sub >> np.uint64(32)], [99, 5])
+    for w in range(4):
+        np.testing.assert_array_equal(so.philox_u32(99 + (5 << 32), sub, 4 + w), block1[w])
+    assert so.uniform_open_closed(np.uint32(0)) == np.float32(2.0 ** -33)
+    assert so.uniform_open_closed(np.uint32(0xFFFFFFFF)) == np.float32(1.0)
+    below = so.philox_below(1, np.arange(1000), 0, 7)
+    assert below.min() >= 0 and below.max() < 7 and len(np.unique(below)) == 7
+
+
+def test_discrete_sampling_picks_by_the_cumulative_distribution():
+    p = np.array([[0.0, 0.25, 0.0, 0.5, 0.25, 0.0]], np.float32)
+    for u, want in ((1e-6, 1), (0.25, 1), (0.2500001, 3), (0.75, 3), (0.76, 4), (1.0, 4)):
+        assert so.discrete_sampling(p, np.array([u], np.float32))[0] == want
+    assert so.discrete_sampling(np.zeros((1, 4), np.float32), np.array([0.5], np.float32))[0] == -1
