@@ -338,7 +338,7 @@ def run_ours(args, rank, world, local_rank):
     dense_store = to_store(denseh) if denseh is not None else None
 
     grads = None
-    peer_mode = training and world > 1 and args.update == "peer"
+    peer_mode = training and world > 1 and args.update in ("peer", "peer-overlap")
     if training and world > 1 and not peer_mode:
         n_params = sb.param_offsets(sizes)[-1]
         grads = torch.zeros(n_params, dtype=torch.float32, device="cuda")
@@ -378,7 +378,8 @@ def run_ours(args, rank, world, local_rank):
             return out
         peer = sb.PeerUpdate(net, world, rank, exchange)
     dp = sb.DataParallel(net, gbatch, all_reduce=(lambda g: dist.all_reduce(g)) if dist is not None else None,
-                         world_size=world, rank=rank, all_reduce_segment=seg, peer_update=peer)
+                         world_size=world, rank=rank, all_reduce_segment=seg, peer_update=peer,
+                         overlap_update=args.update == "peer-overlap", reserve_smem=args.reserve_smem)
 
     def step():
         if training:
@@ -555,7 +556,8 @@ def run_ours(args, rank, world, local_rank):
         "dtype": in_dtype, "data": "synthetic",
         "config": {"workload": workload, "layers": sizes, "global_batch": gbatch, "batch_per_gpu": batch,
                    "parallelism": "dp%d" % world, "lr": LR,
-                   "gradient_exchange": ("peer-memory reduce+update kernel" if peer_mode else "nccl all-reduce") if (training and world > 1) else "none",
+                   "gradient_exchange": (("peer-memory reduce+update kernel" + (", per layer beside the backward pass" if args.update == "peer-overlap" else ""))
+                                         if peer_mode else "nccl all-reduce") if (training and world > 1) else "none",
                    "l2": l2_note},
         "roofline": {"bound": "tensor", "kernel": "mlp_fused_kernel" if fused else "umma_gemm_kernel",
                      "achieved": round(achieved, 1), "peak": peak,
@@ -890,8 +892,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--overlap", action="store_true", help="per-layer asynchronous all-reduce instead of one at the end")
-    ap.add_argument("--update", choices=("peer", "nccl"), default="peer",
-                    help="N > 1 training: the library's reduce+update kernel over peer memory, or NCCL all-reduce + SGD")
+    ap.add_argument("--update", choices=("peer", "peer-overlap", "nccl"), default="peer",
+                    help="N > 1 training: the library's reduce+update kernel over peer memory (one launch after the "
+                         "backward pass, or per layer beside it), or NCCL all-reduce + SGD")
+    ap.add_argument("--reserve-smem", type=int, default=4096,
+                    help="peer-overlap: shared memory per SM the backward GEMMs leave free for the update CTAs")
     ap.add_argument("--layerwise", action="store_true", help="narrow-net inference through one GEMM per layer")
     ap.add_argument("--profile-case", choices=sorted(PROFILE_CASES), default=None,
                     help="run a few launches of one GEMM shape (for ncu) and exit")

@@ -181,6 +181,13 @@ int sb_matmul_head(int a_trans, int b_trans, float alpha, const void* A, const v
                    float* C, int M, int N, int K, int in_dtype, int epilogue, const float* bias,
                    const sb_head_spec* head, void* stream);
 
+/* Keeps `bytes` of shared memory per SM out of the GEMM's pipeline (0 = use all of it; rounded up to a
+ * KiB, at most 64 KiB) so that a CTA of another kernel -- the data-parallel update of the layers whose
+ * gradients are already complete -- can be resident beside a GEMM CTA and run in its idle issue
+ * slots.  A process-wide setting read at every GEMM launch; the pipeline gets shallower (a few per
+ * cent of GEMM throughput).  No counterpart in the reference (single device, one kernel at a time). */
+int sb_gemm_reserve_smem(int bytes);
+
 /* Tile-shape heuristic of the tensor-core path, exposed for tests: the
  * counterpart of matmul_config_tf32 (ml/matmul/run.spi:8-19).  Writes
  * {block_m, block_n, block_k_elems, stages, grid}. */

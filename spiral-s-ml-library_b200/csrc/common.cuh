@@ -65,13 +65,17 @@ void sb_prof_after(cudaStream_t s, double flops);
 
 // The tensor-core GEMM launcher (gemm_umma.cu); every argument is validated there.  `head`
 // describes the row head when `epi` holds a head flag (null: the legacy form -- byte mask in
-// `mask`, arg-max indices to `aux_out`).
+// `mask`, arg-max indices to `aux_out`).  Split-K: by default split s writes its own partial at
+// C + s * M * N.  With `split_partials` (room for splits * M * N floats) the launcher chooses: when C
+// can take TMA boxes every split ADDS its tile to the one fp32 matrix C (which the caller has zeroed)
+// through TMA reduce-add stores and *splits_used comes back as 1; otherwise the partials go to
+// `split_partials`, *splits_used tells how many, and the caller reduces them into C.
 struct SbRowHead;
 int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
                         void* aux_out, cudaStream_t stream, int splits = 1, int* splits_used = nullptr,
-                        const SbRowHead* head = nullptr);
+                        const SbRowHead* head = nullptr, void* split_partials = nullptr);
 // True when a row head over N columns (legal columns j < prefix when prefix >= 0) runs inside the GEMM.
 bool sb_umma_head_fits(int N, int prefix);
 
@@ -234,6 +238,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
 // bulk async-group.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t src_smem, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(src_smem)
+               : "memory");
+}
+// The same box added to the tensor in global memory (fp32 adds done by the memory system, so boxes
+// from different CTAs may target the same elements; the order of the additions is not fixed).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(src_smem)
                : "memory");
 }

@@ -88,6 +88,7 @@ struct UmmaGemmParams {
   int wide;            // 1: 16-bit output boxes span two chunks (64 columns, 128-byte rows)
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
   SbRowHead head;      // the row head, when epi holds a head flag
+  int reduce_add;      // 1: split-K tiles are added to one C through TMA reduce-add stores
 };
 
 __device__ __forceinline__ void tile_coords(const UmmaGemmParams& p, int tile, int& m_blk, int& n_blk) {
@@ -242,6 +243,8 @@ struct EpiShared {
   int block_n;
   float alpha, beta;
   int has_bias, relu, relu_grad, coalesced;
+  int reduce_add;           // finished boxes are ADDED to C (split-K accumulating into one matrix)
+  int split_rows;           // rows between two splits' outputs in the store map (0 when they share C)
   int ln_l2;                // divide every row by its sum of squares before the ReLU (SB_EPI_LN_L2; the tile spans the row)
   uint32_t box_base;        // shared-memory address of the first epilogue warp's 4 KB box
 };
@@ -374,7 +377,8 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(g_epi.tma_c, sbuf, wide ? col0 - 32 : col0, split * g_epi.M + row0_warp);
+        if (g_epi.reduce_add) tma_reduce_add_2d(g_epi.tma_c, sbuf, col0, row0_warp);
+        else tma_store_2d(g_epi.tma_c, sbuf, wide ? col0 - 32 : col0, split * g_epi.split_rows + row0_warp);
         bulk_commit_group();
       }
     }
@@ -750,6 +754,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     g_epi.has_bias = (p.epi & SB_EPI_BIAS) ? 1 : 0; g_epi.relu = (p.epi & SB_EPI_RELU) ? 1 : 0;
     g_epi.relu_grad = (p.epi & SB_EPI_RELU_GRAD) ? 1 : 0; g_epi.coalesced = p.coalesced;
     g_epi.ln_l2 = (p.epi & SB_EPI_LN_L2) ? 1 : 0;
+    g_epi.reduce_add = p.reduce_add; g_epi.split_rows = p.reduce_add ? 0 : p.M;
     g_epi.box_base = stage_base + p.epi_offset;
     g_head.C = reinterpret_cast<float*>(p.C); g_head.bias = p.bias; g_head.ldc = p.ldc; g_head.epi = p.epi;
     g_head.alpha = p.alpha; g_head.beta = p.beta; g_head.rh = p.head;
@@ -1056,6 +1061,10 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int in_dtype, long long row
   return SB_OK;
 }
 
+// Shared memory per SM that the GEMM's pipeline leaves unused so that CTAs of another kernel can be
+// resident beside a GEMM CTA (sb_gemm_reserve_smem).
+std::atomic<int> g_gemm_smem_reserve{0};
+
 // SB_NO_PAIR=1 in the environment keeps every GEMM on single-CTA tiles.
 bool sb_pair_mode_enabled() {
   static int v = -1;
@@ -1124,7 +1133,7 @@ void plan_umma(UmmaGemmParams& p, int in_dtype, int sms, bool allow_pair, bool c
   // tensor pipe from running back to back); they are used when at least three
   // such stages still fit and K is long enough to fill them.
   const int sub_bytes = (UG_BLOCK_M + b_cols) * 128;
-  const int budget = UG_SMEM_LIMIT - 2048 - UG_EPI_STAGING;
+  const int budget = UG_SMEM_LIMIT - 2048 - UG_EPI_STAGING - g_gemm_smem_reserve.load(std::memory_order_relaxed);
   const int sub_k = 128 / es;
   p.subs = (budget / (2 * sub_bytes) >= 3 && p.K >= 6 * sub_k) ? 2 : 1;
   p.block_k = p.subs * sub_k;
@@ -1191,7 +1200,8 @@ __global__ void scale_rows_kernel(void* C, long long total, float beta, int out_
 int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
-                        void* aux_out, cudaStream_t stream, int splits, int* splits_used, const SbRowHead* head) {
+                        void* aux_out, cudaStream_t stream, int splits, int* splits_used, const SbRowHead* head,
+                        void* split_partials) {
   const int es = sb_dtype_size(in_dtype);
   UmmaGemmParams p;
   memset(&p, 0, sizeof(p));
@@ -1245,8 +1255,19 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     p.splits = (p.k_blocks + kbps - 1) / kbps;   // every split owns at least one k-block
     p.num_work = p.num_tiles * p.splits;
     p.split_stride = (long long)M * N;
+    if (split_partials && p.splits > 1) {
+      // Accumulating form: fp32 output, every chunk of a tile leaves as a TMA box (whole 32-column
+      // chunks, 16-byte aligned rows), nothing else in the epilogue.
+      if (out_dtype == SB_F32 && epi == 0 && beta == 0.0f && alpha == 1.0f && p.block_n % 32 == 0 &&
+          ((long long)N * 4) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+        p.reduce_add = 1;
+        p.split_stride = 0;
+      } else {
+        p.C = C = split_partials;
+      }
+    }
   }
-  if (splits_used) *splits_used = p.splits;
+  if (splits_used) *splits_used = p.reduce_add ? 1 : p.splits;
 
   // Row-contiguous (coalesced) stores need a 16-byte aligned base and row pitch;
   // anything else falls back to per-thread stores.  Row heads write directly.
@@ -1268,14 +1289,16 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_store = 0;
-  if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || M % 32 == 0)) {
+  if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || p.reduce_add || M % 32 == 0)) {
     const int cdt = es_out == 4 ? SB_F32 : out_dtype;
     p.wide = (es_out == 2 && p.block_n % 64 == 0 && !(epi & SB_EPI_LN_L2)) ? 1 : 0;
-    rc = make_tmap_2d(&tc, C, cdt, (long long)M * p.splits, N, 32, p.wide ? 64 : 32,
+    rc = make_tmap_2d(&tc, C, cdt, p.reduce_add ? (long long)M : (long long)M * p.splits, N, 32, p.wide ? 64 : 32,
                       (es_out == 4 || p.wide) ? SWZ_128 : SWZ_64);
     if (rc != SB_OK) return rc;
     p.tma_store = 1;
   }
+  if (p.reduce_add && !p.tma_store)
+    return sb_fail(SB_ERR_UNSUPPORTED, "internal: split-K accumulation was chosen for a C that cannot take TMA stores");
   const size_t smem = umma_dyn_smem(p);
   static std::atomic<bool> attr_set[64];
   int dev = 0;
@@ -1301,6 +1324,12 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   sb_prof_after(stream, 2.0 * M * N * K);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+extern "C" int sb_gemm_reserve_smem(int bytes) {
+  if (bytes < 0 || bytes > 64 * 1024) return sb_fail(SB_ERR_BAD_ARG, "sb_gemm_reserve_smem: between 0 and 65536 bytes");
+  g_gemm_smem_reserve.store((bytes + 1023) / 1024 * 1024, std::memory_order_relaxed);
   return SB_OK;
 }
 

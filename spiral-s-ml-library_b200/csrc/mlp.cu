@@ -219,10 +219,17 @@ int blocks_for(long long n, int per_block, int cap = 0) {
 // and reduction -- for a 1024 x 1024 layer at a batch of 262144, 9 splits (144 items, two full
 // waves) instead of 4 (64 items on 74 pairs, 14 % of the GPU idle); at 32768 rows still 4.  Narrow outputs run on single CTAs, one item each.
 int wgrad_splits(int out, int in, int batch, int in_dtype) {
+  static int forced = -1;                  // SB_WGRAD_SPLITS=n in the environment fixes the factor (tuning runs)
+  if (forced < 0) {
+    const char* e = getenv("SB_WGRAD_SPLITS");
+    forced = e ? atoi(e) : 0;
+    if (forced < 0 || forced > 128) forced = 0;
+  }
   const int es = sb_dtype_size(in_dtype);
   const int block_k = 128 / es;
   const int k_blocks = (batch + block_k - 1) / block_k;
   const int max_by_k = k_blocks / 8 > 0 ? k_blocks / 8 : 1;  // keep >= 8 k-blocks per split
+  if (forced > 0) return forced < max_by_k ? forced : max_by_k;
   if (out > 128) {
     const int tiles = ((out + 255) / 256) * ((in + 255) / 256);
     const int workers = sb_sm_count() / 2;
@@ -247,6 +254,15 @@ int wgrad_splits(int out, int in, int batch, int in_dtype) {
   if (s > max_by_k) s = max_by_k;
   if (s > 128) s = 128;
   return s;
+}
+
+bool wgrad_partials_forced() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SB_WGRAD_PARTIALS");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
 }
 
 size_t backward_scratch_bytes(int n_layers, const int* sizes, int batch, int in_dtype) {
@@ -446,8 +462,7 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
   void* dy_next = odd ? sc : sc + dy_bytes;
   float* partial = reinterpret_cast<float*>(sc + 2 * dy_bytes);
 
-  // Bias gradients are accumulated with atomics into zeroed memory; weight
-  // gradients are overwritten.  Zero the whole buffer (padding included) so that
+  // Bias gradients and split-K weight gradients are accumulated into zeroed memory.  Zero the whole buffer (padding included) so that
   // the all-reduce and the SGD update can treat it as one flat vector.
   if (from_top) SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
 
@@ -504,10 +519,16 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
     float* dw = grads + off[2 * i];
     const int want = wgrad_splits(fan_out, fan_in, batch, in_dtype);
     int used = 1;
-    rc = sb_umma_gemm_launch(1, 0, 1.0f, dy_cur, h_in, 0.0f, want > 1 ? (void*)partial : (void*)dw, fan_out,
-                             fan_in, batch, in_dtype, SB_F32, 0, nullptr, nullptr, nullptr, nullptr, s, want, &used);
+    // The splits add their tiles straight into dW (zeroed above) through TMA reduce-add stores: no
+    // partial matrices, no reduction kernel.  The order of those fp32 additions is not fixed, so the
+    // last bits of dW can differ between runs; SB_WGRAD_PARTIALS=1 in the environment selects the
+    // older form, partials reduced in a fixed order by a kernel of their own.
+    const bool may_accumulate = want > 1 && !wgrad_partials_forced();
+    rc = sb_umma_gemm_launch(1, 0, 1.0f, dy_cur, h_in, 0.0f, (want > 1 && !may_accumulate) ? (void*)partial : (void*)dw,
+                             fan_out, fan_in, batch, in_dtype, SB_F32, 0, nullptr, nullptr, nullptr, nullptr, s, want,
+                             &used, nullptr, may_accumulate ? (void*)partial : nullptr);
     if (rc != SB_OK) return rc;
-    if (want > 1) {
+    if (used > 1) {
       const long long n = (long long)fan_out * fan_in;
       SB_CUDA(sb_launch(splitk_reduce_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, s, 1, partial, dw, n, used));
       SB_COUNT_LAUNCH();

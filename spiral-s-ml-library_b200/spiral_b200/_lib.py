@@ -96,6 +96,7 @@ SIGNATURES = {
     "sb_matmul_tf32": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _P]),
     "sb_matmul_ex": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "sb_matmul_head": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P, POINTER(HeadSpec), _P]),
+    "sb_gemm_reserve_smem": (_I, [_I]),
     "sb_matmul_plan": (_I, [_I, _I, _I, _I, _I, _I, _I, _IP]),
     "sb_relu": (_I, [_P, _P, _Z, _P]),
     "sb_row_softmax": (_I, [_P, _P, _I, _I, _P, _I, _P]),

@@ -13,7 +13,7 @@ and stores the new weights into every rank's buffers (csrc/dp.cu).
 import ctypes
 
 from . import _lib
-from .device import DeviceArray, stream_ptr
+from .device import DeviceArray, Event, Stream, stream_ptr
 
 
 def shard_rows(total_rows, world_size, rank):
@@ -59,15 +59,20 @@ class PeerUpdate:
         if net.grads is None or not isinstance(net.grads, DeviceArray):
             raise ValueError("a peer update needs a network built for training with its own gradient buffer")
         self.net, self.world_size, self.rank = net, int(world_size), int(rank)
-        self.timeout_ms, self.epoch = int(timeout_ms), 1
+        self.timeout_ms = int(timeout_ms)
         self.shard_master = bool(shard_master)
         bias_ranges = []
         for layer in range(net.n_layers):
             bias_ranges += [net.offsets[2 * layer + 1], net.offsets[2 * layer + 2]]
         self._ranges = (ctypes.c_longlong * len(bias_ranges))(*bias_ranges)
         self._n_ranges = len(bias_ranges) // 2
-        words = _lib.load().sb_dp_flag_bytes() // 4
-        self.flags = DeviceArray.zeros((words,), "i32")
+        # One flag block for the whole-vector update and one per layer: updates of different layers may
+        # be in flight at the same time (train_step(overlap=True)), and each needs a block of its own.
+        self._flag_words = _lib.load().sb_dp_flag_bytes() // 4
+        self._n_blocks = net.n_layers + 1
+        self.flags = DeviceArray.zeros((self._flag_words * self._n_blocks,), "i32")
+        self._epochs = [1] * self._n_blocks
+        self._per_layer = None                 # form of the last update: whole vector (False) or per layer (True)
         mine = [net.grads.ptr, net.params.ptr, net.w_compute.ptr, self.flags.ptr]
         handles = []
         for ptr in mine:
@@ -90,29 +95,69 @@ class PeerUpdate:
                     self._opened.append(out.value)
                     tables[k][r] = out.value
         self._tables = [(ctypes.c_void_p * self.world_size)(*t) for t in tables]
+        flag_bases = tables[3]
+        self._flag_tables = [(ctypes.c_void_p * self.world_size)(*[b + 4 * self._flag_words * k for b in flag_bases])
+                             for k in range(self._n_blocks)]
 
     def step(self, lr, stream=None):
         """All ranks call this after their backward pass; returns once the launch is enqueued."""
+        self._switch_form(False, stream)
         self._call(self.SHARDED_MASTER if self.shard_master else self.REPLICATED, lr, stream)
 
     def gather_master(self, stream=None):
-        """Every owner's slice of the master parameters is copied to all ranks (all ranks call this)."""
-        self._call(self.GATHER_MASTER, 0.0, stream)
+        """Every owner's slice of the master parameters is copied to all ranks (all ranks call this).
+        The slices are those of the form of update used last: of the whole vector, or of each layer."""
+        if self._per_layer:
+            for layer in range(self.net.n_layers):
+                begin, end = self.net.layer_segment(layer)
+                self._call(self.GATHER_MASTER, 0.0, stream, block=layer + 1, begin=begin, end=end)
+        else:
+            self._call(self.GATHER_MASTER, 0.0, stream)
 
-    def _call(self, mode, lr, stream):
+    def _switch_form(self, per_layer, stream):
+        """With a sharded master a rank owns the slices of the form in use (whole vector, or per layer):
+        before the other form is used the owners' values are gathered, so that every rank's new slices
+        start from current values."""
+        if self._per_layer is not None and self._per_layer != per_layer and self.shard_master:
+            self.gather_master(stream)
+        self._per_layer = per_layer
+
+    def step_layer(self, layer, lr, stream=None, max_blocks=0):
+        """The same for the parameters of one layer only (its weight and bias segments), with that layer's
+        own flag block: all ranks call it for the same layers in the same order.  Updates of different
+        layers may overlap each other and the backward pass of the layers below."""
+        self._switch_form(True, stream)
+        begin, end = self.net.layer_segment(layer)
+        self._call(self.SHARDED_MASTER if self.shard_master else self.REPLICATED, lr, stream, block=layer + 1,
+                   begin=begin, end=end, max_blocks=max_blocks)
+
+    def _call(self, mode, lr, stream, block=0, begin=0, end=None, max_blocks=0):
         net = self.net
-        g, p, w, f = self._tables
-        _lib.call("sb_dp_sgd_update", self.world_size, self.rank, g, p, w, f, ctypes.c_uint(self.epoch),
-                  ctypes.c_longlong(0), ctypes.c_longlong(net.n_params), ctypes.c_float(lr),
-                  _lib.DTYPE_CODES[net.storage], mode, self._ranges, self._n_ranges, 0, self.timeout_ms, 1,
-                  stream_ptr(stream))
-        self.epoch += 2
+        g, p, w, _ = self._tables
+        end = net.n_params if end is None else end
+        _lib.call("sb_dp_sgd_update", self.world_size, self.rank, g, p, w, self._flag_tables[block],
+                  ctypes.c_uint(self._epochs[block]), ctypes.c_longlong(int(begin)), ctypes.c_longlong(int(end)),
+                  ctypes.c_float(lr), _lib.DTYPE_CODES[net.storage], mode, self._ranges, self._n_ranges,
+                  int(max_blocks), self.timeout_ms, 1, stream_ptr(stream))
+        self._epochs[block] += 2
+
+    @property
+    def epoch(self):
+        return self._epochs[0]
+
+    @epoch.setter
+    def epoch(self, value):
+        self._epochs[0] = int(value)
 
     def status(self):
-        """0, or 0x100 + the rank whose arrival a bounded wait gave up on (synchronises the device)."""
+        """0, or 0x100 + the rank whose arrival a bounded wait gave up on, of the first flag block that
+        recorded one (synchronises the device)."""
         out = ctypes.c_int(0)
-        _lib.call("sb_dp_status", self.flags.ptr, ctypes.byref(out))
-        return out.value
+        for k in range(self._n_blocks):
+            _lib.call("sb_dp_status", self.flags.ptr + 4 * self._flag_words * k, ctypes.byref(out))
+            if out.value != 0:
+                return out.value
+        return 0
 
     def check(self):
         """Raises SpiralError (SB_ERR_DEVICE_TIMEOUT) when a flag wait of this rank's update kernel gave
@@ -134,7 +179,7 @@ class DataParallel:
     """Wraps a ``PolicyMLP`` built for this rank's shard."""
 
     def __init__(self, net, global_batch, all_reduce=None, world_size=1, rank=0, all_reduce_segment=None,
-                 peer_update=None):
+                 peer_update=None, overlap_update=False, reserve_smem=4096):
         """``all_reduce(buffer)`` sums the whole flat gradient buffer in place.  Optional
         ``all_reduce_segment(buffer, begin, end)`` starts an asynchronous sum of elements
         [begin, end) and returns a handle with ``wait()`` (or None when it completed in order)."""
@@ -142,6 +187,13 @@ class DataParallel:
         self.all_reduce, self.world_size, self.rank = all_reduce, int(world_size), int(rank)
         self.all_reduce_segment = all_reduce_segment
         self.peer_update = peer_update
+        # overlap_update: with a PeerUpdate, every layer's parameters are exchanged and updated on a second
+        # stream as soon as that layer's gradients are complete, beside the backward pass of the layers
+        # below.  The update CTAs must be resident next to the GEMM CTAs, which fill an SM's shared memory:
+        # during the backward pass the GEMM is told to leave `reserve_smem` bytes free.
+        self.overlap_update = bool(overlap_update) and peer_update is not None
+        self.reserve_smem = int(reserve_smem)
+        self._side = None
         if self.world_size > 1 and all_reduce is None and all_reduce_segment is None and peer_update is None:
             raise ValueError("more than one rank needs an all_reduce callable or a PeerUpdate")
 
@@ -154,6 +206,24 @@ class DataParallel:
         net = self.net
         net.loss.fill_zero(stream)
         net.forward(x, mask, stream=stream)
+        if self.world_size > 1 and self.peer_update is not None and self.overlap_update:
+            if self._side is None:
+                self._side = Stream()
+                self._ready = [Event() for _ in range(net.n_layers)]
+                self._done = Event()
+            side = self._side
+            _lib.call("sb_gemm_reserve_smem", self.reserve_smem)
+            try:
+                for layer in range(net.n_layers - 1, -1, -1):
+                    net.backward_layers(x, mask, target, layer, layer, global_batch=self.global_batch, stream=stream)
+                    self._ready[layer].record(stream)
+                    side.wait_event(self._ready[layer])
+                    self.peer_update.step_layer(layer, lr, stream=side.ptr)
+            finally:
+                _lib.call("sb_gemm_reserve_smem", 0)
+            self._done.record(side.ptr)
+            _lib.call("sb_stream_wait_event", stream_ptr(stream), self._done.ptr)
+            return
         if self.world_size > 1 and self.peer_update is not None:
             net.backward(x, mask, target, global_batch=self.global_batch, stream=stream)
             self.peer_update.step(lr, stream=stream)

@@ -190,8 +190,9 @@ def test_fused_forward_other_shapes_and_limits(gpu):
 
 
 def test_backward_split_by_layer_equals_whole_pass(gpu):
-    """sb_mlp_backward_range over layers 3, 2, 1, 0 in four calls gives the gradients of one call
-    (weight gradients bit-identical; bias gradients are atomic sums, equal to rounding)."""
+    """sb_mlp_backward_range over layers 3, 2, 1, 0 in four calls gives the gradients of one call (both
+    weight and bias gradients are sums whose order is not fixed -- split-K tiles are added by the memory
+    system, bias columns by atomics -- so they agree to fp32 rounding, not bit for bit)."""
     sizes, batch = [32, 256, 256, 256, 3], 2048
     net, ws, bs = build(gpu, sizes, batch, "bf16", 21, training=True, bias_scale=0.05)
     x, mask = so.leduc_inputs(21, batch)
@@ -206,7 +207,7 @@ def test_backward_split_by_layer_equals_whole_pass(gpu):
         net.backward_layers(dx, dm, dt, layer, layer)
     split = net.grads.numpy()
     for i, ((gw, gb), (ww, wb)) in enumerate(zip(net.split_flat(split), net.split_flat(whole))):
-        np.testing.assert_array_equal(gw, ww)
+        np.testing.assert_allclose(gw, ww, rtol=1e-4, atol=1e-6 * float(np.abs(ww).max()))
         np.testing.assert_allclose(gb, wb, rtol=1e-4, atol=1e-7)
     assert abs(float(net.loss.numpy()[0]) - loss_whole) <= 1e-5 * abs(loss_whole)
     assert net.layer_segment(0)[0] == 0 and net.layer_segment(3)[1] == net.n_params
