@@ -455,7 +455,36 @@ int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float*
                      void* const* w_compute, void* const* flags, unsigned int epoch, long long begin, long long end,
                      float lr, int compute_dtype, int mode, const long long* replicate, int n_replicate,
                      int max_blocks, int timeout_ms, int barriers, void* stream);
+/* The same over several element ranges in ONE launch (one pair of barriers): `segments` = HOST array of
+ * n_segments [begin, end) pairs; every range is cut into world_size slices of its own and rank r handles
+ * slice r of each.  reduced[k] != 0 (HOST array, may be NULL): the gradients of range k have already
+ * been summed into the owners' buffers by sb_mlp_backward_dp, so a rank reads only its own buffer there
+ * -- and zeroes what it read, which is what the next step's tiles are added to. */
+int sb_dp_sgd_update_segments(int world_size, int rank, const float* const* grads, float* const* params,
+                              void* const* w_compute, void* const* flags, unsigned int epoch, int n_segments,
+                              const long long* segments, const int* reduced, float lr, int compute_dtype, int mode,
+                              const long long* replicate, int n_replicate, int max_blocks, int timeout_ms, int barriers,
+                              void* stream);
 int sb_dp_status(const void* flags, int* status);
+
+/* Data-parallel backward pass that does the reduce-scatter half of the gradient all-reduce itself:
+ * grads_peers = HOST array of world_size DEVICE pointers, entry r = rank r's flat gradient vector
+ * (own buffer at [rank], peers' buffers opened with sb_ipc_open).  For every layer that
+ * sb_mlp_dp_fused_layers marks (weight matrix of at least 128 * world_size padded rows, at most 8
+ * ranks) the weight-gradient GEMM adds each output tile straight into the copy of the rank that owns
+ * its rows (rows [r * out / world, (r + 1) * out / world) belong to rank r: the slice r of that layer's
+ * weight range in sb_dp_sgd_update_segments) through TMA reduce-add stores over peer memory, tile by
+ * tile while the GEMM runs; after all ranks' passes the owner holds the summed gradient and
+ * sb_dp_sgd_update_segments(reduced = 1 for those ranges) needs no remote reads.  Other gradients
+ * (narrow layers, biases) are written to this rank's own vector as in sb_mlp_backward.  The marked
+ * weight ranges of every rank's vector must be zero before the first pass (a fresh sb_memset) and are
+ * left zero by the update.  No counterpart in the reference (single device). */
+int sb_mlp_dp_fused_layers(int n_layers, const int* sizes, int world_size, int* fused);
+int sb_mlp_backward_dp(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                       const void* x, const void* w_compute, void* const* activations,
+                       void* const* relu_bits, const float* probs, const uint8_t* mask, const float* target,
+                       float* const* grads_peers, int world_size, int rank, int with_bias, void* scratch,
+                       size_t scratch_bytes, float* loss, void* stream);
 
 #ifdef __cplusplus
 }

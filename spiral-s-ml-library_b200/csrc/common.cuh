@@ -70,12 +70,26 @@ void sb_prof_after(cudaStream_t s, double flops);
 // can take TMA boxes every split ADDS its tile to the one fp32 matrix C (which the caller has zeroed)
 // through TMA reduce-add stores and *splits_used comes back as 1; otherwise the partials go to
 // `split_partials`, *splits_used tells how many, and the caller reduces them into C.
+// `peer_out` (see SbPeerOut; the caller has checked sb_umma_peer_out_ok): every tile, split or not, is
+// added to the copy of C on the rank that owns its rows -- the reduce-scatter half of a gradient
+// all-reduce done by the GEMM's own TMA reduce-add stores over peer memory.  C is ignored then.
 struct SbRowHead;
+// Copies of the output matrix on several ranks (data-parallel weight gradients): c[r] is rank r's
+// copy of C, the same [M, N] fp32 matrix in that rank's memory (its own for this rank, peer pointers
+// for the others).  Rows [r * M / n, (r + 1) * M / n) of the product are ADDED to c[r] only.
+struct SbPeerOut {
+  int n;
+  void* c[8];
+};
+// True when a GEMM with an [M, N] fp32 output can add its rows to n ranks' copies (sb_umma_gemm_launch
+// with peer_out): whole 128-row blocks per rank, at most 8 ranks, rows that can leave as TMA boxes.
+bool sb_umma_peer_out_ok(int M, int N, int n);
 int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, const void* B,
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
                         void* aux_out, cudaStream_t stream, int splits = 1, int* splits_used = nullptr,
-                        const SbRowHead* head = nullptr, void* split_partials = nullptr);
+                        const SbRowHead* head = nullptr, void* split_partials = nullptr,
+                        const SbPeerOut* peer_out = nullptr);
 // True when a row head over N columns (legal columns j < prefix when prefix >= 0) runs inside the GEMM.
 bool sb_umma_head_fits(int N, int prefix);
 

@@ -34,6 +34,7 @@ namespace {
 
 constexpr int DP_MAX_WORLD = 16;
 constexpr int DP_MAX_RANGES = 16;
+constexpr int DP_MAX_SEGMENTS = 34;    // element ranges one launch may cover (weights and bias of up to 17 layers)
 constexpr int DP_THREADS = 128;
 constexpr int DP_STATUS_WORD = 16;     // index of the status word in a flag block
 constexpr int DP_COUNTER_WORD = 17;    // CTAs of the running update that have finished their stores
@@ -52,6 +53,26 @@ struct DpPeers {
   int shard_master;   // 0: every rank receives the whole master vector
   int gather_only;    // 1: no gradients, no step: the owners' master slices are copied to every rank
 };
+
+// The element ranges one launch covers.  Every range is cut into world_size slices of whole
+// 4-element vectors of its own; rank r reduces, updates and redistributes slice r of every range.
+// reduced[s] != 0: the gradients of range s were already summed into the owners' buffers by the
+// backward pass (its weight-gradient GEMMs add their tiles to the owner's copy over peer memory), so
+// the owner reads only its own buffer -- and zeroes what it has read, ready for the next step's tiles.
+struct DpSegments {
+  int n;
+  long long begin[DP_MAX_SEGMENTS];
+  long long end[DP_MAX_SEGMENTS];
+  unsigned char reduced[DP_MAX_SEGMENTS];
+};
+
+__device__ __forceinline__ void dp_slice_of(long long begin, long long end, int world, int rank, long long& v_begin,
+                                            long long& v_end) {
+  const long long nvec = (end - begin) >> 2;
+  const long long per = (nvec + world - 1) / world;
+  v_begin = (begin >> 2) + min(nvec, per * rank);
+  v_end = (begin >> 2) + min(nvec, per * rank + per);
+}
 
 __device__ __forceinline__ float4 ld_volatile_f4(const float* p) {
   float4 v;
@@ -139,7 +160,7 @@ __device__ __forceinline__ void store_compute4(void* base, long long i, float4 w
 // 4-element vectors.  barriers = 0 skips both barriers (single rank, or a
 // caller that ordered the ranks by other means).
 __global__ void __launch_bounds__(DP_THREADS)
-dp_update_kernel(DpPeers peers, int world, int rank, unsigned int epoch, long long begin, long long end, float lr,
+dp_update_kernel(DpPeers peers, DpSegments segs, int world, int rank, unsigned int epoch, float lr,
                  int dt, unsigned long long timeout_ns, int barriers) {
   unsigned int* my_flags = peers.flags[rank];
   __shared__ int is_last;
@@ -149,16 +170,41 @@ dp_update_kernel(DpPeers peers, int world, int rank, unsigned int epoch, long lo
   } else if (ld_volatile_u32(my_flags + DP_STATUS_WORD) != 0u) {
     return;
   }
-  const long long nvec = (end - begin) >> 2;
-  const long long per = (nvec + world - 1) / world;
-  const long long v_begin = (begin >> 2) + min(nvec, per * rank);
-  const long long v_end = (begin >> 2) + min(nvec, per * rank + per);
+  long long total = 0;                     // vectors of this rank over all ranges
+  for (int s = 0; s < segs.n; ++s) {
+    long long b, e;
+    dp_slice_of(segs.begin[s], segs.end[s], world, rank, b, e);
+    total += e - b;
+  }
   const long long step = (long long)gridDim.x * blockDim.x;
-  for (long long v = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v_end; v += step) {
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step) {
+    // which range, and which vector of this rank's slice of it
+    long long local = t, v = 0;
+    bool reduced = false;
+    for (int s = 0; s < segs.n; ++s) {
+      long long b, e;
+      dp_slice_of(segs.begin[s], segs.end[s], world, rank, b, e);
+      if (local < e - b) {
+        v = b + local;
+        reduced = segs.reduced[s] != 0;
+        break;
+      }
+      local -= e - b;
+    }
     const long long i = v << 2;
     float4 w = *reinterpret_cast<const float4*>(peers.params[rank] + i);
     bool master_everywhere = peers.shard_master == 0;
-    if (!peers.gather_only) {
+    if (!peers.gather_only && reduced) {
+      // The sum over ranks is already in this rank's buffer (added there tile by tile by every rank's
+      // weight-gradient GEMM); read it, and leave zeros for the next step's tiles.
+      float* mine = const_cast<float*>(peers.grads[rank]) + i;
+      const float4 s4 = ld_volatile_f4(mine);
+      *reinterpret_cast<float4*>(mine) = make_float4(0.f, 0.f, 0.f, 0.f);
+      w.x -= lr * s4.x; w.y -= lr * s4.y; w.z -= lr * s4.z; w.w -= lr * s4.w;
+      if (!master_everywhere)
+        for (int k = 0; k < peers.n_ranges; ++k)
+          if (i >= peers.rep_begin[k] && i < peers.rep_end[k]) master_everywhere = true;
+    } else if (!peers.gather_only) {
       // Eight loads in flight before the first add (two rounds for more than eight ranks): a CTA of
       // this kernel must fit beside a resident GEMM CTA, which leaves it some 90 registers a thread.
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -253,14 +299,15 @@ int sb_dp_slice(long long begin, long long end, int world_size, int rank, long l
   return SB_OK;
 }
 
-int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float* const* params,
-                     void* const* w_compute, void* const* flags, unsigned int epoch, long long begin, long long end,
-                     float lr, int compute_dtype, int mode, const long long* replicate, int n_replicate,
-                     int max_blocks, int timeout_ms, int barriers, void* stream) {
+int sb_dp_sgd_update_segments(int world_size, int rank, const float* const* grads, float* const* params,
+                              void* const* w_compute, void* const* flags, unsigned int epoch, int n_segments,
+                              const long long* segments, const int* reduced, float lr, int compute_dtype, int mode,
+                              const long long* replicate, int n_replicate, int max_blocks, int timeout_ms, int barriers,
+                              void* stream) {
   if (world_size < 1 || world_size > DP_MAX_WORLD || rank < 0 || rank >= world_size)
     return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: rank %d of world size %d (at most %d ranks)", rank, world_size, DP_MAX_WORLD);
-  if (begin < 0 || end < begin || begin % 4 != 0 || end % 4 != 0)
-    return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: [begin, end) must be whole 4-element vectors");
+  if (n_segments < 1 || n_segments > DP_MAX_SEGMENTS || !segments)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: between 1 and %d element ranges", DP_MAX_SEGMENTS);
   if (max_blocks < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: negative max_blocks");
   if (mode != SB_DP_REPLICATED && mode != SB_DP_SHARDED_MASTER && mode != SB_DP_GATHER_MASTER)
     return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: unknown mode %d", mode);
@@ -270,6 +317,19 @@ int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float*
   if (timeout_ms < 1 || timeout_ms > 60000) return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: timeout_ms must be in [1, 60000]");
   if (compute_dtype != SB_F32 && compute_dtype != SB_TF32 && compute_dtype != SB_BF16 && compute_dtype != SB_F16)
     return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: unknown compute dtype %d", compute_dtype);
+  DpSegments segs;
+  memset(&segs, 0, sizeof(segs));
+  segs.n = n_segments;
+  long long slice_vecs = 0;
+  for (int k = 0; k < n_segments; ++k) {
+    const long long begin = segments[2 * k], end = segments[2 * k + 1];
+    if (begin < 0 || end < begin || begin % 4 != 0 || end % 4 != 0)
+      return sb_fail(SB_ERR_BAD_ARG, "sb_dp_sgd_update: range %d must be [begin, end) in whole 4-element vectors", k);
+    segs.begin[k] = begin;
+    segs.end[k] = end;
+    segs.reduced[k] = (reduced && reduced[k]) ? 1 : 0;
+    slice_vecs += (((end - begin) >> 2) + world_size - 1) / world_size;
+  }
   DpPeers peers;
   memset(&peers, 0, sizeof(peers));
   for (int r = 0; r < world_size; ++r) {
@@ -295,18 +355,26 @@ int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float*
   }
   cudaStream_t s = (cudaStream_t)stream;
   const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
-  const long long slice_vecs = (((end - begin) >> 2) + world_size - 1) / world_size;
   long long blocks = (slice_vecs + DP_THREADS - 1) / DP_THREADS;
   if (blocks < 1) blocks = 1;
   const long long cap = max_blocks > 0 ? max_blocks : (long long)sb_sm_count() * 8;
   if (blocks > cap) blocks = cap;
   // A plain launch (no programmatic dependent launch): the first thing this kernel does is to tell
   // its peers that the gradients of this rank -- the work of the kernels before it -- are complete.
-  dp_update_kernel<<<(int)blocks, DP_THREADS, 0, s>>>(peers, world_size, rank, epoch, begin, end, lr, compute_dtype,
-                                                      timeout_ns, barriers ? 1 : 0);
+  dp_update_kernel<<<(int)blocks, DP_THREADS, 0, s>>>(peers, segs, world_size, rank, epoch, lr, compute_dtype, timeout_ns,
+                                                      barriers ? 1 : 0);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
+}
+
+int sb_dp_sgd_update(int world_size, int rank, const float* const* grads, float* const* params,
+                     void* const* w_compute, void* const* flags, unsigned int epoch, long long begin, long long end,
+                     float lr, int compute_dtype, int mode, const long long* replicate, int n_replicate,
+                     int max_blocks, int timeout_ms, int barriers, void* stream) {
+  const long long seg[2] = {begin, end};
+  return sb_dp_sgd_update_segments(world_size, rank, grads, params, w_compute, flags, epoch, 1, seg, nullptr, lr,
+                                   compute_dtype, mode, replicate, n_replicate, max_blocks, timeout_ms, barriers, stream);
 }
 
 int sb_dp_status(const void* flags, int* status) {

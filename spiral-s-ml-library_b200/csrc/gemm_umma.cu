@@ -43,9 +43,16 @@ constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;   // a warp takes every UG_EPI_S
 constexpr int UG_THREADS = 64 + 32 * UG_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
+constexpr int UG_MAX_PEERS = 8;         // ranks whose copies of C one launch can add its tiles to
 constexpr int UG_HEAD_MAX_N = 64;       // widest row a fused head keeps in registers
 constexpr int UG_HEAD_MAX_TILE_N = 256; // widest row a fused head may belong to when a prefix mask confines it to UG_HEAD_MAX_N columns
 constexpr int UG_EPI_STAGING = UG_EPI_WARPS * 4096;  // one 32-row x 128-byte box per epilogue warp
+
+// Tensor maps of the output: m[0] is C itself; with peer_rows > 0, m[r] is rank r's copy of C (the
+// same matrix in that rank's memory) and a CTA adds its rows to the copy of the rank that owns them.
+struct UmmaOutMaps {
+  CUtensorMap m[UG_MAX_PEERS];
+};
 
 struct UmmaGemmParams {
   int M, N, K;
@@ -88,7 +95,8 @@ struct UmmaGemmParams {
   int wide;            // 1: 16-bit output boxes span two chunks (64 columns, 128-byte rows)
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
   SbRowHead head;      // the row head, when epi holds a head flag
-  int reduce_add;      // 1: split-K tiles are added to one C through TMA reduce-add stores
+  int reduce_add;      // 1: tiles are added to C through TMA reduce-add stores (split-K into one matrix, peer copies)
+  int peer_rows;       // > 0: rows [r * peer_rows, (r + 1) * peer_rows) of C are added to rank r's copy (out map r)
 };
 
 __device__ __forceinline__ void tile_coords(const UmmaGemmParams& p, int tile, int& m_blk, int& n_blk) {
@@ -244,6 +252,7 @@ struct EpiShared {
   float alpha, beta;
   int has_bias, relu, relu_grad, coalesced;
   int reduce_add;           // finished boxes are ADDED to C (split-K accumulating into one matrix)
+  int peer_rows;            // > 0: the boxes of rows [r * peer_rows, ...) go to out map r (rank r's copy of C)
   int split_rows;           // rows between two splits' outputs in the store map (0 when they share C)
   int ln_l2;                // divide every row by its sum of squares before the ReLU (SB_EPI_LN_L2; the tile spans the row)
   uint32_t box_base;        // shared-memory address of the first epilogue warp's 4 KB box
@@ -377,7 +386,8 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        if (g_epi.reduce_add) tma_reduce_add_2d(g_epi.tma_c, sbuf, col0, row0_warp);
+        if (g_epi.reduce_add)
+          tma_reduce_add_2d(g_epi.tma_c + (g_epi.peer_rows > 0 ? row0_warp / g_epi.peer_rows : 0), sbuf, col0, row0_warp);
         else tma_store_2d(g_epi.tma_c, sbuf, wide ? col0 - 32 : col0, split * g_epi.split_rows + row0_warp);
         bulk_commit_group();
       }
@@ -708,7 +718,7 @@ template <bool PAIR, bool TF32>
 __global__ void __launch_bounds__(UG_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c,
+                 const __grid_constant__ UmmaOutMaps out_maps,
                  const __grid_constant__ UmmaGemmParams p) {
   extern __shared__ uint8_t ug_smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[UG_MAX_STAGES];
@@ -746,7 +756,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     g_epi.gate_in = (p.epi & SB_EPI_RELU_GRAD_MASK) ? reinterpret_cast<const uint32_t*>(p.aux_in) : nullptr;
     g_epi.gate_out = (p.epi & SB_EPI_RELU_MASK_OUT) ? reinterpret_cast<uint32_t*>(p.aux_out) : nullptr;
     g_epi.colsum = (p.epi & SB_EPI_COLSUM_OUT) ? reinterpret_cast<float*>(p.aux_out) : nullptr;
-    g_epi.tma_c = p.tma_store ? &tmap_c : nullptr;
+    g_epi.tma_c = p.tma_store ? &out_maps.m[0] : nullptr;
+    g_epi.peer_rows = p.peer_rows;
     g_epi.ldc = p.ldc;
     g_epi.split_stride = p.split_stride;
     g_epi.M = p.M; g_epi.N = p.N; g_epi.block_n = p.block_n;
@@ -1201,7 +1212,16 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
                         float beta, void* C, int M, int N, int K, int in_dtype, int out_dtype,
                         int epi, const float* bias, const uint8_t* mask, const void* aux_in,
                         void* aux_out, cudaStream_t stream, int splits, int* splits_used, const SbRowHead* head,
-                        void* split_partials) {
+                        void* split_partials, const SbPeerOut* peer_out) {
+  const bool to_peers = peer_out && peer_out->n > 1;
+  if (to_peers) {
+    if (!sb_umma_peer_out_ok(M, N, peer_out->n) || out_dtype != SB_F32 || epi != 0 || beta != 0.0f || alpha != 1.0f)
+      return sb_fail(SB_ERR_UNSUPPORTED, "GEMM into peer copies: plain fp32 product with whole 128-row blocks per rank only");
+    for (int r = 0; r < peer_out->n; ++r)
+      if (!peer_out->c[r] || (reinterpret_cast<uintptr_t>(peer_out->c[r]) & 15))
+        return sb_fail(SB_ERR_MISALIGNED, "GEMM into peer copies: copy %d is null or not 16-byte aligned", r);
+    C = peer_out->c[0];
+  }
   const int es = sb_dtype_size(in_dtype);
   UmmaGemmParams p;
   memset(&p, 0, sizeof(p));
@@ -1255,7 +1275,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     p.splits = (p.k_blocks + kbps - 1) / kbps;   // every split owns at least one k-block
     p.num_work = p.num_tiles * p.splits;
     p.split_stride = (long long)M * N;
-    if (split_partials && p.splits > 1) {
+    if (split_partials && p.splits > 1 && !to_peers) {
       // Accumulating form: fp32 output, every chunk of a tile leaves as a TMA box (whole 32-column
       // chunks, 16-byte aligned rows), nothing else in the epilogue.
       if (out_dtype == SB_F32 && epi == 0 && beta == 0.0f && alpha == 1.0f && p.block_n % 32 == 0 &&
@@ -1266,6 +1286,12 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
         p.C = C = split_partials;
       }
     }
+  }
+  if (to_peers) {
+    if (p.block_n % 32 != 0) return sb_fail(SB_ERR_UNSUPPORTED, "GEMM into peer copies: the tile plan leaves a 16-column tail");
+    p.reduce_add = 1;
+    p.split_stride = 0;
+    p.peer_rows = M / peer_out->n;
   }
   if (splits_used) *splits_used = p.reduce_add ? 1 : p.splits;
 
@@ -1286,15 +1312,17 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
 
   // TMA stores of the finished boxes: no second tile is read (beta, activation gate), and with
   // split-K -- the partials form one [splits * M, N] tensor -- no 32-row box may straddle two partials.
-  CUtensorMap tc;
+  UmmaOutMaps tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_store = 0;
   if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || p.reduce_add || M % 32 == 0)) {
     const int cdt = es_out == 4 ? SB_F32 : out_dtype;
     p.wide = (es_out == 2 && p.block_n % 64 == 0 && !(epi & SB_EPI_LN_L2)) ? 1 : 0;
-    rc = make_tmap_2d(&tc, C, cdt, p.reduce_add ? (long long)M : (long long)M * p.splits, N, 32, p.wide ? 64 : 32,
-                      (es_out == 4 || p.wide) ? SWZ_128 : SWZ_64);
-    if (rc != SB_OK) return rc;
+    for (int r = 0; r < (to_peers ? peer_out->n : 1); ++r) {
+      rc = make_tmap_2d(&tc.m[r], to_peers ? peer_out->c[r] : C, cdt, p.reduce_add ? (long long)M : (long long)M * p.splits, N,
+                        32, p.wide ? 64 : 32, (es_out == 4 || p.wide) ? SWZ_128 : SWZ_64);
+      if (rc != SB_OK) return rc;
+    }
     p.tma_store = 1;
   }
   if (p.reduce_add && !p.tma_store)
@@ -1357,6 +1385,10 @@ int sb_scale_launch(void* C, long long total, float beta, int out_dtype, cudaStr
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
   return SB_OK;
+}
+
+bool sb_umma_peer_out_ok(int M, int N, int n) {
+  return n >= 2 && n <= UG_MAX_PEERS && M % n == 0 && (M / n) % UG_BLOCK_M == 0 && ((long long)N * 4) % 16 == 0;
 }
 
 bool sb_umma_head_fits(int N, int prefix) {

@@ -421,11 +421,57 @@ int sb_mlp_backward_dy_offset(int n_layers, const int* sizes, int batch, int in_
   return SB_OK;
 }
 
+// Which layers' weight gradients a data-parallel backward pass adds straight into the owners' copies.
+static bool layer_grads_go_to_peers(int fan_out_padded, int fan_in, int world) {
+  return world > 1 && sb_umma_peer_out_ok(fan_out_padded, fan_in, world);
+}
+
+int sb_mlp_dp_fused_layers(int n_layers, const int* sizes, int world_size, int* fused) {
+  if (!fused) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_dp_fused_layers: null output");
+  int rc = check_layout("sb_mlp_dp_fused_layers", n_layers, sizes, 0, SB_BF16);
+  if (rc != SB_OK) return rc;
+  for (int i = 0; i < n_layers; ++i) fused[i] = layer_grads_go_to_peers(padded_out(sizes[i + 1]), sizes[i], world_size) ? 1 : 0;
+  return SB_OK;
+}
+
+static int backward_impl(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                         const void* x, const void* w_compute, void* const* activations,
+                         void* const* relu_bits, const float* probs, const uint8_t* mask,
+                         const float* target, float* grads, int with_bias, void* scratch,
+                         size_t scratch_bytes, float* loss, int first_layer, int last_layer, void* stream,
+                         float* const* grads_peers, int world);
+
 int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
                           const void* x, const void* w_compute, void* const* activations,
                           void* const* relu_bits, const float* probs, const uint8_t* mask,
                           const float* target, float* grads, int with_bias, void* scratch,
                           size_t scratch_bytes, float* loss, int first_layer, int last_layer, void* stream) {
+  return backward_impl(n_layers, sizes, batch, inv_global_batch, in_dtype, x, w_compute, activations, relu_bits, probs,
+                       mask, target, grads, with_bias, scratch, scratch_bytes, loss, first_layer, last_layer, stream,
+                       nullptr, 1);
+}
+
+int sb_mlp_backward_dp(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                       const void* x, const void* w_compute, void* const* activations,
+                       void* const* relu_bits, const float* probs, const uint8_t* mask, const float* target,
+                       float* const* grads_peers, int world_size, int rank, int with_bias, void* scratch,
+                       size_t scratch_bytes, float* loss, void* stream) {
+  if (world_size < 1 || world_size > 16 || rank < 0 || rank >= world_size || !grads_peers)
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward_dp: rank %d of world size %d, or no table of gradient buffers", rank, world_size);
+  for (int r = 0; r < world_size; ++r)
+    if (!grads_peers[r]) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward_dp: gradient buffer of rank %d is null", r);
+  // This rank's own buffer comes first in the peers table handed down: the launcher's C.
+  return backward_impl(n_layers, sizes, batch, inv_global_batch, in_dtype, x, w_compute, activations, relu_bits, probs,
+                       mask, target, grads_peers[rank], with_bias, scratch, scratch_bytes, loss, n_layers - 1, 0, stream,
+                       grads_peers, world_size);
+}
+
+static int backward_impl(int n_layers, const int* sizes, int batch, float inv_global_batch, int in_dtype,
+                         const void* x, const void* w_compute, void* const* activations,
+                         void* const* relu_bits, const float* probs, const uint8_t* mask,
+                         const float* target, float* grads, int with_bias, void* scratch,
+                         size_t scratch_bytes, float* loss, int first_layer, int last_layer, void* stream,
+                         float* const* grads_peers, int world) {
   int rc = check_layout("sb_mlp_backward", n_layers, sizes, batch, in_dtype);
   if (rc != SB_OK) return rc;
   if (!grads) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_backward: grads is null");
@@ -435,8 +481,23 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
   long long off[2 * MLP_MAX_LAYERS + 1];
   param_offsets(n_layers, sizes, off);
   cudaStream_t s = (cudaStream_t)stream;
+  // Zeroes the gradient vector before a pass.  Weight segments that peers add into (data-parallel
+  // pass) are left alone: their owner slices are zeroed by the update kernel that consumed them, and a
+  // faster rank may already be adding this step's tiles.
+  auto zero_grads = [&]() -> int {
+    if (!grads_peers || world <= 1) {
+      SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+      return SB_OK;
+    }
+    for (int i = 0; i < n_layers; ++i) {
+      const bool fused = layer_grads_go_to_peers(padded_out(sizes[i + 1]), sizes[i], world);
+      const long long begin = fused ? off[2 * i + 1] : off[2 * i];
+      SB_CUDA(cudaMemsetAsync(grads + begin, 0, (size_t)(off[2 * i + 2] - begin) * 4, s));
+    }
+    return SB_OK;
+  };
   if (batch == 0) {
-    if (from_top) SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+    if (from_top) return zero_grads();
     return SB_OK;
   }
   if (!x || !w_compute || !probs || !target || !scratch)
@@ -464,7 +525,10 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
 
   // Bias gradients and split-K weight gradients are accumulated into zeroed memory.  Zero the whole buffer (padding included) so that
   // the all-reduce and the SGD update can treat it as one flat vector.
-  if (from_top) SB_CUDA(cudaMemsetAsync(grads, 0, (size_t)off[2 * n_layers] * 4, s));
+  if (from_top) {
+    rc = zero_grads();
+    if (rc != SB_OK) return rc;
+  }
 
   const int n_out = sizes[n_layers];
   const int ld_out = padded_out(n_out);
@@ -524,9 +588,19 @@ int sb_mlp_backward_range(int n_layers, const int* sizes, int batch, float inv_g
     // last bits of dW can differ between runs; SB_WGRAD_PARTIALS=1 in the environment selects the
     // older form, partials reduced in a fixed order by a kernel of their own.
     const bool may_accumulate = want > 1 && !wgrad_partials_forced();
-    rc = sb_umma_gemm_launch(1, 0, 1.0f, dy_cur, h_in, 0.0f, (want > 1 && !may_accumulate) ? (void*)partial : (void*)dw,
-                             fan_out, fan_in, batch, in_dtype, SB_F32, 0, nullptr, nullptr, nullptr, nullptr, s, want,
-                             &used, nullptr, may_accumulate ? (void*)partial : nullptr);
+    if (grads_peers && layer_grads_go_to_peers(fan_out, fan_in, world)) {
+      // Data-parallel pass: every tile is added to the copy of dW on the rank that owns its rows (the
+      // reduce-scatter of the gradient all-reduce, done by the GEMM's own stores over peer memory).
+      SbPeerOut po;
+      po.n = world;
+      for (int r = 0; r < world; ++r) po.c[r] = grads_peers[r] + off[2 * i];
+      rc = sb_umma_gemm_launch(1, 0, 1.0f, dy_cur, h_in, 0.0f, nullptr, fan_out, fan_in, batch, in_dtype, SB_F32, 0, nullptr,
+                               nullptr, nullptr, nullptr, s, want, &used, nullptr, nullptr, &po);
+    } else {
+      rc = sb_umma_gemm_launch(1, 0, 1.0f, dy_cur, h_in, 0.0f, (want > 1 && !may_accumulate) ? (void*)partial : (void*)dw,
+                               fan_out, fan_in, batch, in_dtype, SB_F32, 0, nullptr, nullptr, nullptr, nullptr, s, want,
+                               &used, nullptr, may_accumulate ? (void*)partial : nullptr);
+    }
     if (rc != SB_OK) return rc;
     if (used > 1) {
       const long long n = (long long)fan_out * fan_in;

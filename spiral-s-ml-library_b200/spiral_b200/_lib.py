@@ -115,7 +115,11 @@ SIGNATURES = {
     "sb_dp_slice": (_I, [ctypes.c_longlong, ctypes.c_longlong, _I, _I, POINTER(ctypes.c_longlong)]),
     "sb_dp_sgd_update": (_I, [_I, _I, _PP, _PP, _PP, _PP, ctypes.c_uint, ctypes.c_longlong, ctypes.c_longlong,
                               ctypes.c_float, _I, _I, POINTER(ctypes.c_longlong), _I, _I, _I, _I, _P]),
+    "sb_dp_sgd_update_segments": (_I, [_I, _I, _PP, _PP, _PP, _PP, ctypes.c_uint, _I, POINTER(ctypes.c_longlong), _IP,
+                                       ctypes.c_float, _I, _I, POINTER(ctypes.c_longlong), _I, _I, _I, _I, _P]),
     "sb_dp_status": (_I, [_P, _IP]),
+    "sb_mlp_dp_fused_layers": (_I, [_I, _IP, _I, _IP]),
+    "sb_mlp_backward_dp": (_I, [_I, _IP, _I, _F, _I, _P, _P, _PP, _PP, _P, _P, _P, _PP, _I, _I, _I, _P, _Z, _P, _P]),
     "sb_encode_states": (_I, [_P, _I, _IP, _P, _I, _P, ctypes.c_longlong, _I, _P]),
     "sb_mlp_param_offsets": (_I, [_I, _IP, POINTER(ctypes.c_longlong)]),
     "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),

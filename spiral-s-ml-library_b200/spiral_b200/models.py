@@ -175,6 +175,18 @@ class PolicyMLP:
                   self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
         return self.grads
 
+    def backward_dp(self, x, mask, target, grads_table, world_size, rank, global_batch=None, stream=None):
+        """The backward pass of a data-parallel step: like ``backward``, but the weight-gradient GEMMs of
+        the wide layers add their tiles straight into the gradient buffer of the rank that owns those rows
+        (``grads_table``: HOST array of every rank's buffer, ``PeerUpdate.grads_table()``), over peer
+        memory -- the reduce-scatter half of the gradient all-reduce done by the GEMM itself."""
+        gb = self.batch * int(world_size) if global_batch is None else int(global_batch)
+        _lib.call("sb_mlp_backward_dp", self.n_layers, self._sizes_c, self.batch, ctypes.c_float(1.0 / gb),
+                  _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr, self._acts_c, self._bits_c,
+                  self.probs.ptr, device_ptr(mask), device_ptr(target), grads_table, int(world_size), int(rank),
+                  int(self.with_bias), self.scratch.ptr, self.scratch.nbytes, self.loss.ptr, stream_ptr(stream))
+        return self.grads
+
     def backward_layers(self, x, mask, target, first_layer, last_layer, global_batch=None, stream=None):
         """The backward pass of layers first_layer .. last_layer (descending); successive calls covering
         n_layers-1 .. 0 equal one ``backward``."""

@@ -51,7 +51,7 @@ class PeerUpdate:
 
     REPLICATED, SHARDED_MASTER, GATHER_MASTER = 0, 1, 2
 
-    def __init__(self, net, world_size, rank, exchange, timeout_ms=2000, shard_master=True):
+    def __init__(self, net, world_size, rank, exchange, timeout_ms=2000, shard_master=True, fused_reduce=True):
         """``shard_master``: a rank's fp32 master parameters are kept current only in the slice it owns
         (plus all biases, which the forward pass reads in fp32): a third of the bytes leave the GPU per
         step.  Call ``gather_master()`` before reading the whole master vector on a rank
@@ -61,6 +61,22 @@ class PeerUpdate:
         self.net, self.world_size, self.rank = net, int(world_size), int(rank)
         self.timeout_ms = int(timeout_ms)
         self.shard_master = bool(shard_master)
+        # fused_reduce: the backward pass (net.backward_dp) adds every weight-gradient tile of the wide
+        # layers straight into the owning rank's gradient buffer over peer memory, so the update reads no
+        # remote gradients for those layers.  The parameter vector is handled as one range per layer's
+        # weights and one per layer's bias; rank r owns slice r of every range.
+        fused = (ctypes.c_int * net.n_layers)()
+        if fused_reduce and self.world_size > 1:
+            _lib.call("sb_mlp_dp_fused_layers", net.n_layers, net._sizes_c, self.world_size, fused)
+        self.fused_layers = [bool(v) for v in fused]
+        seg, red = [], []
+        for layer in range(net.n_layers):
+            end = net.offsets[2 * layer + 2] if layer + 1 < net.n_layers else net.n_params
+            seg += [net.offsets[2 * layer], net.offsets[2 * layer + 1], net.offsets[2 * layer + 1], end]
+            red += [int(self.fused_layers[layer]), 0]
+        self._segments = (ctypes.c_longlong * len(seg))(*seg)
+        self._reduced = (ctypes.c_int * len(red))(*red)
+        self._n_segments = len(red)
         bias_ranges = []
         for layer in range(net.n_layers):
             bias_ranges += [net.offsets[2 * layer + 1], net.offsets[2 * layer + 2]]
@@ -72,7 +88,6 @@ class PeerUpdate:
         self._n_blocks = net.n_layers + 1
         self.flags = DeviceArray.zeros((self._flag_words * self._n_blocks,), "i32")
         self._epochs = [1] * self._n_blocks
-        self._per_layer = None                 # form of the last update: whole vector (False) or per layer (True)
         mine = [net.grads.ptr, net.params.ptr, net.w_compute.ptr, self.flags.ptr]
         handles = []
         for ptr in mine:
@@ -99,44 +114,44 @@ class PeerUpdate:
         self._flag_tables = [(ctypes.c_void_p * self.world_size)(*[b + 4 * self._flag_words * k for b in flag_bases])
                              for k in range(self._n_blocks)]
 
-    def step(self, lr, stream=None):
-        """All ranks call this after their backward pass; returns once the launch is enqueued."""
-        self._switch_form(False, stream)
-        self._call(self.SHARDED_MASTER if self.shard_master else self.REPLICATED, lr, stream)
+    def step(self, lr, stream=None, reduced=False):
+        """All ranks call this after their backward pass; returns once the launch is enqueued.
+        ``reduced``: the pass was ``net.backward_dp`` (the wide layers' gradients are already summed in
+        their owners' buffers); False after a plain ``net.backward``, whose gradients are all local."""
+        self._call(self.SHARDED_MASTER if self.shard_master else self.REPLICATED, lr, stream, reduced=reduced)
 
     def gather_master(self, stream=None):
-        """Every owner's slice of the master parameters is copied to all ranks (all ranks call this).
-        The slices are those of the form of update used last: of the whole vector, or of each layer."""
-        if self._per_layer:
-            for layer in range(self.net.n_layers):
-                begin, end = self.net.layer_segment(layer)
-                self._call(self.GATHER_MASTER, 0.0, stream, block=layer + 1, begin=begin, end=end)
-        else:
-            self._call(self.GATHER_MASTER, 0.0, stream)
+        """Every owner's slices of the master parameters are copied to all ranks (all ranks call this)."""
+        self._call(self.GATHER_MASTER, 0.0, stream)
 
-    def _switch_form(self, per_layer, stream):
-        """With a sharded master a rank owns the slices of the form in use (whole vector, or per layer):
-        before the other form is used the owners' values are gathered, so that every rank's new slices
-        start from current values."""
-        if self._per_layer is not None and self._per_layer != per_layer and self.shard_master:
-            self.gather_master(stream)
-        self._per_layer = per_layer
+    def grads_table(self):
+        """HOST array of every rank's gradient buffer (device pointers), for ``net.backward_dp``."""
+        return self._tables[0]
+
+    def zero_gradients(self, stream=None):
+        """Zeroes this rank's whole gradient buffer.  The ranges that peers add into must be zero before the
+        first ``backward_dp`` pass and whenever a plain ``backward`` has written them in between; the
+        caller puts a barrier across the ranks after it."""
+        self.net.grads.fill_zero(stream)
 
     def step_layer(self, layer, lr, stream=None, max_blocks=0):
         """The same for the parameters of one layer only (its weight and bias segments), with that layer's
         own flag block: all ranks call it for the same layers in the same order.  Updates of different
         layers may overlap each other and the backward pass of the layers below."""
-        self._switch_form(True, stream)
-        begin, end = self.net.layer_segment(layer)
         self._call(self.SHARDED_MASTER if self.shard_master else self.REPLICATED, lr, stream, block=layer + 1,
-                   begin=begin, end=end, max_blocks=max_blocks)
+                   layer=layer, max_blocks=max_blocks, reduced=False)
 
-    def _call(self, mode, lr, stream, block=0, begin=0, end=None, max_blocks=0):
+    def _call(self, mode, lr, stream, block=0, layer=None, max_blocks=0, reduced=False):
         net = self.net
         g, p, w, _ = self._tables
-        end = net.n_params if end is None else end
-        _lib.call("sb_dp_sgd_update", self.world_size, self.rank, g, p, w, self._flag_tables[block],
-                  ctypes.c_uint(self._epochs[block]), ctypes.c_longlong(int(begin)), ctypes.c_longlong(int(end)),
+        if layer is None:
+            n_seg, seg, red = self._n_segments, self._segments, self._reduced
+        else:                                   # the weight and the bias range of one layer
+            n_seg = 2
+            seg = (ctypes.c_longlong * 4)(*self._segments[4 * layer:4 * layer + 4])
+            red = (ctypes.c_int * 2)(*self._reduced[2 * layer:2 * layer + 2])
+        _lib.call("sb_dp_sgd_update_segments", self.world_size, self.rank, g, p, w, self._flag_tables[block],
+                  ctypes.c_uint(self._epochs[block]), n_seg, seg, red if (reduced and mode != self.GATHER_MASTER) else None,
                   ctypes.c_float(lr), _lib.DTYPE_CODES[net.storage], mode, self._ranges, self._n_ranges,
                   int(max_blocks), self.timeout_ms, 1, stream_ptr(stream))
         self._epochs[block] += 2
@@ -225,8 +240,15 @@ class DataParallel:
             _lib.call("sb_stream_wait_event", stream_ptr(stream), self._done.ptr)
             return
         if self.world_size > 1 and self.peer_update is not None:
-            net.backward(x, mask, target, global_batch=self.global_batch, stream=stream)
-            self.peer_update.step(lr, stream=stream)
+            peer = self.peer_update
+            if any(getattr(peer, "fused_layers", ())):
+                # the weight-gradient GEMMs of the wide layers add their tiles into the owners' buffers
+                net.backward_dp(x, mask, target, peer.grads_table(), self.world_size, self.rank,
+                                global_batch=self.global_batch, stream=stream)
+                peer.step(lr, stream=stream, reduced=True)
+            else:
+                net.backward(x, mask, target, global_batch=self.global_batch, stream=stream)
+                peer.step(lr, stream=stream)
             return
         if self.world_size > 1 and self.all_reduce_segment is not None:
             pending = []

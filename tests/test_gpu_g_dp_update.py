@@ -181,3 +181,88 @@ def test_argument_checks(gpu):
             _lib.call("sb_dp_sgd_update", bad.get("world", 1), bad.get("rank", 0), g_t, p_t, w_t, f_t, ctypes.c_uint(1),
                       ctypes.c_longlong(0), ctypes.c_longlong(bad.get("n", n)), ctypes.c_float(0.1),
                       bad.get("dtype", _lib.DTYPE_CODES["bf16"]), bad.get("mode", 0), None, 0, 0, bad.get("timeout", 100), 0, None)
+
+
+@pytest.mark.parametrize("world,sizes", [(2, [32, 256, 256, 3]), (4, [64, 512, 512, 10])])
+def test_emulated_ranks_backward_adds_tiles_to_the_owners_and_update_reads_only_its_own(gpu, world, sizes):
+    """The data-parallel backward pass whose weight-gradient GEMMs add their tiles into the owner's buffer
+    (sb_mlp_backward_dp), with the ranks emulated one after the other on one GPU: every rank has its own net
+    buffers and batch shard, all gradient buffers sit in one table.  After all ranks' passes, rank r's buffer
+    holds the batch-wide sum of the rows it owns for the wide layers (rows of the other ranks stay zero);
+    the update over per-layer ranges (reduced = 1 for those layers, barriers off) then gives every rank the
+    oracle's SGD step on the whole batch and leaves the owned rows zero again."""
+    from spiral_b200 import _lib
+    shard, lr = 1024, 0.05
+    gbatch = shard * world
+    ws, bs = so.mlp_weights(61, sizes)
+    bs = [(so.rng(62 + i).normal(size=b.shape) * 0.05).astype(np.float32) for i, b in enumerate(bs)]
+    if sizes[0] == 32:
+        x, mask = so.leduc_inputs(63, gbatch)
+    else:
+        x = so.round_bf16(so.rng(63).random((gbatch, sizes[0]), dtype=np.float32))
+        mask = (so.rng(64).random((gbatch, sizes[-1])) < 0.6).astype(np.uint8)
+        mask[:, :2] = 1
+    target = so.random_target(65, mask)
+    nets = []
+    for r in range(world):
+        net = gpu.PolicyMLP(sizes, shard, in_dtype="bf16", training=True)
+        net.load_weights(ws, bs)
+        net.grads.fill_zero()
+        nets.append(net)
+    n_layers = len(sizes) - 1
+    fused = (ctypes.c_int * n_layers)()
+    _lib.call("sb_mlp_dp_fused_layers", n_layers, nets[0]._sizes_c, world, fused)
+    assert list(fused) == [1, 1, 0]
+    table = (ctypes.c_void_p * world)(*[n.grads.ptr for n in nets])
+    for r, net in enumerate(nets):
+        rows = slice(r * shard, (r + 1) * shard)
+        dx, dm, dt = gpu.to_storage(x[rows], "bf16"), gpu.DeviceArray.from_numpy(mask[rows]), gpu.DeviceArray.from_numpy(target[rows])
+        net.loss.fill_zero()
+        net.forward(dx, dm, head_flags=8)
+        net.backward_dp(dx, dm, dt, table, world, r, global_batch=gbatch)
+    gpu.synchronize()
+    new_w, new_b, loss, want = so.mlp_train_step(x, [so.round_bf16(w) for w in ws], bs, mask, target, lr,
+                                                 in_dtype="bf16", act_dtype="bf16")
+    got = [n.split_flat(n.grads.numpy()) for n in nets]
+    for layer in range(n_layers):
+        out = sizes[layer + 1]
+        if fused[layer]:
+            per = out // world
+            for r in range(world):
+                mine = got[r][layer][0]
+                assert so.rel_frobenius(mine[r * per:(r + 1) * per], want[layer][0][r * per:(r + 1) * per]) <= 2e-3
+                other = np.delete(mine, np.s_[r * per:(r + 1) * per], axis=0)
+                assert not other.any()                      # nobody adds into rows this rank does not own
+        else:
+            total = sum(got[r][layer][0] for r in range(world))
+            assert so.rel_frobenius(total, want[layer][0]) <= 2e-3
+        assert so.rel_frobenius(sum(got[r][layer][1] for r in range(world)), want[layer][1]) <= 5e-3
+    assert abs(sum(float(n.loss.numpy()[0]) for n in nets) - loss) <= 2e-3 * abs(loss)
+
+    # the update: one launch per rank over the per-layer ranges, reading only its own buffer where reduced
+    seg, red = [], []
+    net0 = nets[0]
+    for layer in range(n_layers):
+        end = net0.offsets[2 * layer + 2] if layer + 1 < n_layers else net0.n_params
+        seg += [net0.offsets[2 * layer], net0.offsets[2 * layer + 1], net0.offsets[2 * layer + 1], end]
+        red += [int(fused[layer]), 0]
+    seg_c, red_c = (ctypes.c_longlong * len(seg))(*seg), (ctypes.c_int * len(red))(*red)
+    flags = [gpu.DeviceArray.zeros((32,), "i32") for _ in range(world)]
+    p_t = (ctypes.c_void_p * world)(*[n.params.ptr for n in nets])
+    w_t = (ctypes.c_void_p * world)(*[n.w_compute.ptr for n in nets])
+    f_t = (ctypes.c_void_p * world)(*[f.ptr for f in flags])
+    for r in range(world):
+        _lib.call("sb_dp_sgd_update_segments", world, r, table, p_t, w_t, f_t, ctypes.c_uint(1), len(red), seg_c, red_c,
+                  ctypes.c_float(lr), _lib.DTYPE_CODES["bf16"], 0, None, 0, 0, 100, 0, None)
+    gpu.synchronize()
+    for r, net in enumerate(nets):
+        gw, gb = net.get_weights()
+        for layer in range(n_layers):
+            step_got, step_want = ws[layer] - gw[layer], ws[layer] - new_w[layer]
+            assert so.rel_frobenius(step_got, step_want) <= 1e-2          # fp32 cancellation in w - w'
+        np.testing.assert_array_equal(net.params.numpy(), nets[0].params.numpy())
+        np.testing.assert_array_equal(net.w_compute.numpy(), so.round_bf16(net.params.numpy()))
+        left = net.split_flat(net.grads.numpy())
+        for layer in range(n_layers):
+            if fused[layer]:
+                assert not left[layer][0].any()                          # consumed and zeroed by its owner
