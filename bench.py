@@ -376,7 +376,7 @@ def run_ours(args, rank, world, local_rank):
             out = [None] * world
             dist.all_gather_object(out, payload)
             return out
-        peer = sb.PeerUpdate(net, world, rank, exchange, fused_reduce=not args.no_fused_reduce)
+        peer = sb.PeerUpdate(net, world, rank, exchange, fused_reduce=args.fused_reduce)
     dp = sb.DataParallel(net, gbatch, all_reduce=(lambda g: dist.all_reduce(g)) if dist is not None else None,
                          world_size=world, rank=rank, all_reduce_segment=seg, peer_update=peer,
                          overlap_update=args.update == "peer-overlap", reserve_smem=args.reserve_smem)
@@ -896,9 +896,9 @@ def main():
     ap.add_argument("--update", choices=("peer", "peer-overlap", "nccl"), default="peer",
                     help="N > 1 training: the library's reduce+update kernel over peer memory (one launch after the "
                          "backward pass, or per layer beside it), or NCCL all-reduce + SGD")
-    ap.add_argument("--no-fused-reduce", action="store_true",
-                    help="peer update: keep every gradient local in the backward pass and let the update kernel read "
-                         "the peers' buffers (instead of weight-gradient GEMMs that add their tiles to the owners)")
+    ap.add_argument("--fused-reduce", action="store_true",
+                    help="peer update: the weight-gradient GEMMs add their tiles straight into the owning rank's "
+                         "buffer over peer memory (measured slower than letting the update kernel read the peers)")
     ap.add_argument("--reserve-smem", type=int, default=4096,
                     help="peer-overlap: shared memory per SM the backward GEMMs leave free for the update CTAs")
     ap.add_argument("--layerwise", action="store_true", help="narrow-net inference through one GEMM per layer")

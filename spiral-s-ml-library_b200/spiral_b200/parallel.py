@@ -51,7 +51,7 @@ class PeerUpdate:
 
     REPLICATED, SHARDED_MASTER, GATHER_MASTER = 0, 1, 2
 
-    def __init__(self, net, world_size, rank, exchange, timeout_ms=2000, shard_master=True, fused_reduce=True):
+    def __init__(self, net, world_size, rank, exchange, timeout_ms=2000, shard_master=True, fused_reduce=False):
         """``shard_master``: a rank's fp32 master parameters are kept current only in the slice it owns
         (plus all biases, which the forward pass reads in fp32): a third of the bytes leave the GPU per
         step.  Call ``gather_master()`` before reading the whole master vector on a rank
@@ -61,10 +61,13 @@ class PeerUpdate:
         self.net, self.world_size, self.rank = net, int(world_size), int(rank)
         self.timeout_ms = int(timeout_ms)
         self.shard_master = bool(shard_master)
-        # fused_reduce: the backward pass (net.backward_dp) adds every weight-gradient tile of the wide
-        # layers straight into the owning rank's gradient buffer over peer memory, so the update reads no
-        # remote gradients for those layers.  The parameter vector is handled as one range per layer's
-        # weights and one per layer's bias; rank r owns slice r of every range.
+        # The parameter vector is handled as one range per layer's weights and one per layer's bias; rank r
+        # owns slice r of every range.  fused_reduce: the backward pass (net.backward_dp) adds every
+        # weight-gradient tile of the wide layers straight into the owning rank's gradient buffer over peer
+        # memory, so the update reads no remote gradients for those layers.  Off by default: with split-K
+        # every split's tile crosses NVLink (4 x the gradient bytes at 32768 rows per rank) in a burst at
+        # the end of each GEMM, which measured 12 us per weight-gradient GEMM against the 10 us the update
+        # kernel saves (2 x B200).
         fused = (ctypes.c_int * net.n_layers)()
         if fused_reduce and self.world_size > 1:
             _lib.call("sb_mlp_dp_fused_layers", net.n_layers, net._sizes_c, self.world_size, fused)
