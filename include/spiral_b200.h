@@ -171,6 +171,18 @@ int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const voi
                  const float* bias, const uint8_t* mask, const void* aux_in, void* aux_out,
                  void* stream);
 
+/* The fp32 accuracy class (1e-5 relative Frobenius error against a float32 product) on the tensor
+ * cores: every operand is split into a TF32 head and a TF32 tail and the product is taken as
+ * Ah*Bh + Ah*Bl + Al*Bh in one tcgen05 GEMM with fp32 accumulation ("3 x TF32"; the reference's own
+ * arithmetic is single-pass TF32, corecuda/wmma.spi:20,78-82, which cannot meet 1e-5).  Two launches:
+ * the split into `workspace` (caller memory, at least sb_matmul_f32_workspace_bytes) and the GEMM.
+ * Contiguous dimensions must be multiples of 4 elements; other shapes use the SB_F32 class of
+ * sb_matmul_ex (FFMA).  epilogue: SB_EPI_BIAS, SB_EPI_RELU. */
+int sb_matmul_f32_workspace_bytes(int M, int N, int K, size_t* bytes);
+int sb_matmul_f32x3(int a_trans, int b_trans, float alpha, const float* A, const float* B, float beta, float* C,
+                    int M, int N, int K, int epilogue, const float* bias, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
 /* The dense layer with a row head described by `head` (ml/layers.spi:408-436 on top of :227-240):
  * C <- head(alpha * op(A) * op(B) + beta * C (+ bias) (ReLU)), fp32 output.  `epilogue` may hold
  * SB_EPI_BIAS, SB_EPI_RELU and SB_EPI_LN_L2; the head flags come from head->flags.  One launch when

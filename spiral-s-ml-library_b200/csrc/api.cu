@@ -62,7 +62,143 @@ int check_head(const char* who, const SbRowHead& h, int N) {
 }
 }  // namespace
 
+// ---------------------------------------------------------------------------
+// fp32 class on the tensor cores: the "3 x TF32" split.
+//
+// An fp32 value x is written hi + lo with hi = tf32(x) and lo = tf32(x - hi) (both rounded to
+// nearest); then A * B = Ah*Bh + Ah*Bl + Al*Bh up to terms of relative size 2^-22.  The three products
+// are ONE tensor-core GEMM over operands concatenated along K:
+//     [Ah | Ah | Al] (M x 3K)   times   [Bh ; Bl ; Bh] (3K x N),
+// accumulated in fp32 in tensor memory.  A pre-pass kernel writes the concatenated operands (in the
+// same storage order as the originals, so every layout flag carries over) into a caller workspace.
+// ---------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ float tf32_rn(float v) {
+  uint32_t u = __float_as_uint(v);
+  if ((u & 0x7f800000u) == 0x7f800000u) return v;
+  u += 0x0fffu + ((u >> 13) & 1u);
+  return __uint_as_float(u & 0xffffe000u);
+}
+
+// `src` is [rows, cols] row-major.  k_is_col: K runs along the columns (dst [rows, 3 * cols], the three
+// parts side by side in every row); otherwise K runs along the rows (dst [3 * rows, cols], the parts
+// stacked).  Part order p0, p1, p2 with 0 = hi, 1 = lo.  Two matrices per launch (A then B).
+struct SplitJob {
+  const float* src;
+  float* dst;
+  long long rows, cols;
+  int k_is_col;
+  int part[3];
+};
+
+// c_init: when non-null the same launch also brings C to beta * C (zero for beta == 0), the state the
+// split-K tiles are then added to.
+__global__ void split3_kernel(SplitJob ja, SplitJob jb, float* c_init, long long c_count, float beta) {
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
+  const long long na = ja.rows * ja.cols, total = na + jb.rows * jb.cols;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  if (c_init) {
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < c_count; t += step)
+      c_init[t] = beta == 0.0f ? 0.0f : beta * c_init[t];
+  }
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += step) {
+    const bool first = t < na;
+    const SplitJob& j = first ? ja : jb;
+    const long long i = first ? t : t - na;
+    const float x = j.src[i];
+    const float hi = tf32_rn(x);
+    const float lo = tf32_rn(x - hi);
+    const long long r = i / j.cols, c = i - r * j.cols;
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      const float v = j.part[p] ? lo : hi;
+      if (j.k_is_col) j.dst[r * (3 * j.cols) + p * j.cols + c] = v;
+      else j.dst[(p * j.rows + r) * j.cols + c] = v;
+    }
+  }
+}
+
+}  // namespace
+
 extern "C" {
+
+int sb_matmul_f32_workspace_bytes(int M, int N, int K, size_t* bytes) {
+  if (!bytes) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_f32_workspace_bytes: null output");
+  if (M < 0 || N < 0 || K < 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_f32_workspace_bytes: negative dimension");
+  const size_t a = ((size_t)3 * M * K * 4 + 255) / 256 * 256, b = ((size_t)3 * N * K * 4 + 255) / 256 * 256;
+  *bytes = a + b + 256;
+  return SB_OK;
+}
+
+int sb_matmul_f32x3(int a_trans, int b_trans, float alpha, const float* A, const float* B, float beta, float* C,
+                    int M, int N, int K, int epilogue, const float* bias, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  if (M < 0 || N < 0 || K <= 0) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_f32x3: dimensions M=%d N=%d K=%d", M, N, K);
+  if (epilogue & ~(SB_EPI_BIAS | SB_EPI_RELU)) return sb_fail(SB_ERR_UNSUPPORTED, "sb_matmul_f32x3: epilogue may hold SB_EPI_BIAS and SB_EPI_RELU");
+  if ((epilogue & SB_EPI_BIAS) && !bias) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_f32x3: SB_EPI_BIAS without a bias pointer");
+  if (M == 0 || N == 0) return SB_OK;
+  if (!A || !B || !C || !workspace) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_f32x3: null pointer");
+  size_t need = 0;
+  sb_matmul_f32_workspace_bytes(M, N, K, &need);
+  if (workspace_bytes < need) return sb_fail(SB_ERR_BAD_ARG, "sb_matmul_f32x3: workspace of %zu bytes, %zu needed", workspace_bytes, need);
+  if ((long long)3 * K > 0x7fffffffLL) return sb_fail(SB_ERR_TOO_LARGE, "sb_matmul_f32x3: 3 * K exceeds the index range");
+  // Row pitches of the concatenated operands must be multiples of 16 bytes (TMA): K % 4 == 0 where K is
+  // contiguous, M (N) % 4 == 0 where M (N) is.
+  const long long lda = a_trans ? M : 3LL * K, ldb = b_trans ? 3LL * K : N;
+  if ((lda * 4) % 16 != 0 || (ldb * 4) % 16 != 0 || ((long long)N * 4) % 16 != 0 || (reinterpret_cast<uintptr_t>(C) & 15))
+    return sb_fail(SB_ERR_MISALIGNED, "sb_matmul_f32x3: contiguous dimensions must be multiples of 4 elements and C 16-byte "
+                                      "aligned (use the SB_F32 class of sb_matmul_ex for other shapes)");
+  char* ws = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255);
+  float* a3 = reinterpret_cast<float*>(ws);
+  float* b3 = reinterpret_cast<float*>(ws + ((size_t)3 * M * K * 4 + 255) / 256 * 256);
+  SplitJob ja, jb;
+  ja.src = A; ja.dst = a3; ja.rows = a_trans ? K : M; ja.cols = a_trans ? M : K; ja.k_is_col = a_trans ? 0 : 1;
+  ja.part[0] = 0; ja.part[1] = 0; ja.part[2] = 1;                     // Ah | Ah | Al
+  jb.src = B; jb.dst = b3; jb.rows = b_trans ? N : K; jb.cols = b_trans ? K : N; jb.k_is_col = b_trans ? 1 : 0;
+  jb.part[0] = 0; jb.part[1] = 1; jb.part[2] = 0;                     // Bh ; Bl ; Bh
+  const long long total = (long long)M * K + (long long)N * K;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)sb_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = (cudaStream_t)stream;
+  // Split-K with the tiles ADDED to C (TMA reduce-add) serves two ends.  Accuracy: the tensor core's
+  // fp32 accumulator does not round to nearest, so a long chain of accumulations drifts (4e-5 at
+  // K = 4096 in one pass); chains of at most 256 elements of K per part stay far below 1e-5 and the
+  // additions between chains are ordinary fp32 additions.  Parallelism: a 512 x 512 output is four
+  // tiles; with the splits it is spread over the whole GPU.  Needs a plain product (no bias / ReLU)
+  // and whole 32-column chunks; C is first brought to beta * C (zero for beta == 0).
+  int splits = 1;
+  if (epilogue == 0 && N % 32 == 0 && 3 * K >= 512) {
+    const int by_accuracy = (K + 255) / 256;
+    const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    long long by_fill = tiles > 0 ? (sb_sm_count() / 2) / tiles : 1;                // one wave of CTA pairs
+    if (by_fill > 8) by_fill = 8;             // every split adds a whole tile to C: more than a few cost more than they spread
+    const int by_k = (3 * K) / 128 > 0 ? (3 * K) / 128 : 1;                          // at least two k-blocks of 64 per split
+    long long want = by_accuracy > by_fill ? by_accuracy : by_fill;
+    if (want > by_k) want = by_k;
+    if (want > 128) want = 128;
+    splits = (int)(want < 1 ? 1 : want);
+  }
+  const bool init_c = splits > 1 && beta != 1.0f;
+  SB_CUDA(sb_launch(split3_kernel, dim3((int)blocks), dim3(256), 0, s, 1, ja, jb, init_c ? C : (float*)nullptr,
+                    (long long)M * N, beta));
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  if (splits > 1) {
+    int used = 0;
+    // `C` doubles as the partials pointer: every condition for adding into C holds here by construction
+    // (fp32 output, no epilogue, aligned rows, whole chunks), so no partial is ever written.
+    int rc = sb_umma_gemm_launch(a_trans, b_trans, alpha, a3, b3, 0.0f, C, M, N, 3 * K, SB_TF32, SB_F32, 0, nullptr, nullptr,
+                                 nullptr, nullptr, s, splits, &used, nullptr, C);
+    if (rc != SB_OK) return rc;
+    if (used != 1) return sb_fail(SB_ERR_UNSUPPORTED, "internal: sb_matmul_f32x3 expected its splits to be added into C");
+    return SB_OK;
+  }
+  return sb_umma_gemm_launch(a_trans, b_trans, alpha, a3, b3, beta, C, M, N, 3 * K, SB_TF32, SB_F32, epilogue, bias, nullptr,
+                             nullptr, nullptr, s);
+}
 
 int sb_matmul_ex(int a_trans, int b_trans, float alpha, const void* A, const void* B, float beta,
                  void* C, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,

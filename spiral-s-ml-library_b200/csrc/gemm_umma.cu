@@ -1228,8 +1228,10 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_trans ? 1 : 0;   // A stored [K,M]: M contiguous
   p.b_mn = b_trans ? 0 : 1;   // B stored [K,N]: N contiguous
+  // Whole 32-column chunks per tile where every chunk must leave as a box: sign words, column sums, and
+  // tiles that are added to C (split-K accumulation, peer copies).
   plan_umma(p, in_dtype, cached_sm_count(), !(epi & EPI_HEAD_MASK) && sb_pair_mode_enabled(),
-            (epi & (EPI_GATE_MASK | SB_EPI_COLSUM_OUT)) != 0);
+            (epi & (EPI_GATE_MASK | SB_EPI_COLSUM_OUT)) != 0 || (split_partials && splits > 1) || to_peers);
   p.alpha = alpha; p.beta = beta;
   p.C = C; p.ldc = N; p.out_dtype = out_dtype;
   p.epi = epi; p.bias = bias; p.mask = mask; p.aux_in = aux_in; p.aux_out = aux_out;
@@ -1278,7 +1280,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     if (split_partials && p.splits > 1 && !to_peers) {
       // Accumulating form: fp32 output, every chunk of a tile leaves as a TMA box (whole 32-column
       // chunks, 16-byte aligned rows), nothing else in the epilogue.
-      if (out_dtype == SB_F32 && epi == 0 && beta == 0.0f && alpha == 1.0f && p.block_n % 32 == 0 &&
+      if (out_dtype == SB_F32 && epi == 0 && beta == 0.0f && p.block_n % 32 == 0 &&
           ((long long)N * 4) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
         p.reduce_add = 1;
         p.split_stride = 0;

@@ -95,6 +95,8 @@ SIGNATURES = {
     "sb_gemm_profile_entry": (_I, [_I, POINTER(ctypes.c_double), POINTER(ctypes.c_double)]),
     "sb_matmul_tf32": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _P]),
     "sb_matmul_ex": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "sb_matmul_f32_workspace_bytes": (_I, [_I, _I, _I, POINTER(c_size_t)]),
+    "sb_matmul_f32x3": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _P, _P, _Z, _P]),
     "sb_matmul_head": (_I, [_I, _I, _F, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P, POINTER(HeadSpec), _P]),
     "sb_gemm_reserve_smem": (_I, [_I]),
     "sb_matmul_plan": (_I, [_I, _I, _I, _I, _I, _I, _I, _IP]),

@@ -35,6 +35,28 @@ def _dims(a_trans, b_trans, a, b, c):
     return m, n, k
 
 
+_F32X3_WORKSPACES = {}
+
+
+def _f32x3_aligned(a_trans, b_trans, m, n, k):
+    """Contiguous dimensions are multiples of 4 elements (16-byte row pitches for the split operands)."""
+    return n % 4 == 0 and (m % 4 == 0 if a_trans else k % 4 == 0) and (k % 4 == 0 if b_trans else n % 4 == 0)
+
+
+def _f32x3_workspace(m, n, k, stream):
+    from .device import DeviceArray
+    need = ctypes.c_size_t(0)
+    _lib.call("sb_matmul_f32_workspace_bytes", m, n, k, ctypes.byref(need))
+    key = stream_ptr(stream) or 0
+    ws = _F32X3_WORKSPACES.get(key)
+    if ws is None or ws.nbytes < need.value:
+        if ws is not None:
+            _lib.call("sb_stream_sync", stream_ptr(stream))      # the old buffer may still be in use
+        ws = DeviceArray((need.value,), "u8")
+        _F32X3_WORKSPACES[key] = ws
+    return ws
+
+
 def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype=None, epilogue=(), bias=None, mask=None,
            aux_in=None, aux_out=None, stream=None):
     """``c <- alpha * op(a) @ op(b) + beta * c`` with an optional fused epilogue.
@@ -57,6 +79,15 @@ def matmul(a_trans, b_trans, alpha, a, b, beta, c, in_dtype=None, epilogue=(), b
     epi = 0
     for name in epilogue:
         epi |= EPILOGUE_FLAGS[name]
+    if in_dtype == "f32" and out_dtype == "f32" and not (epi & ~(_lib.EPI_BIAS | _lib.EPI_RELU)) and k > 0 \
+            and _f32x3_aligned(bool(a_trans), bool(b_trans), m, n, k) and device_ptr(c) % 16 == 0:
+        # fp32 class on the tensor cores (3 x TF32); the split operands live in a workspace this host
+        # keeps per stream and grows on demand (the C ABI itself allocates nothing).
+        ws = _f32x3_workspace(m, n, k, stream)
+        _lib.call("sb_matmul_f32x3", int(bool(a_trans)), int(bool(b_trans)), ctypes.c_float(alpha), device_ptr(a),
+                  device_ptr(b), ctypes.c_float(beta), device_ptr(c), m, n, k, epi, device_ptr(bias), ws.ptr,
+                  ws.nbytes, stream_ptr(stream))
+        return c
     _lib.call("sb_matmul_ex", int(bool(a_trans)), int(bool(b_trans)), ctypes.c_float(alpha),
               device_ptr(a), device_ptr(b), ctypes.c_float(beta), device_ptr(c), m, n, k,
               _lib.DTYPE_CODES[in_dtype], _lib.DTYPE_CODES[out_dtype], epi, device_ptr(bias),
