@@ -286,9 +286,11 @@ int sb_mlp_forward(int n_layers, const int* sizes, int batch, int in_dtype, cons
 /* The same forward pass as ONE persistent kernel for narrow nets (the Leduc-sized
  * policy MLP): hidden activations stay in shared memory / TMEM, so no activations
  * buffer is needed.  Replaces the same reference chain (ml/layers.py:4500-4546).
- * Limits: in_dtype SB_F16 or SB_BF16; sizes[0] in 8..256 and a multiple of 8;
- * hidden widths multiples of 64 up to 256; sizes[n_layers] <= 64; n_layers <= 8;
- * otherwise SB_ERR_UNSUPPORTED (use sb_mlp_forward). */
+ * Limits: in_dtype SB_F16 or SB_BF16; sizes[0] in 8..512 and a multiple of 8 (the
+ * input tile, the widest hidden tile and the weight ring share 225 KB of shared memory:
+ * inputs beyond 256 fit with hidden layers of at most 128 columns); hidden widths
+ * multiples of 64 up to 256; sizes[n_layers] <= 64; n_layers <= 8; otherwise
+ * SB_ERR_UNSUPPORTED (use sb_mlp_forward). */
 int sb_mlp_forward_fused(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
                          const void* w_compute, const float* params, int head, const uint8_t* mask,
                          float* out, int32_t* actions, void* stream);

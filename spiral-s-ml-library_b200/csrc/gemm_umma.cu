@@ -99,6 +99,30 @@ struct UmmaGemmParams {
   int peer_rows;       // > 0: rows [r * peer_rows, (r + 1) * peer_rows) of C are added to rank r's copy (out map r)
 };
 
+// Walks the work of one worker (a CTA, or a CTA pair): work items (split, tile) strided over the
+// workers.  Items of one split sit side by side, so the workers that run at the same time read the same
+// K range of different tiles and share the operands through L2.  (Cutting the k-blocks of all tiles
+// into one equal range per worker -- "stream-K" -- was measured: no worker idles, but no two workers
+// are at the same K at the same time, every operand byte comes from DRAM once per tile column instead
+// of once, and the Hold'em weight-gradient GEMM went from 0.36 to 0.49 ms.)
+struct WorkIter {
+  int work, stride;
+  __device__ __forceinline__ WorkIter(const UmmaGemmParams&, int worker, int num_workers) {
+    work = worker;
+    stride = num_workers;
+  }
+  // The next item: tile index, split index, k-block range.  False when done.
+  __device__ __forceinline__ bool next(const UmmaGemmParams& p, int& tile, int& split, int& kb_begin, int& kb_end) {
+    if (work >= p.num_work) return false;
+    split = work / p.num_tiles;
+    tile = work - split * p.num_tiles;
+    kb_begin = split * p.kb_per_split;
+    kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+    work += stride;
+    return true;
+  }
+};
+
 __device__ __forceinline__ void tile_coords(const UmmaGemmParams& p, int tile, int& m_blk, int& n_blk) {
   constexpr int GROUP = 8;
   const int per_group = GROUP * p.tiles_n;
@@ -811,14 +835,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t a_sub_bytes = p.a_sub_bytes, b_sub_bytes = p.b_sub_bytes;
       const int stages = p.stages;
       uint32_t a_dst = stage_base;
-      for (int work = worker; ok && work < p.num_work; work += num_workers) {
-        const int split = work / p.num_tiles;
+      WorkIter it(p, worker, num_workers);
+      int tile, split, kb_begin, kb_end;
+      while (ok && it.next(p, tile, split, kb_begin, kb_end)) {
         int m_blk, n_blk;
-        tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
+        tile_coords(p, tile, m_blk, n_blk);
         const int m0 = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M;
         const int n0 = n_blk * p.block_n + (int)cta_rank * b_cols;
-        const int kb_begin = split * p.kb_per_split;
-        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
         int k0 = kb_begin * block_k;
         for (int kb = kb_begin; kb < kb_end; ++kb, k0 += block_k) {
           if (!mbar_wait(empty0 + 8u * (uint32_t)stage, phase ^ 1u, abortp, SB_SITE_PRODUCER_EMPTY)) {
@@ -885,10 +908,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
       const int stages = p.stages;
       uint32_t a_lo = a_lo0, b_lo = b_lo0;
-      for (int work = worker; ok && work < p.num_work; work += num_workers) {
-        const int split = work / p.num_tiles;
-        const int kb_begin = split * p.kb_per_split;
-        const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+      WorkIter it(p, worker, num_workers);
+      int tile, split, kb_begin, kb_end;
+      while (ok && it.next(p, tile, split, kb_begin, kb_end)) {
         if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, abortp, SB_SITE_MMA_TMEM_EMPTY)) {
           ok = false;
           break;
@@ -948,10 +970,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         ((p.epi & SB_EPI_COLSUM_OUT) ? 16 : 0);
       if (flags == 0 || flags == 3 || flags == 7 || flags == 8 || flags == 16 || flags == 24) epi_mode = flags;
     }
-    for (int work = worker; work < p.num_work; work += num_workers) {
-      const int split = work / p.num_tiles;
+    WorkIter it(p, worker, num_workers);
+    int tile, split, kb_begin, kb_end;
+    while (it.next(p, tile, split, kb_begin, kb_end)) {
       int m_blk, n_blk;
-      tile_coords(p, work - split * p.num_tiles, m_blk, n_blk);
+      tile_coords(p, tile, m_blk, n_blk);
       const int row0_warp = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M + quad * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
       const uint32_t full_bar = smem_u32(&bar_tmem_full[acc]);

@@ -16,8 +16,9 @@
 //                    into the activation tile in exactly the swizzled K-major layout
 //                    the next layer's MMAs read; the last layer ends in the row head
 //                    (masked softmax / regret matching / argmax) written to global.
-// 16-bit arithmetic classes only (SB_F16, SB_BF16); widths: input <= 256 and a
-// multiple of 8, hidden layers multiples of 64 up to 256, output <= 64 (<= 256 when a
+// 16-bit arithmetic classes only (SB_F16, SB_BF16); widths: input <= 512 and a
+// multiple of 8 (inputs beyond 256 as far as shared memory allows: the reference's Hold'em
+// policy net is 512 -> 64, game/nl_hu_holdem/model_cem.spi:71-98), hidden layers multiples of 64 up to 256, output <= 64 (<= 256 when a
 // prefix mask confines the head to its first 64 columns, the shape of the reference's
 // own policy nets, game/leduc/model_cem.spi:37,52-60).
 //
@@ -36,7 +37,7 @@ constexpr int FM_THREADS = 320;
 constexpr int FM_EPI_WARPS = 8;
 constexpr int FM_W_STAGES = 4;
 constexpr uint32_t FM_CHUNK_BYTES = 128u * 128u;       // activation chunk: 128 rows x 64 elements x 2 B
-constexpr uint32_t FM_STAGE_BYTES = 256u * 128u;       // weight stage: up to 256 rows x 64 elements x 2 B
+// A weight stage holds one 64-column K-chunk of a layer: (widest layer's rows) x 128 bytes, at most 256 rows.
 
 struct FusedMaps {
   CUtensorMap x;                      // [batch, in] box {64, 128}
@@ -59,6 +60,7 @@ struct FusedParams {
   long long member_stride;            // elements between two members' parameter vectors
   long long out_stride;               // elements between two members' outputs (batch x n_out)
   uint32_t x_chunks;                  // chunks of the input tile
+  uint32_t stage_bytes;               // bytes of one weight stage
   uint32_t act_offset, w_offset;      // byte offsets of the activation tile and the weight ring
   // head
   float* out;
@@ -253,7 +255,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
               break;
             }
             mbar_arrive_expect_tx(smem_u32(&bar_w_full[stage]), p.w_bytes[l]);
-            tma_load_3d(w_base + (uint32_t)stage * FM_STAGE_BYTES, &maps.w[l], c * 64, 0, member, smem_u32(&bar_w_full[stage]));
+            tma_load_3d(w_base + (uint32_t)stage * p.stage_bytes, &maps.w[l], c * 64, 0, member, smem_u32(&bar_w_full[stage]));
             if (++stage == FM_W_STAGES) {
               stage = 0;
               w_phase ^= 1u;
@@ -287,7 +289,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
             if (!mbar_wait(smem_u32(&bar_w_full[stage]), w_phase, abortp, SB_SITE_MLP_WEIGHTS)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t a_lo = (uint32_t)umma_smem_desc(a_base + (uint32_t)c * FM_CHUNK_BYTES, 16u, 1024u, 2u);
-            const uint32_t b_lo = (uint32_t)umma_smem_desc(w_base + (uint32_t)stage * FM_STAGE_BYTES, 16u, 1024u, 2u);
+            const uint32_t b_lo = (uint32_t)umma_smem_desc(w_base + (uint32_t)stage * p.stage_bytes, 16u, 1024u, 2u);
 #pragma unroll
             for (uint32_t ks = 0; ks < 4; ++ks) {
               umma_issue<false, false>(tmem_base, a_lo + 2u * ks, hi, b_lo + 2u * ks, hi, p.idesc[l], accumulate);
@@ -442,7 +444,7 @@ static int fused_launch(const char* who, int n_layers, const int* sizes, int bat
   if (batch < 0) return sb_fail(SB_ERR_BAD_ARG, "%s: negative batch", who);
   if (head.flags & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX | SB_EPI_SAMPLE))
     return sb_fail(SB_ERR_BAD_ARG, "%s: the head may hold softmax, regret matching, arg-max and sampling", who);
-  if (sizes[0] < 8 || sizes[0] > 256 || sizes[0] % 8) return sb_fail(SB_ERR_UNSUPPORTED, "%s: input width %d (8..256, multiple of 8)", who, sizes[0]);
+  if (sizes[0] < 8 || sizes[0] > 512 || sizes[0] % 8) return sb_fail(SB_ERR_UNSUPPORTED, "%s: input width %d (8..512, multiple of 8)", who, sizes[0]);
   for (int i = 1; i < n_layers; ++i)
     if (sizes[i] < 64 || sizes[i] > 256 || sizes[i] % 64)
       return sb_fail(SB_ERR_UNSUPPORTED, "%s: hidden width %d (64..256, multiple of 64)", who, sizes[i]);
@@ -503,7 +505,8 @@ static int fused_launch(const char* who, int n_layers, const int* sizes, int bat
     p.tile_counters = decide->tile_counters; p.ensemble_id = decide->ensemble_id; p.action = decide->action;
     p.prob_selected = decide->prob_selected; p.prob_ensemble = decide->prob_ensemble;
   }
-  const size_t smem = (size_t)p.w_offset + (size_t)FM_W_STAGES * FM_STAGE_BYTES + 1024;
+  p.stage_bytes = ((uint32_t)max_n * 128u + 1023u) / 1024u * 1024u;     // stages stay 1024-byte aligned (swizzle atoms)
+  const size_t smem = (size_t)p.w_offset + (size_t)FM_W_STAGES * p.stage_bytes + 1024;
 
   static std::atomic<bool> attr_set[64];
   int dev = 0;
@@ -512,7 +515,9 @@ static int fused_launch(const char* who, int n_layers, const int* sizes, int bat
     SB_CUDA(cudaFuncSetAttribute(mlp_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024));
     attr_set[dev].store(true, std::memory_order_release);
   }
-  if (smem > 225 * 1024) return sb_fail(SB_ERR_UNSUPPORTED, "%s: %zu bytes of shared memory needed", who, smem);
+  if (smem > 225 * 1024)
+    return sb_fail(SB_ERR_UNSUPPORTED, "%s: the input tile, the widest hidden tile and the weight ring need %zu bytes of "
+                                       "shared memory (inputs wider than 256 fit with hidden layers of at most 128)", who, smem);
   const int sms = sb_sm_count();
   const int grid = p.num_items < sms ? p.num_items : sms;
   double flops = 0.0;

@@ -242,7 +242,7 @@ class EnsemblePolicyMLP:
     single launch of the fused kernel (the reference builds such nets with ``layers.matmul_ensemble``,
     ml/layers.spi:468-471, and runs the graph once per member, ml/models.spi:47-49).
 
-    16-bit arithmetic classes and the fused kernel's width limits only (input <= 256, hidden layers
+    16-bit arithmetic classes and the fused kernel's width limits only (input <= 512, hidden layers
     multiples of 64 up to 256, at most 64 outputs -- or 256 under a prefix mask of at most 64 columns).
     Outputs: ``probs`` fp32 [members, batch, n_out] and, with an argmax head, ``actions`` int32
     [members, batch].

@@ -124,3 +124,27 @@ def test_policy_decide_with_a_legal_action_mask_and_ready_input(gpu):
     np.testing.assert_array_equal(out["ensemble_id"].numpy(), member)
     np.testing.assert_array_equal(out["sampling_prob_ensemble"].numpy(), by_member)
     assert np.all(mask[np.arange(batch), action] == 1)
+
+
+def test_holdem_cem_shape_512_to_64(gpu):
+    """The reference's Hold'em policy net (game/nl_hu_holdem/model_cem.spi:62-98): one dense layer from the
+    512-wide pickled state to 64 columns, `masked_regret_matching'` over the first 3, an ensemble of 4.  The
+    pickled state is bits and one-hot groups, so the input here is {0,1}."""
+    sizes, members, batch = [512, 64], 4, 5000
+    ws = member_weights(750, sizes, members)
+    x = (so.rng(75).random((batch, 512)) < 0.1).astype(np.float32)
+    ens = gpu.EnsemblePolicyMLP(sizes, batch, members, in_dtype="bf16", with_bias=False)
+    ens.load_weights(ws)
+    l0 = gpu.launch_count()
+    out = ens.decide(9, x=gpu.to_storage(x, "bf16"), head=("regret_matching",), prefix=3)
+    assert gpu.launch_count() - l0 == 1
+    probs = out["output_probs"].numpy()
+    want = so.ensemble_forward(x, ws, None, so.prefix_mask((batch, 64), 3), in_dtype="bf16", head=("regret_matching",))
+    assert so.rel_frobenius(probs, want) <= TOL
+    action, member, selected, by_member, indices = so.policy_decide(probs, 9)
+    np.testing.assert_array_equal(out["action"].numpy(), action)
+    np.testing.assert_array_equal(out["sampling_prob_ensemble"].numpy(), by_member)
+    # a wide input with wide hidden layers does not fit the kernel's shared memory and says so
+    with pytest.raises(gpu.SpiralError) as err:
+        gpu.EnsemblePolicyMLP([512, 256, 64], 128, 2, in_dtype="bf16").forward_head(gpu.DeviceArray((128, 512), "bf16"), prefix=3)
+    assert err.value.code == -3
