@@ -4,8 +4,9 @@
 // (BlockMap / BlockRowMap / BlockRowReduce, ml/layers.spi:195-210;
 // row math ml/primitives.spi:701-722,748-780).
 //
-// One warp owns one row; lanes stride over the columns with warp-shuffle
-// reductions, so any column count works.
+// Rows of at most 64 columns (the policy heads) take one thread per row with the
+// row in registers; wider rows one warp per row, lanes striding over the columns
+// with warp-shuffle reductions, so any column count works.
 #include "common.cuh"
 #include "row_head.cuh"
 
@@ -82,6 +83,20 @@ __global__ void row_map_kernel(const float* x, float* out, int rows, int cols,
       s = warp_sum(s);
       for (int j = lane; j < cols; j += 32) orow[j] = s != 0.f ? xr[j] / s : 0.f;
     }
+  }
+}
+
+// Narrow rows (at most 64 columns, the policy heads): one THREAD per row with the row in registers, the
+// same code the fused GEMM heads run (row_head.cuh), instead of a warp per row with most lanes idle.
+// x and out are [rows, cols] fp32 and may alias (a row is read whole before it is written).
+template <int W>
+__global__ void __launch_bounds__(128) row_head_kernel(const float* x, float* out, int rows, SbRowHead h) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x) {
+    float v[W];
+    const float* xr = x + r * h.n;
+#pragma unroll
+    for (int j = 0; j < W; ++j) v[j] = j < h.n ? xr[j] : 0.f;
+    sb_row_head_finish<W>(h, v, r, out + r * h.n);
   }
 }
 
@@ -326,10 +341,27 @@ static int row_args_ok(const char* who, const void* x, const void* out, int rows
   return SB_OK;
 }
 
+// Softmax / regret matching of rows of at most 64 columns through the thread-per-row kernel.
+static int launch_narrow_head(const float* x, float* out, int rows, int cols, const uint8_t* mask, int prefix, int flag,
+                              void* stream) {
+  SbRowHead h;
+  memset(&h, 0, sizeof(h));
+  h.n = cols; h.flags = flag; h.prefix = prefix < 0 ? -1 : (prefix > cols ? cols : prefix); h.mask = mask;
+  const int grid = grid_for(rows, 128);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cols <= 16) row_head_kernel<16><<<grid, 128, 0, s>>>(x, out, rows, h);
+  else if (cols <= 32) row_head_kernel<32><<<grid, 128, 0, s>>>(x, out, rows, h);
+  else row_head_kernel<64><<<grid, 128, 0, s>>>(x, out, rows, h);
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
 int sb_row_softmax(const float* x, float* out, int rows, int cols, const uint8_t* mask, int prefix,
                    void* stream) {
   int rc = row_args_ok("sb_row_softmax", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  if (cols <= 64) return launch_narrow_head(x, out, rows, cols, mask, prefix, SB_EPI_MASKED_SOFTMAX, stream);
   row_map_kernel<ROW_SOFTMAX><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, mask, prefix);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
@@ -340,6 +372,7 @@ int sb_row_regret_matching(const float* x, float* out, int rows, int cols, const
                            int prefix, void* stream) {
   int rc = row_args_ok("sb_row_regret_matching", x, out, rows, cols);
   if (rc != SB_OK) return rc > 0 ? SB_OK : rc;
+  if (cols <= 64) return launch_narrow_head(x, out, rows, cols, mask, prefix, SB_EPI_REGRET_MATCHING, stream);
   row_map_kernel<ROW_REGRET><<<grid_for(rows, 8), 256, 0, (cudaStream_t)stream>>>(x, out, rows, cols, mask, prefix);
   SB_COUNT_LAUNCH();
   SB_CUDA(cudaGetLastError());
