@@ -770,6 +770,8 @@ PROFILE_CASES = {
     "gemm4096_bf16_tn": (True, False, 4096, 4096, 4096, "bf16", "f32", ()),
     "gemm4096_tf32_nt": (False, True, 4096, 4096, 4096, "tf32", "f32", ()),
     "holdem_layer_fwd": (False, True, 65536, 1024, 1024, "bf16", "bf16", ("bias", "relu")),
+    "holdem_layer_plain": (False, True, 65536, 1024, 1024, "bf16", "bf16", ()),
+    "holdem_layer_plain_f32": (False, True, 65536, 1024, 1024, "bf16", "f32", ()),
     "holdem_layer_dgrad": (False, False, 65536, 1024, 1024, "bf16", "bf16", ("relu_grad",)),
     "holdem_layer_wgrad": (True, False, 1024, 1024, 65536, "bf16", "f32", ()),
     "holdem_layer_dgrad_bits": (False, False, 65536, 1024, 1024, "bf16", "bf16", ("relu_grad_mask",)),

@@ -55,6 +55,7 @@ struct FusedParams {
   const float* bias[FM_MAX_LAYERS];   // may be null
   int is_bf16;
   int tmem_cols;
+  int acc_stride;                     // TMEM columns between the two accumulators (layers alternate between them)
   int num_tiles;                      // 128-row tiles of the batch
   int num_items;                      // work items = tiles x ensemble members
   long long member_stride;            // elements between two members' parameter vectors
@@ -104,9 +105,13 @@ __device__ __noinline__ void fused_head(const SbRowHead& h, const float* bias, f
 // Writes relu(acc + bias) in the storage type into the activation tile, in the
 // 128-byte-swizzled K-major layout the next layer's A descriptors expect:
 // element (row, j) -> chunk j / 64, byte row * 128 + (((j % 64) / 8) ^ (row % 8)) * 16 + (j % 8) * 2.
+// After each 32-column chunk the warp arrives on the barrier of the 64-column activation chunk it
+// belongs to (`chunk_bar0` + 8 bytes per chunk): the next layer's MMAs on that K-chunk start as soon as
+// all eight warps have delivered it, while the later chunks of this layer are still being finished.
 template <bool BF16>
 __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const float* bias, uint32_t act_base,
-                                          uint32_t bias_smem, int row_in_tile, int lane, int half, int norm) {
+                                          uint32_t bias_smem, int row_in_tile, int lane, int half, int norm,
+                                          uint32_t chunk_bar0) {
   const int nchunks = n_cols >> 5;
   // Row normalisation (local_ln_l2, ml/primitives.spi:701-703; no bias in this mode): a first pass
   // over the whole accumulator row sums the squares; both warps of a quadrant do it for themselves.
@@ -168,6 +173,11 @@ __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const floa
       st_shared_v4(addr, make_uint4(packed[0], packed[1], packed[2], packed[3]));
     }
     bias_cur = bias_nxt;
+    // generic-proxy writes of the activation tile must be visible to the MMA's async-proxy reads
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(chunk_bar0 + 8u * (uint32_t)(c >> 1));
   }
 }
 
@@ -193,7 +203,8 @@ __device__ __noinline__ void decide_row(const FusedParams& p, long long row) {
 __global__ void __launch_bounds__(FM_THREADS, 1)
 mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__ FusedParams p) {
   extern __shared__ uint8_t fm_smem_raw[];
-  __shared__ __align__(8) uint64_t bar_x_full, bar_x_empty, bar_acc_full, bar_act_ready, bar_tail_in, bar_tail_out;
+  __shared__ __align__(8) uint64_t bar_x_full, bar_x_empty, bar_acc_full, bar_item_done, bar_tail_in, bar_tail_out;
+  __shared__ __align__(8) uint64_t bar_chunk[4];       // 64-column chunk k of the activation tile is written (8 warps each)
   __shared__ __align__(8) uint64_t bar_w_full[FM_W_STAGES], bar_w_empty[FM_W_STAGES];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -211,7 +222,8 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
     mbar_init(smem_u32(&bar_x_full), 1);
     mbar_init(smem_u32(&bar_x_empty), 1);
     mbar_init(smem_u32(&bar_acc_full), 1);
-    mbar_init(smem_u32(&bar_act_ready), FM_EPI_WARPS);
+    mbar_init(smem_u32(&bar_item_done), FM_EPI_WARPS);
+    for (int k = 0; k < 4; ++k) mbar_init(smem_u32(&bar_chunk[k]), FM_EPI_WARPS);
     mbar_init(smem_u32(&bar_tail_in), 4);       // the four warps that finish head rows
     mbar_init(smem_u32(&bar_tail_out), 1);
     for (int s = 0; s < FM_W_STAGES; ++s) {
@@ -267,7 +279,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0;
-      uint32_t w_phase = 0, x_phase = 0, act_phase = 0;
+      uint32_t w_phase = 0, x_phase = 0, item_phase = 0, chunk_phase = 0;     // chunk_phase: one parity bit per chunk barrier
       bool ok = true;
       const uint32_t hi = (uint32_t)(umma_smem_desc(0u, 16u, 1024u, 2u) >> 32);
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
@@ -278,21 +290,28 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
             x_phase ^= 1u;
             a_base = x_base;
           } else {
-            // the epilogue has drained the accumulator and written this layer's input
-            if (!mbar_wait(smem_u32(&bar_act_ready), act_phase, abortp, SB_SITE_MLP_ACT)) { ok = false; break; }
-            act_phase ^= 1u;
             a_base = act_base;
           }
           tc_fence_after_sync();
+          // Layers alternate between two accumulators: the epilogue of layer l-1 still reads its own while
+          // this layer's first MMAs run.  (Layer l+1 reuses the accumulator of layer l-1 only after every
+          // chunk of this layer's input -- the whole of layer l-1's epilogue -- has been delivered.)
+          const uint32_t d_tmem = tmem_base + (uint32_t)((l & 1) * p.acc_stride);
           uint32_t accumulate = 0u;
           for (int c = 0; c < p.k_chunks[l]; ++c) {
+            if (l > 0) {
+              // K-chunk c of this layer's input = 64-column chunk c of the previous layer's output
+              if (!mbar_wait(smem_u32(&bar_chunk[c]), (chunk_phase >> c) & 1u, abortp, SB_SITE_MLP_ACT)) { ok = false; break; }
+              chunk_phase ^= 1u << c;
+              tc_fence_after_sync();
+            }
             if (!mbar_wait(smem_u32(&bar_w_full[stage]), w_phase, abortp, SB_SITE_MLP_WEIGHTS)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t a_lo = (uint32_t)umma_smem_desc(a_base + (uint32_t)c * FM_CHUNK_BYTES, 16u, 1024u, 2u);
             const uint32_t b_lo = (uint32_t)umma_smem_desc(w_base + (uint32_t)stage * p.stage_bytes, 16u, 1024u, 2u);
 #pragma unroll
             for (uint32_t ks = 0; ks < 4; ++ks) {
-              umma_issue<false, false>(tmem_base, a_lo + 2u * ks, hi, b_lo + 2u * ks, hi, p.idesc[l], accumulate);
+              umma_issue<false, false>(d_tmem, a_lo + 2u * ks, hi, b_lo + 2u * ks, hi, p.idesc[l], accumulate);
               accumulate = 1u;
             }
             tc_commit(smem_u32(&bar_w_empty[stage]));
@@ -305,10 +324,11 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
           if (l == 0) tc_commit(smem_u32(&bar_x_empty));     // the input tile may be refilled
           tc_commit(smem_u32(&bar_acc_full));
         }
-        // The next tile's first layer overwrites the accumulator: wait until the head has read it.
+        // The next tile's layers overwrite the accumulators and the activation tile: wait until the head
+        // has read the last accumulator.
         if (ok && item + (int)gridDim.x < p.num_items) {
-          if (!mbar_wait(smem_u32(&bar_act_ready), act_phase, abortp, SB_SITE_MLP_ACT)) break;
-          act_phase ^= 1u;
+          if (!mbar_wait(smem_u32(&bar_item_done), item_phase, abortp, SB_SITE_MLP_ACT)) break;
+          item_phase ^= 1u;
         }
       }
     }
@@ -339,21 +359,22 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
         if (!mbar_wait(smem_u32(&bar_acc_full), acc_phase, abortp, SB_SITE_MLP_ACC)) { ok = false; break; }
         acc_phase ^= 1u;
         tc_fence_after_sync();
+        const uint32_t t_acc = t_row + (uint32_t)((l & 1) * p.acc_stride);
         if (l < L - 1) {
           const float* bias_l = p.bias[l] ? p.bias[l] + pofs : nullptr;
-          if (p.is_bf16) fused_hidden<true>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm);
-          else fused_hidden<false>(t_row, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm);
-          // generic-proxy writes of the activation tile must be visible to the MMA's async-proxy reads
-          fence_proxy_async_smem();
-        } else if (half == 0) {
-          const long long row = (long long)tile * 128 + row_in_tile;
-          if (p.n_pad[l] > 32) fused_head<64>(h, head_bias, out_m, t_row, row, p.batch);
-          else if (p.n_pad[l] > 16) fused_head<32>(h, head_bias, out_m, t_row, row, p.batch);
-          else fused_head<16>(h, head_bias, out_m, t_row, row, p.batch);
+          if (p.is_bf16) fused_hidden<true>(t_acc, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm, smem_u32(&bar_chunk[0]));
+          else fused_hidden<false>(t_acc, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm, smem_u32(&bar_chunk[0]));
+        } else {
+          if (half == 0) {
+            const long long row = (long long)tile * 128 + row_in_tile;
+            if (p.n_pad[l] > 32) fused_head<64>(h, head_bias, out_m, t_acc, row, p.batch);
+            else if (p.n_pad[l] > 16) fused_head<32>(h, head_bias, out_m, t_acc, row, p.batch);
+            else fused_head<16>(h, head_bias, out_m, t_acc, row, p.batch);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_item_done));
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_act_ready));
       }
       if (ok && p.tile_counters && half == 0) {
         // Decision tail (ml/models.spi:51-76).  The four head warps publish their rows of this member, count
@@ -496,8 +517,9 @@ static int fused_launch(const char* who, int n_layers, const int* sizes, int bat
   p.x_chunks = (uint32_t)p.k_chunks[0];
   p.act_offset = p.x_chunks * FM_CHUNK_BYTES;
   p.w_offset = p.act_offset + max_act_chunks * FM_CHUNK_BYTES;
-  p.tmem_cols = 32;
-  while (p.tmem_cols < max_n) p.tmem_cols <<= 1;
+  p.acc_stride = 32;
+  while (p.acc_stride < max_n) p.acc_stride <<= 1;
+  p.tmem_cols = 2 * p.acc_stride;            // two accumulators (at most 2 x 256 columns)
   head.n = n_out;
   p.out = out; p.head = head; p.hidden_norm = hidden_norm ? 1 : 0;
   p.members = members;
