@@ -38,15 +38,21 @@
 namespace {
 
 constexpr int UG_BLOCK_M = 128;
-constexpr int UG_EPI_WARPS = 8;      // 4 or 8: one or two warps per TMEM lane quadrant
-constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;   // a warp takes every UG_EPI_STRIDE-th 32-column chunk
-constexpr int UG_THREADS = 64 + 32 * UG_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
+// Epilogue warps per CTA (template parameter EW of the kernel): 8 = two warps per TMEM lane quadrant, the
+// general form; 16 = four per quadrant, for 16-bit outputs of CTA-pair tiles whose K is so short that the
+// launch is all epilogue (the head layer's dgrad, K = 16: 277 -> 242 us at 262144 rows).  A warp takes
+// every (EW / 4)-th 32-column chunk and owns a staging slot of 32 KB / EW.  Measured: with a real main
+// loop (K = 1024) sixteen warps are 4 % SLOWER than eight although the drain alone is 10 % faster -- the
+// MMA-issuing thread shares its scheduler with twice as many busy warps and the tensor pipe waits for it.
+constexpr int UG_EPI_WARPS = 8;
+constexpr int UG_EPI_WARPS_MAX = 16;
+constexpr int ug_threads(int ew) { return 64 + 32 * ew; }   // producer warp, MMA warp, epilogue warps
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
 constexpr int UG_MAX_PEERS = 8;         // ranks whose copies of C one launch can add its tiles to
 constexpr int UG_HEAD_MAX_N = 64;       // widest row a fused head keeps in registers
 constexpr int UG_HEAD_MAX_TILE_N = 256; // widest row a fused head may belong to when a prefix mask confines it to UG_HEAD_MAX_N columns
-constexpr int UG_EPI_STAGING = UG_EPI_WARPS * 4096;  // one 32-row x 128-byte box per epilogue warp
+constexpr int UG_EPI_STAGING = UG_EPI_WARPS * 4096;  // one 32-row x 128-byte box per epilogue warp (8 warps), or 2 KB each (16)
 
 // Tensor maps of the output: m[0] is C itself; with peer_rows > 0, m[r] is rank r's copy of C (the
 // same matrix in that rank's memory) and a CTA adds its rows to the copy of the rank that owns them.
@@ -95,6 +101,7 @@ struct UmmaGemmParams {
   int wide;            // 1: 16-bit output boxes span two chunks (64 columns, 128-byte rows)
   uint32_t epi_offset; // byte offset of the epilogue staging area from the stage base
   SbRowHead head;      // the row head, when epi holds a head flag
+  int epi_warps;       // 8 or 16 epilogue warps (the kernel instance launched)
   int reduce_add;      // 1: tiles are added to C through TMA reduce-add stores (split-K into one matrix, peer copies)
   int peer_rows;       // > 0: rows [r * peer_rows, (r + 1) * peer_rows) of C are added to rank r's copy (out map r)
 };
@@ -296,7 +303,7 @@ __shared__ __align__(16) float g_bias_spread[8][32];
 //   MODE = -1 : run-time flags, no second tile read;
 //   MODE = -2 : run-time flags plus the two features that read a second tile
 //               through the box (beta != 0, gate by the activation tile).
-template <typename OutT, bool ROUND_TF32, int MODE, bool WIDE = false>
+template <typename OutT, bool ROUND_TF32, int MODE, bool WIDE = false, int EW = UG_EPI_WARPS>
 __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, uint32_t gate, int split,
                                                     int row0_warp, int col0, uint32_t sbuf,
                                                     uint32_t bias_smem, int lane, int e) {
@@ -326,7 +333,12 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] *= alpha;
   }
-  if (has_bias) {
+  if (has_bias && EW == 16) {
+    // Lane j holds bias[col0 + j]; every lane needs all 32.  With sixteen epilogue warps there is no
+    // shared memory left for a spread buffer per warp: the values go round by shuffles.
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
+  } else if (has_bias) {
     // Lane j holds bias[col0 + j]; every lane needs all 32: spread them through
     // 128 bytes of shared memory and read them back as broadcasts.
     if (WIDE && e == 1) __syncwarp();   // every lane has read the first chunk's values (no other warp-wide sync lies between)
@@ -361,7 +373,7 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
     // so the warp's 4 KB slot holds two that alternate and only the store before last is awaited.
     if (!wide || e == 0) {
       if (lane == 0) {
-        if (sizeof(OutT) == 2 && !wide) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+        if (sizeof(OutT) == 2 && !wide && EW == 8) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
       }
       __syncwarp();
     }
@@ -499,14 +511,14 @@ __device__ __forceinline__ void direct_chunk16(float* v, long long row, int col0
 
 // Chunks that cannot take the coalesced path, from chunk `c` on: per-thread stores, 16 columns at
 // a time.  A function of its own so that its registers do not add to the fast path's.
-template <typename OutT, bool ROUND_TF32>
+template <typename OutT, bool ROUND_TF32, int EW>
 __device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0, int split, int c) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)row0_warp + lane;
   const bool row_ok = row < g_epi.M;
   const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
-  for (; c < nchunks; c += UG_EPI_STRIDE) {
+  for (; c < nchunks; c += EW / 4) {
     const int w = min(32, block_n - c * 32);
     for (int h = 0; h < w; h += 16) {
       uint32_t raw[16];
@@ -525,14 +537,16 @@ __device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0
 // for the accumulator).  Out of line, one instance per output type and mode; it
 // must not spill: with the L1 carved out as shared memory a spilled register
 // costs an L2 round trip.  Returns false when the wait for the accumulator expired.
-template <typename OutT, bool ROUND_TF32, int MODE>
+template <typename OutT, bool ROUND_TF32, int MODE, int EW>
 __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0, int split, uint32_t bar_full,
                                            uint32_t parity) {
+  static_assert(EW == 8 || (EW == 16 && sizeof(OutT) == 2), "sixteen epilogue warps: 2 KB staging slots, 16-bit outputs only");
+  constexpr int STRIDE = EW / 4;
   const int lane = threadIdx.x & 31;
   const int ewarp = (int)(threadIdx.x >> 5) - 2;
   const int half = ewarp >> 2;
-  const uint32_t sbuf = g_epi.box_base + (uint32_t)ewarp * 4096u;
-  const uint32_t bias_smem = smem_u32(&g_bias_spread[ewarp][0]);
+  const uint32_t sbuf = g_epi.box_base + (uint32_t)ewarp * (EW == 8 ? 4096u : 2048u);
+  const uint32_t bias_smem = smem_u32(&g_bias_spread[ewarp & 7][0]);
   const bool has_bias = MODE >= 0 ? (MODE & 1) != 0 : g_epi.has_bias != 0;
   const bool want_gate_in = MODE >= 0 ? (MODE & 8) != 0 : g_epi.gate_in != nullptr;
   const bool want_gate_out = MODE >= 0 ? (MODE & 4) != 0 : g_epi.gate_out != nullptr;
@@ -579,9 +593,9 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
       for (int j = 0; j < 32; ++j) sumsq = fmaf(__uint_as_float(raw_a[j]), __uint_as_float(raw_a[j]), sumsq);
     }
   }
-  for (; c < nfull; c += UG_EPI_STRIDE) {
+  for (; c < nfull; c += STRIDE) {
     tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
-    fetch(c + UG_EPI_STRIDE, bias_nxt, gate_nxt);    // in flight while this chunk is finished
+    fetch(c + STRIDE, bias_nxt, gate_nxt);    // in flight while this chunk is finished
     tmem_ld_wait();
     if (ln_l2) {
 #pragma unroll
@@ -589,9 +603,9 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
     }
     const int col0 = n0 + c * 32;
     if (rows_live && col0 < N) {
-      const uint32_t box = sbuf + ((MODE != -2 && sizeof(OutT) == 2 && g_epi.tma_c) ? box_sel : 0u);
+      const uint32_t box = sbuf + ((EW == 8 && MODE != -2 && sizeof(OutT) == 2 && g_epi.tma_c) ? box_sel : 0u);
       box_sel ^= 2048u;
-      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
+      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE, false, EW>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
                                                                      split, row0_warp, col0, box, bias_smem, lane, 0);
       if (want_gate_out && row_ok) g_epi.gate_out[(col0 >> 5) * gate_pitch + gate_row] = signs;
       if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_a), col0, lane);
@@ -601,7 +615,7 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
   }
   // What is left for this warp: a 16-column tail chunk, or every chunk when C
   // cannot take row-contiguous 16-byte stores.
-  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32>(t_row, row0_warp, n0, split, c);
+  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32, EW>(t_row, row0_warp, n0, split, c);
   return true;
 }
 
@@ -652,6 +666,7 @@ __device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, i
   // finished.
   constexpr bool BOTH_AT_ONCE = MODE >= 0 && (MODE & 16) == 0;
   uint32_t raw_a[32], raw_b[32];
+  constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;
   for (; c < nchunks; c += 2 * UG_EPI_STRIDE) {
     tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
     if (BOTH_AT_ONCE) tmem_ld32(t_row + (uint32_t)(c * 32 + 32), raw_b);
@@ -738,8 +753,8 @@ constexpr int EPI_GATE_MASK = SB_EPI_RELU_MASK_OUT | SB_EPI_RELU_GRAD_MASK;
 //   128 accumulator rows and arrives on the leader's tmem_empty barrier.  Halving
 //   the B bytes each SM stages is what lifts the shared-memory ceiling of the
 //   single-CTA form.
-template <bool PAIR, bool TF32>
-__global__ void __launch_bounds__(UG_THREADS, 1)
+template <bool PAIR, bool TF32, int EW = UG_EPI_WARPS>
+__global__ void __launch_bounds__(ug_threads(EW), 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ UmmaOutMaps out_maps,
@@ -773,7 +788,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tmem_full[a]), 1);
-      mbar_init(smem_u32(&bar_tmem_empty[a]), PAIR ? 2 * UG_EPI_WARPS : UG_EPI_WARPS);
+      mbar_init(smem_u32(&bar_tmem_empty[a]), PAIR ? 2 * EW : EW);
     }
     g_abort_flag = 0;
     g_epi.c = p.C; g_epi.aux = p.aux_in; g_epi.bias = p.bias;
@@ -978,26 +993,33 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row0_warp = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M + quad * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
       const uint32_t full_bar = smem_u32(&bar_tmem_full[acc]);
-      if (head) {
-        if (!mbar_wait(full_bar, acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
-        tc_fence_after_sync();
-        if (half == 0) {               // a thread finishes a whole head row: the second warp of the quadrant idles
-          if (p.block_n > 32) epilogue_head<64>(t_row, (long long)row0_warp + lane, p.M);
-          else if (p.block_n > 16) epilogue_head<32>(t_row, (long long)row0_warp + lane, p.M);
-          else epilogue_head<16>(t_row, (long long)row0_warp + lane, p.M);
+      if (EW == 8 && head) {           // row heads always run on the eight-warp instance
+        if constexpr (EW == 8) {
+          if (!mbar_wait(full_bar, acc_phase, abortp, SB_SITE_EPI_TMEM_FULL)) break;
+          tc_fence_after_sync();
+          if (half == 0) {               // a thread finishes a whole head row: the second warp of the quadrant idles
+            if (p.block_n > 32) epilogue_head<64>(t_row, (long long)row0_warp + lane, p.M);
+            else if (p.block_n > 16) epilogue_head<32>(t_row, (long long)row0_warp + lane, p.M);
+            else epilogue_head<16>(t_row, (long long)row0_warp + lane, p.M);
+          }
         }
       } else {
         const int n0 = n_blk * p.block_n;
         bool ok;
-#define SB_EPI_CALL(T, R, G) epilogue_tile<T, R, G>(t_row, row0_warp, n0, split, full_bar, acc_phase)
+#define SB_EPI_CALL(T, R, G) epilogue_tile<T, R, G, EW>(t_row, row0_warp, n0, split, full_bar, acc_phase)
 #define SB_EPI_WIDE(T, G) epilogue_tile_wide<T, (G) == -2 ? -1 : (G)>(t_row, row0_warp, n0, split, full_bar, acc_phase)
 #define SB_EPI_BY_TYPE(G)                                                        \
   do {                                                                           \
-    if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, G);                \
-    else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, G);           \
-    else if (p.out_dtype == SB_BF16)                                             \
-      ok = (p.wide && (G) != -2) ? SB_EPI_WIDE(__nv_bfloat16, G) : SB_EPI_CALL(__nv_bfloat16, false, G); \
-    else ok = (p.wide && (G) != -2) ? SB_EPI_WIDE(__half, G) : SB_EPI_CALL(__half, false, G);            \
+    if constexpr (EW == 16) {            /* 16-bit outputs only, one 32 x 32 box per chunk */ \
+      if (p.out_dtype == SB_BF16) ok = SB_EPI_CALL(__nv_bfloat16, false, G);     \
+      else ok = SB_EPI_CALL(__half, false, G);                                   \
+    } else {                                                                     \
+      if (p.out_dtype == SB_F32) ok = SB_EPI_CALL(float, false, G);              \
+      else if (p.out_dtype == SB_TF32) ok = SB_EPI_CALL(float, true, G);         \
+      else if (p.out_dtype == SB_BF16)                                           \
+        ok = (p.wide && (G) != -2) ? SB_EPI_WIDE(__nv_bfloat16, G) : SB_EPI_CALL(__nv_bfloat16, false, G); \
+      else ok = (p.wide && (G) != -2) ? SB_EPI_WIDE(__half, G) : SB_EPI_CALL(__half, false, G);            \
+    }                                                                            \
   } while (0)
         switch (epi_mode) {
           case 0: SB_EPI_BY_TYPE(0); break;        // plain: standalone GEMMs, wgrad partials
@@ -1105,6 +1127,16 @@ bool sb_pair_mode_enabled() {
   if (v < 0) {
     const char* e = getenv("SB_NO_PAIR");
     v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// SB_EPI_WARPS=8 in the environment keeps every GEMM on eight epilogue warps.
+bool epi16_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SB_EPI_WARPS");
+    v = (e && atoi(e) == 8) ? 0 : 1;
   }
   return v == 1;
 }
@@ -1345,7 +1377,11 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
   p.tma_store = 0;
   if (p.coalesced && beta == 0.0f && !(epi & SB_EPI_RELU_GRAD) && (p.splits == 1 || p.reduce_add || M % 32 == 0)) {
     const int cdt = es_out == 4 ? SB_F32 : out_dtype;
-    p.wide = (es_out == 2 && p.block_n % 64 == 0 && !(epi & SB_EPI_LN_L2)) ? 1 : 0;
+    // Sixteen epilogue warps: CTA-pair tiles with a 16-bit output and next to no main loop; one 32 x 32
+    // box per chunk, no 64-column boxes.
+    p.epi_warps = (p.pair && es_out == 2 && !(epi & EPI_HEAD_MASK) && p.block_n % 32 == 0 && p.k_blocks <= 2 &&
+                   epi16_enabled()) ? 16 : 8;
+    p.wide = (es_out == 2 && p.block_n % 64 == 0 && !(epi & SB_EPI_LN_L2) && p.epi_warps == 8) ? 1 : 0;
     for (int r = 0; r < (to_peers ? peer_out->n : 1); ++r) {
       rc = make_tmap_2d(&tc.m[r], to_peers ? peer_out->c[r] : C, cdt, p.reduce_add ? (long long)M : (long long)M * p.splits, N,
                         32, p.wide ? 64 : 32, (es_out == 4 || p.wide) ? SWZ_128 : SWZ_64);
@@ -1353,6 +1389,7 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     }
     p.tma_store = 1;
   }
+  if (p.epi_warps == 0) p.epi_warps = 8;
   if (p.reduce_add && !p.tma_store)
     return sb_fail(SB_ERR_UNSUPPORTED, "internal: split-K accumulation was chosen for a C that cannot take TMA stores");
   const size_t smem = umma_dyn_smem(p);
@@ -1364,18 +1401,20 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
+    SB_CUDA(cudaFuncSetAttribute(umma_gemm_kernel<true, false, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_LIMIT - 2048));
     attr_set[dev].store(true, std::memory_order_release);
   }
   sb_prof_before(stream);
   if (!p.pair) {
     const int grid = min(p.num_work, cached_sm_count());
-    if (p.kind_tf32) SB_CUDA(sb_launch(umma_gemm_kernel<false, true>, dim3(grid), dim3(UG_THREADS), smem, stream, 1, ta, tb, tc, p));
-    else SB_CUDA(sb_launch(umma_gemm_kernel<false, false>, dim3(grid), dim3(UG_THREADS), smem, stream, 1, ta, tb, tc, p));
+    if (p.kind_tf32) SB_CUDA(sb_launch(umma_gemm_kernel<false, true>, dim3(grid), dim3(ug_threads(8)), smem, stream, 1, ta, tb, tc, p));
+    else SB_CUDA(sb_launch(umma_gemm_kernel<false, false>, dim3(grid), dim3(ug_threads(8)), smem, stream, 1, ta, tb, tc, p));
   } else {
     // One cluster of two CTAs per worker; the two CTAs of a cluster share a TPC.
     const int workers = min(p.num_work, cached_sm_count() / 2);
-    if (p.kind_tf32) SB_CUDA(sb_launch(umma_gemm_kernel<true, true>, dim3(2 * workers), dim3(UG_THREADS), smem, stream, 2, ta, tb, tc, p));
-    else SB_CUDA(sb_launch(umma_gemm_kernel<true, false>, dim3(2 * workers), dim3(UG_THREADS), smem, stream, 2, ta, tb, tc, p));
+    if (p.kind_tf32) SB_CUDA(sb_launch(umma_gemm_kernel<true, true>, dim3(2 * workers), dim3(ug_threads(8)), smem, stream, 2, ta, tb, tc, p));
+    else if (p.epi_warps == 16) SB_CUDA(sb_launch(umma_gemm_kernel<true, false, 16>, dim3(2 * workers), dim3(ug_threads(16)), smem, stream, 2, ta, tb, tc, p));
+    else SB_CUDA(sb_launch(umma_gemm_kernel<true, false>, dim3(2 * workers), dim3(ug_threads(8)), smem, stream, 2, ta, tb, tc, p));
   }
   sb_prof_after(stream, 2.0 * M * N * K);
   SB_COUNT_LAUNCH();
