@@ -305,6 +305,19 @@ int sb_mlp_forward_fused_ensemble(int n_layers, const int* sizes, int batch, int
                                   const void* x, const void* w_compute, const float* params, int head,
                                   const uint8_t* mask, float* out, int32_t* actions, void* stream);
 
+/* The training form of the fused forward (one net): the same single launch, and the hidden
+ * activations (activations[l]: [batch, sizes[l+1]] in the storage type) and their ReLU sign words
+ * (relu_bits[l]: uint32 [sizes[l+1]/32, batch], may be NULL) are also written to global memory, in the
+ * layout sb_mlp_forward leaves them, so that sb_mlp_backward can follow.  The activation tile in
+ * shared memory already has the layout of a TMA box and leaves through one TMA store per 64-column
+ * chunk.  sb_mlp_fused_supported tells (1 / 0) whether a net is within the fused kernel's limits;
+ * sb_mlp_train_step takes this path by itself when it is. */
+int sb_mlp_fused_supported(int n_layers, const int* sizes, int in_dtype);
+int sb_mlp_forward_fused_train(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                               const void* w_compute, const float* params, void* const* activations,
+                               void* const* relu_bits, int head, const uint8_t* mask, float* out,
+                               int32_t* actions, void* stream);
+
 /* The fused ensemble forward with the head given as an sb_head_spec and the reference's other
  * graph pieces: hidden_norm = 1 puts ln_l2 (x / sum(x^2) over the row, ml/primitives.spi:701-703)
  * before every ReLU as the reference's nets do (ml/layers.spi:594-603; then params must be NULL:

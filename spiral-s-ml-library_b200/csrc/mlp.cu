@@ -656,8 +656,14 @@ int sb_mlp_train_step(int n_layers, const int* sizes, int batch, int in_dtype, c
                       const uint8_t* mask,
                       const float* target, float* probs, float* grads, int with_bias, float lr,
                       void* scratch, size_t scratch_bytes, float* loss, void* stream) {
-  int rc = sb_mlp_forward(n_layers, sizes, batch, in_dtype, x, w_compute, with_bias ? params : nullptr,
-                          activations, relu_bits, SB_EPI_MASKED_SOFTMAX, mask, probs, nullptr, stream);
+  // Narrow nets run the whole forward pass as one fused launch that also writes what backward needs.
+  int rc;
+  if (sb_mlp_fused_supported(n_layers, sizes, in_dtype) && batch > 0)
+    rc = sb_mlp_forward_fused_train(n_layers, sizes, batch, in_dtype, x, w_compute, with_bias ? params : nullptr,
+                                    activations, relu_bits, SB_EPI_MASKED_SOFTMAX, mask, probs, nullptr, stream);
+  else
+    rc = sb_mlp_forward(n_layers, sizes, batch, in_dtype, x, w_compute, with_bias ? params : nullptr,
+                        activations, relu_bits, SB_EPI_MASKED_SOFTMAX, mask, probs, nullptr, stream);
   if (rc != SB_OK) return rc;
   rc = sb_mlp_backward(n_layers, sizes, batch, batch > 0 ? 1.0f / (float)batch : 0.f, in_dtype, x, w_compute,
                        activations, relu_bits, probs, mask, target, grads, with_bias, scratch, scratch_bytes, loss,

@@ -42,6 +42,7 @@ constexpr uint32_t FM_CHUNK_BYTES = 128u * 128u;       // activation chunk: 128 
 struct FusedMaps {
   CUtensorMap x;                      // [batch, in] box {64, 128}
   CUtensorMap w[FM_MAX_LAYERS];       // W_l [members, out_l, in_l] box {64, rows_l, 1}
+  CUtensorMap act[FM_MAX_LAYERS];     // training forward: hidden activations of layer l, [batch, width_l] box {64, 128}
 };
 
 struct FusedParams {
@@ -67,6 +68,10 @@ struct FusedParams {
   float* out;
   SbRowHead head;                     // n, flags, prefix, mask, seed, ...; argmax_out / sample_out are [members, batch]
   int hidden_norm;                    // 1: x / sum(x^2) over the row before every ReLU
+  // training forward: the hidden activations and their ReLU sign words are also written to global
+  // memory for the backward pass (single net only)
+  int store_acts;
+  uint32_t* bits[FM_MAX_LAYERS];      // uint32 [width_l / 32, batch] per hidden layer, or null
   // decision tail (null counters = off)
   int members;
   int* tile_counters;                 // int32 [num_tiles], zero between calls
@@ -111,7 +116,7 @@ __device__ __noinline__ void fused_head(const SbRowHead& h, const float* bias, f
 template <bool BF16>
 __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const float* bias, uint32_t act_base,
                                           uint32_t bias_smem, int row_in_tile, int lane, int half, int norm,
-                                          uint32_t chunk_bar0) {
+                                          uint32_t chunk_bar0, uint32_t* bits_out, long long row, int batch) {
   const int nchunks = n_cols >> 5;
   // Row normalisation (local_ln_l2, ml/primitives.spi:701-703; no bias in this mode): a first pass
   // over the whole accumulator row sums the squares; both warps of a quadrant do it for themselves.
@@ -151,6 +156,14 @@ __device__ __noinline__ void fused_hidden(uint32_t t_row, int n_cols, const floa
         v[4 * q + 3] += __uint_as_float(b.w);
       }
       __syncwarp();
+    }
+    if (bits_out) {
+      // ReLU sign word of this row and chunk (bit j = value j > 0), stored [chunk, row]: the 32 rows of
+      // the warp are 32 consecutive words.  The backward pass gates its gradients by these words.
+      uint32_t signs = 0u;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) signs |= (v[j] > 0.f ? 1u : 0u) << j;
+      if (row < batch) bits_out[(long long)c * batch + row] = signs;
     }
     const int col0 = c * 32;
     const uint32_t chunk_base = act_base + (uint32_t)(col0 >> 6) * FM_CHUNK_BYTES + (uint32_t)row_in_tile * 128u;
@@ -283,6 +296,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
       bool ok = true;
       const uint32_t hi = (uint32_t)(umma_smem_desc(0u, 16u, 1024u, 2u) >> 32);
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        const int tile = item % p.num_tiles;
         for (int l = 0; ok && l < L; ++l) {
           uint32_t a_base;
           if (l == 0) {
@@ -304,6 +318,12 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
               if (!mbar_wait(smem_u32(&bar_chunk[c]), (chunk_phase >> c) & 1u, abortp, SB_SITE_MLP_ACT)) { ok = false; break; }
               chunk_phase ^= 1u << c;
               tc_fence_after_sync();
+              // Training forward: the delivered chunk of the previous layer's output also leaves for global
+              // memory; the tile in shared memory already has the layout of a TMA box.
+              if (p.store_acts) {
+                tma_store_2d(&maps.act[l - 1], a_base + (uint32_t)c * FM_CHUNK_BYTES, c * 64, tile * 128);
+                bulk_commit_group();
+              }
             }
             if (!mbar_wait(smem_u32(&bar_w_full[stage]), w_phase, abortp, SB_SITE_MLP_WEIGHTS)) { ok = false; break; }
             tc_fence_after_sync();
@@ -322,6 +342,8 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
           }
           if (!ok) break;
           if (l == 0) tc_commit(smem_u32(&bar_x_empty));     // the input tile may be refilled
+          // This layer's epilogue overwrites the activation tile: the stores of its chunks must have read it.
+          if (p.store_acts && l > 0) bulk_wait_group_read<0>();
           tc_commit(smem_u32(&bar_acc_full));
         }
         // The next tile's layers overwrite the accumulators and the activation tile: wait until the head
@@ -362,8 +384,9 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
         const uint32_t t_acc = t_row + (uint32_t)((l & 1) * p.acc_stride);
         if (l < L - 1) {
           const float* bias_l = p.bias[l] ? p.bias[l] + pofs : nullptr;
-          if (p.is_bf16) fused_hidden<true>(t_acc, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm, smem_u32(&bar_chunk[0]));
-          else fused_hidden<false>(t_acc, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm, smem_u32(&bar_chunk[0]));
+          const long long grow = (long long)tile * 128 + row_in_tile;
+          if (p.is_bf16) fused_hidden<true>(t_acc, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm, smem_u32(&bar_chunk[0]), p.bits[l], grow, p.batch);
+          else fused_hidden<false>(t_acc, p.n_pad[l], bias_l, act_base, bias_smem, row_in_tile, lane, half, p.hidden_norm, smem_u32(&bar_chunk[0]), p.bits[l], grow, p.batch);
         } else {
           if (half == 0) {
             const long long row = (long long)tile * 128 + row_in_tile;
@@ -406,6 +429,7 @@ mlp_fused_kernel(const __grid_constant__ FusedMaps maps, const __grid_constant__
     }
   }
 
+  if (warp == 1 && lane == 0 && p.store_acts) bulk_wait_group<0>();
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
@@ -456,7 +480,8 @@ struct FusedDecide {
 // [members, batch].  `who` names the entry point in error texts.
 static int fused_launch(const char* who, int n_layers, const int* sizes, int batch, int members, int in_dtype,
                         const void* x, const void* w_compute, const float* params, SbRowHead head, int hidden_norm,
-                        float* out, const FusedDecide* decide, void* stream) {
+                        float* out, const FusedDecide* decide, void* stream, void* const* acts_out = nullptr,
+                        void* const* bits_out = nullptr) {
   if (members < 1 || members > 1024) return sb_fail(SB_ERR_BAD_ARG, "%s: 1..1024 ensemble members", who);
   if (n_layers < 1 || n_layers > FM_MAX_LAYERS) return sb_fail(SB_ERR_UNSUPPORTED, "%s: 1..%d layers", who, FM_MAX_LAYERS);
   if (!sizes) return sb_fail(SB_ERR_BAD_ARG, "%s: sizes is null", who);
@@ -512,6 +537,18 @@ static int fused_launch(const char* who, int n_layers, const int* sizes, int bat
     if (rc != SB_OK) return rc;
   }
   for (int l = n_layers; l < FM_MAX_LAYERS; ++l) maps.w[l] = maps.w[0];
+  if (acts_out) {
+    if (members != 1) return sb_fail(SB_ERR_UNSUPPORTED, "%s: the training forward runs one net", who);
+    for (int l = 0; l + 1 < n_layers; ++l) {
+      if (!acts_out[l] || (reinterpret_cast<uintptr_t>(acts_out[l]) & 15))
+        return sb_fail(SB_ERR_BAD_ARG, "%s: activations[%d] is null or not 16-byte aligned", who, l);
+      rc = make_tmap_2d(&maps.act[l], acts_out[l], in_dtype, batch, sizes[l + 1], 128, 64, SWZ_128);
+      if (rc != SB_OK) return rc;
+      p.bits[l] = (bits_out && bits_out[l]) ? reinterpret_cast<uint32_t*>(bits_out[l]) : nullptr;
+    }
+    p.store_acts = 1;
+  }
+  for (int l = acts_out ? (n_layers > 1 ? n_layers - 1 : 0) : 0; l < FM_MAX_LAYERS; ++l) maps.act[l] = maps.w[0];
   rc = make_tmap_2d(&maps.x, x, in_dtype, batch, sizes[0], 128, 64, SWZ_128);
   if (rc != SB_OK) return rc;
   p.x_chunks = (uint32_t)p.k_chunks[0];
@@ -620,4 +657,46 @@ extern "C" int sb_policy_decide(const sb_decide_args* a, void* stream) {
   d.prob_selected = a->sampling_prob_selected; d.prob_ensemble = a->sampling_prob_ensemble;
   return fused_launch("sb_policy_decide", a->n_layers, a->sizes, (int)a->rows, a->members, a->in_dtype, a->x, a->w_compute,
                       a->params, h, a->hidden_norm, a->output_probs, &d, stream);
+}
+
+// True when the fused kernel can run this net (the checks of fused_launch that depend on the shape only).
+static bool fused_shape_ok(int n_layers, const int* sizes, int in_dtype) {
+  if (n_layers < 1 || n_layers > FM_MAX_LAYERS || !sizes) return false;
+  if (in_dtype != SB_F16 && in_dtype != SB_BF16) return false;
+  if (sizes[0] < 8 || sizes[0] > 512 || sizes[0] % 8) return false;
+  uint32_t max_act_chunks = 1;
+  int max_n = 32;
+  for (int i = 1; i < n_layers; ++i) {
+    if (sizes[i] < 64 || sizes[i] > 256 || sizes[i] % 64) return false;
+    if ((uint32_t)(sizes[i] / 64) > max_act_chunks) max_act_chunks = (uint32_t)(sizes[i] / 64);
+    if (sizes[i] > max_n) max_n = sizes[i];
+  }
+  const int n_out = sizes[n_layers];
+  if (n_out < 1 || n_out > 64) return false;
+  if ((n_out + 15) / 16 * 16 > max_n) max_n = (n_out + 15) / 16 * 16;
+  const size_t stage = ((size_t)max_n * 128 + 1023) / 1024 * 1024;
+  const size_t smem = (size_t)((sizes[0] + 63) / 64 + max_act_chunks) * FM_CHUNK_BYTES + FM_W_STAGES * stage + 1024;
+  return smem <= 225 * 1024;
+}
+
+extern "C" int sb_mlp_fused_supported(int n_layers, const int* sizes, int in_dtype) {
+  return fused_shape_ok(n_layers, sizes, in_dtype) ? 1 : 0;
+}
+
+extern "C" int sb_mlp_forward_fused_train(int n_layers, const int* sizes, int batch, int in_dtype, const void* x,
+                                          const void* w_compute, const float* params, void* const* activations,
+                                          void* const* relu_bits, int head, const uint8_t* mask, float* out,
+                                          int32_t* actions, void* stream) {
+  if (head & ~(SB_EPI_MASKED_SOFTMAX | SB_EPI_REGRET_MATCHING | SB_EPI_ARGMAX))
+    return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused_train: head may hold only row-head flags");
+  if (n_layers > 1 && !activations) return sb_fail(SB_ERR_BAD_ARG, "sb_mlp_forward_fused_train: activations is null");
+  for (int l = 0; l + 1 < n_layers; ++l)
+    if (relu_bits && relu_bits[l] && sizes && sizes[l + 1] % 32 != 0)
+      return sb_fail(SB_ERR_UNSUPPORTED, "sb_mlp_forward_fused_train: sign words need widths that are multiples of 32");
+  SbRowHead h;
+  memset(&h, 0, sizeof(h));
+  h.flags = head; h.prefix = -1; h.mask = mask; h.argmax_out = actions;
+  static void* const no_acts[1] = {nullptr};
+  return fused_launch("sb_mlp_forward_fused_train", n_layers, sizes, batch, 1, in_dtype, x, w_compute, params, h, 0, out,
+                      nullptr, stream, n_layers > 1 ? activations : no_acts, relu_bits);
 }

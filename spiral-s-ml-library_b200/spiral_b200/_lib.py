@@ -127,6 +127,8 @@ SIGNATURES = {
     "sb_mlp_forward": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused_ensemble": (_I, [_I, _IP, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "sb_mlp_fused_supported": (_I, [_I, _IP, _I]),
+    "sb_mlp_forward_fused_train": (_I, [_I, _IP, _I, _I, _P, _P, _P, _PP, _PP, _I, _P, _P, _P, _P]),
     "sb_mlp_forward_fused_head": (_I, [_I, _IP, _I, _I, _I, _P, _P, _P, _I, POINTER(HeadSpec), _P, _P]),
     "sb_policy_decide": (_I, [POINTER(DecideArgs), _P]),
     "sb_mlp_forward_static": (_I, [_I, _IP, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),

@@ -129,14 +129,29 @@ class PolicyMLP:
         return out
 
     # -- execution -----------------------------------------------------------
-    def forward(self, x, mask=None, head_flags=None, stream=None):
-        """probs <- head(MLP(x)); returns the probs DeviceArray (and fills actions for argmax heads)."""
+    def forward(self, x, mask=None, head_flags=None, stream=None, fused=None):
+        """probs <- head(MLP(x)); returns the probs DeviceArray (and fills actions for argmax heads).
+        A net built for training whose shape the fused kernel takes runs the whole pass as one launch that
+        also writes the activations and sign words backward needs (``fused=False``: one GEMM per layer)."""
         flags = self.head_flags if head_flags is None else head_flags
+        if fused is None:
+            fused = self.training and self.batch > 0 and self._fused_ok()
+        if fused:
+            _lib.call("sb_mlp_forward_fused_train", self.n_layers, self._sizes_c, self.batch,
+                      _lib.DTYPE_CODES[self.in_dtype], device_ptr(x), self.w_compute.ptr,
+                      self.params.ptr if self.with_bias else None, self._acts_c, self._bits_c, flags, device_ptr(mask),
+                      self.probs.ptr, device_ptr(self.actions) if flags & _lib.EPI_ARGMAX else None, stream_ptr(stream))
+            return self.probs
         _lib.call("sb_mlp_forward", self.n_layers, self._sizes_c, self.batch, _lib.DTYPE_CODES[self.in_dtype],
                   device_ptr(x), self.w_compute.ptr, self.params.ptr if self.with_bias else None, self._acts_c,
                   self._bits_c, flags, device_ptr(mask), self.probs.ptr, device_ptr(self.actions) if flags & _lib.EPI_ARGMAX else None,
                   stream_ptr(stream))
         return self.probs
+
+    def _fused_ok(self):
+        if self.in_dtype not in ("bf16", "f16"):
+            return False
+        return bool(_lib.load().sb_mlp_fused_supported(self.n_layers, self._sizes_c, _lib.DTYPE_CODES[self.in_dtype]))
 
     def forward_fused(self, x, mask=None, head_flags=None, stream=None):
         """Forward pass as one persistent kernel (narrow nets: 16-bit class, hidden widths multiples of

@@ -320,3 +320,48 @@ def test_layer_graph_binarize_head(gpu):
     ref = so.matmul(False, True, 1.0, x, w, 0.0, None, in_dtype="tf32")
     decided = np.all(np.abs(ref) > 5e-3, axis=1)              # rows whose signs do not hinge on TF32 rounding
     np.testing.assert_array_equal(got[decided], so.binarize(ref, 1000003)[decided])
+
+
+@pytest.mark.parametrize("in_dtype,batch,sizes", [("bf16", 3000, [32, 256, 256, 256, 3]), ("f16", 65536, [32, 256, 256, 256, 3]),
+                                                  ("bf16", 1000, [64, 128, 64, 10])])
+def test_fused_training_forward_leaves_what_backward_needs(gpu, in_dtype, batch, sizes):
+    """The training forward of a narrow net as ONE launch (sb_mlp_forward_fused_train): hidden activations and
+    ReLU sign words land in global memory as the layer-wise forward leaves them, and the backward pass that
+    follows gives the oracle's gradients."""
+    net, ws, bs = build(gpu, sizes, batch, in_dtype, 31, training=True, bias_scale=0.05)
+    if sizes[0] == 32:
+        x, mask = so.leduc_inputs(31, batch)
+    else:
+        g = so.rng(31)
+        x = g.random((batch, sizes[0]), dtype=np.float32)
+        mask = (g.random((batch, sizes[-1])) < 0.6).astype(np.uint8)
+        mask[:, 0] = 1
+    target = so.random_target(32, mask)
+    dx, dm, dt = gpu.to_storage(x, in_dtype), gpu.DeviceArray.from_numpy(mask), gpu.DeviceArray.from_numpy(target)
+    net.forward(dx, dm, head_flags=8, fused=False)
+    acts_ref = [a.numpy().copy() for a in net.activations]
+    bits_ref = [b.numpy().copy() for b in net.relu_bits]
+    probs_ref = net.probs.numpy().copy()
+    for buf in net.activations + net.relu_bits + [net.probs]:
+        buf.fill_zero()
+    l0 = gpu.launch_count()
+    net.forward(dx, dm, head_flags=8)              # a training net of this shape takes the fused path by itself
+    assert gpu.launch_count() - l0 == 1
+    for i, a in enumerate(net.activations):
+        got = a.numpy()
+        assert so.rel_frobenius(got, acts_ref[i]) <= 1e-5, "activations of layer %d" % i
+        words = net.relu_bits[i].numpy().view(np.uint32).reshape(sizes[i + 1] // 32, batch)
+        by_row = np.ascontiguousarray(words.T)
+        bits = np.unpackbits(by_row.view(np.uint8).reshape(batch, -1), axis=1, bitorder="little").astype(bool)
+        np.testing.assert_array_equal(bits, got > 0)
+        assert np.mean(words != bits_ref[i].view(np.uint32).reshape(words.shape)) < 1e-3
+    assert so.rel_frobenius(net.probs.numpy(), probs_ref) <= 1e-5
+    net.loss.fill_zero()
+    net.backward(dx, dm, dt)
+    got = net.split_flat(net.grads.numpy())
+    _, _, loss, want = so.mlp_train_step(x, [so.round_input(w, in_dtype) for w in ws], bs, mask, target, 0.0,
+                                         in_dtype=in_dtype, act_dtype=in_dtype)
+    assert abs(float(net.loss.numpy()[0]) - loss) <= 2e-3 * abs(loss)
+    for i, ((gw, gb), (ww, wb)) in enumerate(zip(got, want)):
+        assert so.rel_frobenius(gw, ww) <= TOL, "dW of layer %d" % i
+        assert so.rel_frobenius(gb, wb) <= 5e-3, "db of layer %d" % i
