@@ -353,7 +353,12 @@ def test_fused_training_forward_leaves_what_backward_needs(gpu, in_dtype, batch,
         words = net.relu_bits[i].numpy().view(np.uint32).reshape(sizes[i + 1] // 32, batch)
         by_row = np.ascontiguousarray(words.T)
         bits = np.unpackbits(by_row.view(np.uint8).reshape(batch, -1), axis=1, bitorder="little").astype(bool)
-        np.testing.assert_array_equal(bits, got > 0)
+        # The sign is taken from the fp32 value before it is rounded to the storage type, as the
+        # layer-wise kernel does: a positive value below the smallest fp16 subnormal is stored as 0
+        # with its bit set, nothing else may differ.
+        stored = got.astype(np.float32) > 0
+        assert not (stored & ~bits).any()
+        assert np.mean(bits & ~stored) < 1e-6
         assert np.mean(words != bits_ref[i].view(np.uint32).reshape(words.shape)) < 1e-3
     assert so.rel_frobenius(net.probs.numpy(), probs_ref) <= 1e-5
     net.loss.fill_zero()
