@@ -303,10 +303,10 @@ __shared__ __align__(16) float g_bias_spread[8][32];
 //   MODE = -1 : run-time flags, no second tile read;
 //   MODE = -2 : run-time flags plus the two features that read a second tile
 //               through the box (beta != 0, gate by the activation tile).
-template <typename OutT, bool ROUND_TF32, int MODE, bool WIDE = false, int EW = UG_EPI_WARPS>
+template <typename OutT, bool ROUND_TF32, int MODE, int EW = UG_EPI_WARPS>
 __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, uint32_t gate, int split,
                                                     int row0_warp, int col0, uint32_t sbuf,
-                                                    uint32_t bias_smem, int lane, int e) {
+                                                    uint32_t bias_smem, int lane) {
   constexpr int VEC = 16 / sizeof(OutT);      // elements per 16-byte piece
   constexpr int PIECES = 32 / VEC;            // 16-byte pieces per row of the box
   constexpr int ROWS_PER_INST = 32 / PIECES;
@@ -341,7 +341,6 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
   } else if (has_bias) {
     // Lane j holds bias[col0 + j]; every lane needs all 32: spread them through
     // 128 bytes of shared memory and read them back as broadcasts.
-    if (WIDE && e == 1) __syncwarp();   // every lane has read the first chunk's values (no other warp-wide sync lies between)
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(bias_smem + 4u * (uint32_t)lane), "f"(bias_lane) : "memory");
     __syncwarp();
 #pragma unroll
@@ -363,27 +362,18 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
     load_chunk_to_box<OutT>(reinterpret_cast<const OutT*>(g_epi.aux), g_epi.ldc, row0_warp, g_epi.M, col0, g_epi.N,
                             sbuf, lane);
   const bool tma_out = !GENERAL && g_epi.tma_c != nullptr;
-  // A wide box (16-bit output) is 32 rows x 64 columns with 128-byte rows in the 128-byte swizzle:
-  // chunk e = 0 / 1 of a column pair fills pieces 4e .. 4e+3 of every row and the pair leaves as one
-  // store of full 128-byte row segments.  A narrow 16-bit box is 32 x 32 (64-byte swizzle).
-  constexpr bool wide = WIDE;
-  static_assert(!WIDE || (!GENERAL && sizeof(OutT) == 2), "wide boxes: 16-bit output through TMA stores only");
+  // A 16-bit box here is 32 rows x 32 columns (64-byte swizzle).
   if (tma_out) {
-    // The store that last read this box must have finished reading it.  A narrow 16-bit box is 2 KB,
+    // The store that last read this box must have finished reading it.  A 16-bit box is 2 KB,
     // so the warp's 4 KB slot holds two that alternate and only the store before last is awaited.
-    if (!wide || e == 0) {
-      if (lane == 0) {
-        if (sizeof(OutT) == 2 && !wide && EW == 8) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
-      }
-      __syncwarp();
+    if (lane == 0) {
+      if (sizeof(OutT) == 2 && EW == 8) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
     }
+    __syncwarp();
   }
-  const uint32_t wide_row = sbuf + (uint32_t)lane * 128u;
-  const uint32_t wide_key = (uint32_t)(4 * e) ^ ((uint32_t)lane & 7u);   // (4e + q) ^ key == (4e ^ key) ^ q for q < 4
 #pragma unroll
   for (int q = 0; q < PIECES; ++q) {
-    const uint32_t mine = wide ? wide_row + (((wide_key ^ (uint32_t)q) & 7u) << 4)
-                               : sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
+    const uint32_t mine = sbuf + box_offset<OutT>((uint32_t)lane, (uint32_t)q);
     uint4 araw = make_uint4(0u, 0u, 0u, 0u);
     if (tile_gate) araw = ld_shared_v4(mine);     // this lane's piece of the activation tile
     const OutT* acte = reinterpret_cast<const OutT*>(&araw);
@@ -418,15 +408,13 @@ __device__ __forceinline__ uint32_t coalesced_chunk(float* v, float bias_lane, u
   if (tma_out) {
     // The box already has the layout of a swizzled TMA box: one asynchronous bulk store writes
     // it (clipped at the matrix edges) without occupying the load/store pipe.
-    if (!wide || e == 1) {
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        if (g_epi.reduce_add)
-          tma_reduce_add_2d(g_epi.tma_c + (g_epi.peer_rows > 0 ? row0_warp / g_epi.peer_rows : 0), sbuf, col0, row0_warp);
-        else tma_store_2d(g_epi.tma_c, sbuf, wide ? col0 - 32 : col0, split * g_epi.split_rows + row0_warp);
-        bulk_commit_group();
-      }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (g_epi.reduce_add)
+        tma_reduce_add_2d(g_epi.tma_c + (g_epi.peer_rows > 0 ? row0_warp / g_epi.peer_rows : 0), sbuf, col0, row0_warp);
+      else tma_store_2d(g_epi.tma_c, sbuf, col0, split * g_epi.split_rows + row0_warp);
+      bulk_commit_group();
     }
     return signs;
   }
@@ -605,8 +593,8 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
     if (rows_live && col0 < N) {
       const uint32_t box = sbuf + ((EW == 8 && MODE != -2 && sizeof(OutT) == 2 && g_epi.tma_c) ? box_sel : 0u);
       box_sel ^= 2048u;
-      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE, false, EW>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
-                                                                     split, row0_warp, col0, box, bias_smem, lane, 0);
+      const uint32_t signs = coalesced_chunk<OutT, ROUND_TF32, MODE, EW>(reinterpret_cast<float*>(raw_a), bias_cur, gate_cur,
+                                                              split, row0_warp, col0, box, bias_smem, lane);
       if (want_gate_out && row_ok) g_epi.gate_out[(col0 >> 5) * gate_pitch + gate_row] = signs;
       if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_a), col0, lane);
     }
@@ -619,11 +607,70 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
   return true;
 }
 
+// Finishes one 32-column chunk of a 16-bit output in registers: scale, bias, gate, ReLU, rounding to
+// the storage type.  out[0..3] are the row's four 16-byte pieces of the chunk; returns the sign bits
+// (bit j = value j > 0 before the ReLU).  v[] keeps the gated fp32 values (the column sums use them).
+template <typename OutT, int MODE>
+__device__ __forceinline__ uint32_t wide_prepare(float* v, float bias_lane, uint32_t gate, uint32_t bias_smem, int lane,
+                                                 uint4* out) {
+  const bool has_bias = MODE >= 0 ? (MODE & 1) != 0 : g_epi.has_bias != 0;
+  const bool relu = MODE >= 0 ? (MODE & 2) != 0 : g_epi.relu != 0;
+  const bool gate_out = MODE >= 0 ? (MODE & 4) != 0 : g_epi.gate_out != nullptr;
+  const bool gate_in = MODE >= 0 ? (MODE & 8) != 0 : g_epi.gate_in != nullptr;
+  if (MODE < 0 && g_epi.alpha != 1.0f) {
+    const float alpha = g_epi.alpha;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= alpha;
+  }
+  if (has_bias) {
+    // Lane j holds bias[col0 + j]; every lane needs all 32: spread them through 128 bytes of shared
+    // memory and read them back as broadcasts.
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(bias_smem + 4u * (uint32_t)lane), "f"(bias_lane) : "memory");
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint4 b = ld_shared_v4(bias_smem + 16u * (uint32_t)q);
+      v[4 * q + 0] += __uint_as_float(b.x);
+      v[4 * q + 1] += __uint_as_float(b.y);
+      v[4 * q + 2] += __uint_as_float(b.z);
+      v[4 * q + 3] += __uint_as_float(b.w);
+    }
+    __syncwarp();      // every lane has read them: the next chunk may overwrite the spread buffer
+  }
+  if (gate_in) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = ((gate >> j) & 1u) ? v[j] : 0.f;
+  }
+  uint32_t signs = 0u;
+  if (gate_out) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) signs |= (__float_as_int(v[j]) > 0 ? 1u : 0u) << j;
+  }
+  // ReLU of a compile-time mode rides on the 16-bit conversion itself.
+  constexpr bool RELU_IN_CVT = MODE >= 0 && (MODE & 2) != 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float x[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      x[t] = v[q * 8 + t];
+      if (relu && !RELU_IN_CVT) x[t] = fmaxf(x[t], 0.f);
+    }
+    out[q].x = pack2<OutT, RELU_IN_CVT>(x[0], x[1]);
+    out[q].y = pack2<OutT, RELU_IN_CVT>(x[2], x[3]);
+    out[q].z = pack2<OutT, RELU_IN_CVT>(x[4], x[5]);
+    out[q].w = pack2<OutT, RELU_IN_CVT>(x[6], x[7]);
+  }
+  return signs;
+}
+
 // The same for a 16-bit output whose tile is a whole number of 64-column chunk pairs and leaves
 // through TMA stores: the two warps of a quadrant take alternate PAIRS of adjacent chunks
-// (with two warps per quadrant, warp 0: chunks 0 1 4 5 ..., warp 1: 2 3 6 7 ...).  Both accumulator chunks of a pair are
-// requested from tensor memory at once, both halves go into one 32-row x 64-column box with
-// 128-byte rows, and one store (one proxy fence, one wait for the box to be free) serves the pair.
+// (warp 0: chunks 0 1 4 5 ..., warp 1: 2 3 6 7 ...).  Both accumulator chunks of a pair are
+// requested from tensor memory at once and finished in registers; only then does the warp wait for
+// its box -- 32 rows x 64 columns, 128-byte rows in the 128-byte swizzle, chunk e = 0 / 1 filling
+// pieces 4e .. 4e+3 of every row -- to be free, so that the store of the previous pair reads the
+// box while this pair is computed.  One store (one proxy fence) serves the pair.
 template <typename OutT, int MODE>
 __device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, int n0, int split, uint32_t bar_full,
                                                 uint32_t parity) {
@@ -667,6 +714,8 @@ __device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, i
   constexpr bool BOTH_AT_ONCE = MODE >= 0 && (MODE & 16) == 0;
   uint32_t raw_a[32], raw_b[32];
   constexpr int UG_EPI_STRIDE = UG_EPI_WARPS / 4;
+  const uint32_t wide_row = sbuf + (uint32_t)lane * 128u;
+  const uint32_t key = (uint32_t)lane & 7u;
   for (; c < nchunks; c += 2 * UG_EPI_STRIDE) {
     tmem_ld32(t_row + (uint32_t)(c * 32), raw_a);
     if (BOTH_AT_ONCE) tmem_ld32(t_row + (uint32_t)(c * 32 + 32), raw_b);
@@ -676,18 +725,33 @@ __device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, i
     const int col0 = n0 + c * 32;
     // A second chunk beyond N is all zeros and the store clips it; it is still written into the box.
     if (rows_live && col0 < N) {
-      const uint32_t sa = coalesced_chunk<OutT, false, MODE, true>(reinterpret_cast<float*>(raw_a), bias_a, gate_a, split,
-                                                                   row0_warp, col0, sbuf, bias_smem, lane, 0);
+      uint4 out_a[4], out_b[4];
+      const uint32_t sa = wide_prepare<OutT, MODE>(reinterpret_cast<float*>(raw_a), bias_a, gate_a, bias_smem, lane, out_a);
       if (want_gate_out && row_ok) g_epi.gate_out[(col0 >> 5) * gate_pitch + gate_row] = sa;
       if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_a), col0, lane);
       if (!BOTH_AT_ONCE) {
         tmem_ld32(t_row + (uint32_t)(c * 32 + 32), raw_b);
         tmem_ld_wait();
       }
-      const uint32_t sb = coalesced_chunk<OutT, false, MODE, true>(reinterpret_cast<float*>(raw_b), bias_b, gate_b, split,
-                                                                   row0_warp, col0 + 32, sbuf, bias_smem, lane, 1);
+      const uint32_t sb = wide_prepare<OutT, MODE>(reinterpret_cast<float*>(raw_b), bias_b, gate_b, bias_smem, lane, out_b);
       if (want_gate_out && row_ok && col0 + 32 < N) g_epi.gate_out[((col0 >> 5) + 1) * gate_pitch + gate_row] = sb;
       if constexpr (MODE >= 0 && (MODE & 16) != 0) chunk_colsum<MODE>(reinterpret_cast<float*>(raw_b), col0 + 32, lane);
+      // The store that last read this box must have finished reading it.
+      if (lane == 0) bulk_wait_group_read<0>();
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {        // piece 4e + q of the row sits at ((4e + q) ^ key) * 16
+        st_shared_v4(wide_row + (((uint32_t)q ^ key) << 4), out_a[q]);
+        st_shared_v4(wide_row + (((uint32_t)(4 + q) ^ key) << 4), out_b[q]);
+      }
+      // The box has the layout of a swizzled TMA box: one asynchronous bulk store writes it (clipped
+      // at the matrix edges) without occupying the load/store pipe.
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(g_epi.tma_c, sbuf, col0, split * g_epi.split_rows + row0_warp);
+        bulk_commit_group();
+      }
     }
     bias_a = bias_na; bias_b = bias_nb;
     gate_a = gate_na; gate_b = gate_nb;
