@@ -58,6 +58,7 @@ constexpr int UG_EPI_STAGING = UG_EPI_WARPS * 4096;  // one 32-row x 128-byte bo
 // same matrix in that rank's memory) and a CTA adds its rows to the copy of the rank that owns them.
 struct UmmaOutMaps {
   CUtensorMap m[UG_MAX_PEERS];
+  CUtensorMap b_tail;     // a K-major B with boxes of half as many rows: the half-width tiles of the last wave
 };
 
 struct UmmaGemmParams {
@@ -104,6 +105,8 @@ struct UmmaGemmParams {
   int epi_warps;       // 8 or 16 epilogue warps (the kernel instance launched)
   int reduce_add;      // 1: tiles are added to C through TMA reduce-add stores (split-K into one matrix, peer copies)
   int peer_rows;       // > 0: rows [r * peer_rows, (r + 1) * peer_rows) of C are added to rank r's copy (out map r)
+  int tail_first;      // work items from this one on are HALF tiles (block_n / 2 columns); == num_work: none
+  uint32_t idesc_tail; // instruction descriptor of a half tile
 };
 
 // Walks the work of one worker (a CTA, or a CTA pair): work items (split, tile) strided over the
@@ -119,12 +122,26 @@ struct WorkIter {
     stride = num_workers;
   }
   // The next item: tile index, split index, k-block range.  False when done.
-  __device__ __forceinline__ bool next(const UmmaGemmParams& p, int& tile, int& split, int& kb_begin, int& kb_end) {
+  // `half`: -1 for a whole tile; 0 / 1 for the left / right half of one (the last wave of a launch whose
+  // tiles would fill less than half of the workers is cut into half-width tiles, so that it takes about
+  // half as long; only launches without split-K have such items).
+  __device__ __forceinline__ bool next(const UmmaGemmParams& p, int& tile, int& split, int& kb_begin, int& kb_end,
+                                       int& half) {
     if (work >= p.num_work) return false;
-    split = work / p.num_tiles;
-    tile = work - split * p.num_tiles;
-    kb_begin = split * p.kb_per_split;
-    kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+    if (work >= p.tail_first) {
+      const int t = work - p.tail_first;
+      split = 0;
+      tile = p.tail_first + (t >> 1);
+      half = t & 1;
+      kb_begin = 0;
+      kb_end = p.k_blocks;
+    } else {
+      half = -1;
+      split = work / p.num_tiles;
+      tile = work - split * p.num_tiles;
+      kb_begin = split * p.kb_per_split;
+      kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+    }
     work += stride;
     return true;
   }
@@ -500,11 +517,10 @@ __device__ __forceinline__ void direct_chunk16(float* v, long long row, int col0
 // Chunks that cannot take the coalesced path, from chunk `c` on: per-thread stores, 16 columns at
 // a time.  A function of its own so that its registers do not add to the fast path's.
 template <typename OutT, bool ROUND_TF32, int EW>
-__device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0, int split, int c) {
+__device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0, int block_n, int split, int c) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)row0_warp + lane;
   const bool row_ok = row < g_epi.M;
-  const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
   for (; c < nchunks; c += EW / 4) {
     const int w = min(32, block_n - c * 32);
@@ -526,8 +542,8 @@ __device__ __noinline__ void epilogue_rest(uint32_t t_row, int row0_warp, int n0
 // must not spill: with the L1 carved out as shared memory a spilled register
 // costs an L2 round trip.  Returns false when the wait for the accumulator expired.
 template <typename OutT, bool ROUND_TF32, int MODE, int EW>
-__device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0, int split, uint32_t bar_full,
-                                           uint32_t parity) {
+__device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0, int block_n, int split,
+                                           uint32_t bar_full, uint32_t parity) {
   static_assert(EW == 8 || (EW == 16 && sizeof(OutT) == 2), "sixteen epilogue warps: 2 KB staging slots, 16-bit outputs only");
   constexpr int STRIDE = EW / 4;
   const int lane = threadIdx.x & 31;
@@ -541,7 +557,6 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
   const int N = g_epi.N;
   const bool row_ok = row0_warp + lane < g_epi.M;
   const bool rows_live = row0_warp < g_epi.M;
-  const int block_n = g_epi.block_n;
   const int nchunks = (block_n + 31) >> 5;
   const int nfull = g_epi.coalesced ? (block_n >> 5) : 0;     // chunks that take the coalesced path
   // The sign-bit matrices are stored [N / 32, M]: the 32 rows of a warp are 32 consecutive words,
@@ -603,7 +618,7 @@ __device__ __noinline__ bool epilogue_tile(uint32_t t_row, int row0_warp, int n0
   }
   // What is left for this warp: a 16-column tail chunk, or every chunk when C
   // cannot take row-contiguous 16-byte stores.
-  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32, EW>(t_row, row0_warp, n0, split, c);
+  if (c < nchunks) epilogue_rest<OutT, ROUND_TF32, EW>(t_row, row0_warp, n0, block_n, split, c);
   return true;
 }
 
@@ -672,8 +687,8 @@ __device__ __forceinline__ uint32_t wide_prepare(float* v, float bias_lane, uint
 // pieces 4e .. 4e+3 of every row -- to be free, so that the store of the previous pair reads the
 // box while this pair is computed.  One store (one proxy fence) serves the pair.
 template <typename OutT, int MODE>
-__device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, int n0, int split, uint32_t bar_full,
-                                                uint32_t parity) {
+__device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, int n0, int block_n, int split,
+                                                uint32_t bar_full, uint32_t parity) {
   static_assert(sizeof(OutT) == 2 && MODE != -2, "wide boxes: 16-bit output through TMA stores only");
   const int lane = threadIdx.x & 31;
   const int ewarp = (int)(threadIdx.x >> 5) - 2;
@@ -686,7 +701,7 @@ __device__ __noinline__ bool epilogue_tile_wide(uint32_t t_row, int row0_warp, i
   const int N = g_epi.N;
   const bool row_ok = row0_warp + lane < g_epi.M;
   const bool rows_live = row0_warp < g_epi.M;
-  const int nchunks = g_epi.block_n >> 5;     // even
+  const int nchunks = block_n >> 5;     // even
   const long long gate_row = (long long)(row0_warp + lane);
   const long long gate_pitch = g_epi.M;
 
@@ -903,24 +918,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       const int b_cols = PAIR ? p.block_n / 2 : p.block_n;   // half of the B columns per CTA in a pair
-      const uint32_t tx_bytes = PAIR ? 2u * stage_bytes : stage_bytes;
       const uint32_t full0_local = smem_u32(&bar_full[0]);
       const uint32_t full0 = PAIR ? map_to_cta(full0_local, 0u) : full0_local;
       const uint32_t empty0 = smem_u32(&bar_empty[0]);
       const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0;
-      const int a_boxes = p.a_boxes, b_boxes = p.b_boxes, mn_box_elems = p.mn_box_elems, block_k = p.block_k;
+      const int a_boxes = p.a_boxes, mn_box_elems = p.mn_box_elems, block_k = p.block_k;
       const uint32_t mn_box_bytes = p.mn_box_bytes, a_stage_bytes = p.a_stage_bytes;
       const int subs = p.subs;
       const uint32_t a_sub_bytes = p.a_sub_bytes, b_sub_bytes = p.b_sub_bytes;
       const int stages = p.stages;
       uint32_t a_dst = stage_base;
       WorkIter it(p, worker, num_workers);
-      int tile, split, kb_begin, kb_end;
-      while (ok && it.next(p, tile, split, kb_begin, kb_end)) {
+      int tile, split, kb_begin, kb_end, half;
+      while (ok && it.next(p, tile, split, kb_begin, kb_end, half)) {
         int m_blk, n_blk;
         tile_coords(p, tile, m_blk, n_blk);
         const int m0 = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M;
-        const int n0 = n_blk * p.block_n + (int)cta_rank * b_cols;
+        // A half tile: half as many B columns per CTA (half the boxes, or a tensor map with half-height boxes).
+        const int item_cols = half < 0 ? b_cols : b_cols / 2;
+        const int n0 = n_blk * p.block_n + (half > 0 ? p.block_n / 2 : 0) + (int)cta_rank * item_cols;
+        const CUtensorMap* map_b = half < 0 ? &tmap_b : &out_maps.b_tail;
+        const int b_boxes = half < 0 ? p.b_boxes : p.b_boxes / 2;
+        const uint32_t item_b_bytes = half < 0 ? p.b_stage_bytes : p.b_stage_bytes / 2u;
+        const uint32_t tx_bytes = PAIR ? 2u * (a_stage_bytes + item_b_bytes) : a_stage_bytes + item_b_bytes;
         int k0 = kb_begin * block_k;
         for (int kb = kb_begin; kb < kb_end; ++kb, k0 += block_k) {
           if (!mbar_wait(empty0 + 8u * (uint32_t)stage, phase ^ 1u, abortp, SB_SITE_PRODUCER_EMPTY)) {
@@ -944,8 +964,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (!b_mn) {
             for (int s = 0; s < subs; ++s) {
-              if (PAIR) tma_load_2d_pair(b_dst + (uint32_t)s * b_sub_bytes, &tmap_b, k0 + s * mn_box_elems, n0, full);
-              else tma_load_2d(b_dst + (uint32_t)s * b_sub_bytes, &tmap_b, k0 + s * mn_box_elems, n0, full);
+              if (PAIR) tma_load_2d_pair(b_dst + (uint32_t)s * b_sub_bytes, map_b, k0 + s * mn_box_elems, n0, full);
+              else tma_load_2d(b_dst + (uint32_t)s * b_sub_bytes, map_b, k0 + s * mn_box_elems, n0, full);
             }
           } else {
             for (int i = 0; i < b_boxes; ++i) {
@@ -981,15 +1001,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
       const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0;
       const uint32_t stage_step = stage_bytes >> 4;
-      const uint32_t a_kstep = p.a_kstep, b_kstep = p.b_kstep, idesc = p.idesc;
+      const uint32_t a_kstep = p.a_kstep, b_kstep = p.b_kstep;
       const uint32_t a_sub_step = p.a_sub_step, b_sub_step = p.b_sub_step;
       const bool two_subs = p.subs == 2;
       const uint32_t full0 = smem_u32(&bar_full[0]), empty0 = smem_u32(&bar_empty[0]);
       const int stages = p.stages;
       uint32_t a_lo = a_lo0, b_lo = b_lo0;
       WorkIter it(p, worker, num_workers);
-      int tile, split, kb_begin, kb_end;
-      while (ok && it.next(p, tile, split, kb_begin, kb_end)) {
+      int tile, split, kb_begin, kb_end, half;
+      while (ok && it.next(p, tile, split, kb_begin, kb_end, half)) {
+        const uint32_t idesc = half < 0 ? p.idesc : p.idesc_tail;
         if (!mbar_wait(smem_u32(&bar_tmem_empty[acc]), acc_phase ^ 1u, abortp, SB_SITE_MMA_TMEM_EMPTY)) {
           ok = false;
           break;
@@ -1050,10 +1071,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (flags == 0 || flags == 3 || flags == 7 || flags == 8 || flags == 16 || flags == 24) epi_mode = flags;
     }
     WorkIter it(p, worker, num_workers);
-    int tile, split, kb_begin, kb_end;
-    while (it.next(p, tile, split, kb_begin, kb_end)) {
+    int tile, split, kb_begin, kb_end, half_tile;
+    while (it.next(p, tile, split, kb_begin, kb_end, half_tile)) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
+      const int item_n = half_tile < 0 ? p.block_n : p.block_n / 2;
       const int row0_warp = m_blk * TILE_M + (int)cta_rank * UG_BLOCK_M + quad * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
       const uint32_t full_bar = smem_u32(&bar_tmem_full[acc]);
@@ -1068,10 +1090,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       } else {
-        const int n0 = n_blk * p.block_n;
+        const int n0 = n_blk * p.block_n + (half_tile > 0 ? item_n : 0);
         bool ok;
-#define SB_EPI_CALL(T, R, G) epilogue_tile<T, R, G, EW>(t_row, row0_warp, n0, split, full_bar, acc_phase)
-#define SB_EPI_WIDE(T, G) epilogue_tile_wide<T, (G) == -2 ? -1 : (G)>(t_row, row0_warp, n0, split, full_bar, acc_phase)
+#define SB_EPI_CALL(T, R, G) epilogue_tile<T, R, G, EW>(t_row, row0_warp, n0, item_n, split, full_bar, acc_phase)
+#define SB_EPI_WIDE(T, G) epilogue_tile_wide<T, (G) == -2 ? -1 : (G)>(t_row, row0_warp, n0, item_n, split, full_bar, acc_phase)
 #define SB_EPI_BY_TYPE(G)                                                        \
   do {                                                                           \
     if constexpr (EW == 16) {            /* 16-bit outputs only, one 32 x 32 box per chunk */ \
@@ -1196,6 +1218,14 @@ bool sb_pair_mode_enabled() {
 }
 
 // SB_EPI_WARPS=8 in the environment keeps every GEMM on eight epilogue warps.
+bool tail_split_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SB_TAIL_SPLIT");     // SB_TAIL_SPLIT=0 keeps whole tiles in the last wave (tuning runs)
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 bool epi16_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -1454,6 +1484,24 @@ int sb_umma_gemm_launch(int a_trans, int b_trans, float alpha, const void* A, co
     p.tma_store = 1;
   }
   if (p.epi_warps == 0) p.epi_warps = 8;
+  // A last wave that would fill at most half of the pairs is cut into half-width tiles (twice as many
+  // items, each about half as long): 4096^3 is 256 tiles on 74 pairs, three full waves and 34 tiles.
+  p.tail_first = p.num_work;
+  p.idesc_tail = p.idesc;
+  if (p.pair && p.splits == 1 && !to_peers && !(epi & (EPI_HEAD_MASK | SB_EPI_LN_L2)) && p.block_n % 128 == 0 &&
+      tail_split_enabled()) {
+    const int workers = cached_sm_count() / 2;
+    const int rem = workers > 0 ? p.num_tiles % workers : 0;
+    if (p.num_tiles > workers && rem > 0 && 2 * rem <= workers) {
+      p.tail_first = p.num_tiles - rem;
+      p.num_work = p.num_tiles + rem;
+      p.idesc_tail = sb_umma_idesc(in_dtype, p.a_mn, p.b_mn, 2 * UG_BLOCK_M, p.block_n / 2);
+      if (!p.b_mn) {
+        rc = make_tmap_2d(&tc.b_tail, B, in_dtype, N, K, p.block_n / 4, p.mn_box_elems, SWZ_128);
+        if (rc != SB_OK) return rc;
+      }
+    }
+  }
   if (p.reduce_add && !p.tma_store)
     return sb_fail(SB_ERR_UNSUPPORTED, "internal: split-K accumulation was chosen for a C that cannot take TMA stores");
   const size_t smem = umma_dyn_smem(p);

@@ -5,7 +5,7 @@ TMEM accumulators fed by TMA).  No CPU fallback exists: without the built
 library every operation raises.
 """
 from ._lib import SpiralError, LIB_PATH  # noqa: F401
-from .device import (DeviceArray, Event, Stream, wait_event, GemmProfile, launch_count, device_count, device_ptr, device_status, check_device, mem_info, set_device,  # noqa: F401
+from .device import (DeviceArray, Event, Stream, wait_event, GemmProfile, launch_count, device_count, device_ptr, device_status, check_device, mem_info, set_device, sm_count,  # noqa: F401
                      synchronize)
 from .matmul import head_spec, matmul, matmul_head, matmul_plan, matmul_tf32  # noqa: F401
 from . import primitives  # noqa: F401

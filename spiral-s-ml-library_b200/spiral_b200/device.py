@@ -28,6 +28,13 @@ def set_device(index):
     _lib.call("sb_set_device", int(index))
 
 
+def sm_count():
+    """Streaming multiprocessors of the current device (the tile planner's worker count)."""
+    n = ctypes.c_int(0)
+    _lib.call("sb_device_sm_count", ctypes.byref(n))
+    return n.value
+
+
 def synchronize():
     """Waits for all device work (corecuda/base.spi:45 device_sync)."""
     _lib.call("sb_device_sync")

@@ -63,6 +63,33 @@ def test_ragged_4000x3000x1000(gpu, at, bt, in_dtype):
     assert so.rel_frobenius(got, so.matmul(at, bt, 1.0, a, b, 0.0, None)) <= TIGHT
 
 
+@pytest.mark.parametrize("in_dtype,out_dtype", [("bf16", "f32"), ("f16", "bf16"), ("tf32", "f32")])
+@pytest.mark.parametrize("at,bt", LAYOUTS[:3])
+def test_last_wave_of_half_width_tiles(gpu, at, bt, in_dtype, out_dtype):
+    """More 256 x 256 tiles than CTA pairs, with a remainder of at most half the pairs: the last wave runs
+    as half-width tiles (two work items per tile, their own instruction descriptor and B boxes).  Sized
+    from the SM count so that the remainder is 9 tiles; a ragged M and N put the clipped tiles there."""
+    pairs = gpu.sm_count() // 2
+    tiles_m = pairs + 9
+    m, n, k = 256 * tiles_m - 40, 248, 192
+    a, b, c = operands(61, at, bt, m, n, k, in_dtype)
+    bias = so.rng(62).normal(size=n).astype(np.float32)
+    plan = gpu.matmul_plan(at, bt, m, n, k, in_dtype)
+    assert plan["block_m"] == 256 and plan["block_n"] == 256       # CTA pairs, one tile column
+    kw = {}
+    if out_dtype != "f32":
+        kw = dict(epilogue=("bias", "relu"), bias=gpu.DeviceArray.from_numpy(bias))
+    got = run(gpu, at, bt, 1.0, a, b, 0.0, c, in_dtype, out_dtype=out_dtype, **kw)
+    want = so.matmul(at, bt, 1.0, a, b, 0.0, None)
+    if out_dtype != "f32":
+        want = so.round_input(so.relu(want + bias), out_dtype)
+        assert so.rel_frobenius(got, want) <= 3e-3
+    else:
+        assert so.rel_frobenius(got, want) <= TIGHT
+    tail = slice(256 * (tiles_m - 9), m)          # the rows of the half-width tiles, by themselves
+    assert so.rel_frobenius(got[tail], want[tail]) <= (3e-3 if out_dtype != "f32" else TIGHT)
+
+
 @pytest.mark.parametrize("m,n,k", [(8, 8, 8), (136, 24, 72), (120, 264, 200), (304, 520, 136), (64, 1000, 8)])
 @pytest.mark.parametrize("at,bt", LAYOUTS[:3])
 def test_small_odd_shapes_bf16(gpu, at, bt, m, n, k):
