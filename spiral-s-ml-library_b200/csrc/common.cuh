@@ -238,6 +238,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// 16 bytes from global to shared memory without passing through registers (cp.async); the copies
+// of a thread complete in the order of their commit groups.
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 // The same for a 3-D tensor (x innermost).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* tmap, int x, int y, int z,
                                             uint32_t bar) {

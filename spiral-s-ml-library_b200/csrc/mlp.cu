@@ -173,6 +173,179 @@ colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int 
   }
 }
 
+// dgrad of a layer with at most 16 outputs (the head): dX[r, n] = gate(r, n) * sum_k dY[r, k] * W[k, n],
+// k < KV.  With so short an inner dimension the tensor-core kernel is all epilogue (it drains a
+// 128 x 256 accumulator in 4.4 us whatever K is); here a thread keeps its 8 columns of W in
+// registers, 8 * KV fused multiply-adds make one 16-byte store, rows are taken eight at a time so
+// that the sign words of a column block (stored [N / 32, rows]) come as two 16-byte loads, and the
+// output leaves at HBM rate.  Column sums of the output (the bias gradient of the layer below) are
+// kept per thread over all its rows and added once per block and column.
+constexpr int ND_THREADS = 384;
+constexpr int ND_MAX_SLOTS = ND_THREADS / 32;
+template <typename T, int KV>
+__global__ void __launch_bounds__(ND_THREADS, 1)
+narrow_dgrad_kernel(const T* __restrict__ dy, int ldy, const T* __restrict__ w, int n, const uint32_t* __restrict__ bits,
+                    T* __restrict__ dx, float* __restrict__ colsum, int rows) {
+  __shared__ float sums[1024];
+  // The dY rows of the next eight rows of every slot arrive here (cp.async) while this eight are computed.
+  __shared__ __align__(16) uint4 dy_s[2][ND_MAX_SLOTS][8][2];
+  sb_grid_dependency_wait();
+  sb_grid_dependents_launch();
+  const int groups = n >> 3;                                    // 16-byte column groups of a row
+  const int tpr = groups < 128 ? ((groups + 31) & ~31) : 128;   // threads per row slot: whole warps
+  const int slots = ND_THREADS / tpr;                           // row slots of a block (3 when n >= 1024)
+  const int slot = (int)threadIdx.x / tpr, t = (int)threadIdx.x % tpr;
+  const long long stride = (long long)gridDim.x * slots * 8;
+  const int iters = (int)((rows + stride - 1) / stride);        // the same for every thread: the loop holds barriers
+  const int halves = ldy >= 16 ? 2 : 1;                         // 16-byte pieces of a dY row that are read
+  for (int cg0 = 0; cg0 < groups; cg0 += 128) {                 // n > 1024: one pass per 1024 columns
+    const int cg = cg0 + t;
+    const bool live = cg < groups && slot < slots;
+    float wr[KV][8];
+#pragma unroll
+    for (int k = 0; k < KV; ++k) {
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (live) raw = *reinterpret_cast<const uint4*>(w + (long long)k * n + cg * 8);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wr[k][j] = (float)e[j];
+    }
+    float cs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cs[j] = 0.f;
+    const int shift = (cg & 3) * 8;                // this thread's 8 bits inside its 32-column sign word
+    const long long first = ((long long)blockIdx.x * slots + slot) * 8;
+
+    // Thread t < 16 of a slot fetches piece (t & 1) of row (t >> 1) of the slot's eight rows.
+    auto fetch_dy = [&](int it) {
+      if (slot < slots && t < 16) {
+        const long long r = first + (long long)it * stride + (t >> 1);
+        if (r < rows && (t & 1) < halves)
+          cp_async_16(smem_u32(&dy_s[it & 1][slot][t >> 1][t & 1]), dy + r * ldy + (t & 1) * 8);
+      }
+      cp_async_commit();
+    };
+    auto fetch_gate = [&](int it, uint32_t* gate) {
+      const long long r0 = first + (long long)it * stride;
+      if (!live || r0 >= rows) return;
+      if (bits) {
+        const uint32_t* g = bits + (long long)(cg >> 2) * rows + r0;
+        if (r0 + 8 <= rows && ((reinterpret_cast<uintptr_t>(g) & 15) == 0)) {
+          const uint4 a = __ldg(reinterpret_cast<const uint4*>(g)), b = __ldg(reinterpret_cast<const uint4*>(g) + 1);
+          gate[0] = a.x; gate[1] = a.y; gate[2] = a.z; gate[3] = a.w;
+          gate[4] = b.x; gate[5] = b.y; gate[6] = b.z; gate[7] = b.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) gate[i] = r0 + i < rows ? __ldg(g + i) : 0u;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gate[i] = 0xffffffffu;
+      }
+    };
+
+    uint32_t gate[8], gate_next[8];
+    fetch_dy(0);
+    fetch_gate(0, gate);
+    for (int it = 0; it < iters; ++it) {
+      cp_async_wait_all();
+      __syncthreads();                       // this iteration's dY rows are in; the other buffer is free
+      if (it + 1 < iters) {
+        fetch_dy(it + 1);
+        fetch_gate(it + 1, gate_next);
+      }
+      const long long r0 = first + (long long)it * stride;
+      if (live && r0 < rows) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const long long r = r0 + i;
+          if (r < rows) {
+            float d[KV];
+#pragma unroll
+            for (int k8 = 0; k8 < KV; k8 += 8) {
+              const uint4 raw = dy_s[it & 1][slot][i][k8 >> 3];      // the same address for the whole warp
+              const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (k8 + j < KV) d[k8 + j] = (float)e[j];
+            }
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+            for (int k = 0; k < KV; ++k)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] = fmaf(d[k], wr[k][j], acc[j]);
+            const uint32_t gb = gate[i] >> shift;
+            uint4 out;
+            T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float v = ((gb >> j) & 1u) ? acc[j] : 0.f;
+              cs[j] += v;
+              o[j] = (T)v;
+            }
+            *reinterpret_cast<uint4*>(dx + r * n + cg * 8) = out;
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gate[i] = gate_next[i];
+    }
+    __syncthreads();
+    if (colsum) {
+      // One addition per block and column: the row slots fold in shared memory first.
+      for (int c = (int)threadIdx.x; c < tpr * 8; c += ND_THREADS) sums[c] = 0.f;
+      __syncthreads();
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(&sums[t * 8 + j], cs[j]);
+      }
+      __syncthreads();
+      for (int c = (int)threadIdx.x; c < tpr * 8; c += ND_THREADS) {
+        const int col = cg0 * 8 + c;
+        const float v = sums[c];
+        if (col < n && v != 0.f) atomicAdd(colsum + col, v);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Whether the narrow dgrad kernel serves a layer: a 16-bit storage type, at most 16 (real) outputs,
+// rows of whole 16-byte groups.
+bool narrow_dgrad_ok(int fan_out_real, int fan_in, int in_dtype) {
+  static int off = -1;
+  if (off < 0) {
+    const char* e = getenv("SB_NARROW_DGRAD");          // SB_NARROW_DGRAD=0: the tensor-core kernel for every layer
+    off = (e && e[0] == '0') ? 1 : 0;
+  }
+  return !off && (in_dtype == SB_BF16 || in_dtype == SB_F16) && fan_out_real >= 1 && fan_out_real <= 16 && fan_in % 8 == 0;
+}
+
+template <typename T>
+int narrow_dgrad_launch(const void* dy, int ldy, const void* w, int fan_out_real, int n, const uint32_t* bits, void* dx,
+                        float* colsum, int rows, cudaStream_t s) {
+  const int groups = n / 8;
+  const int tpr = groups < 128 ? ((groups + 31) & ~31) : 128;
+  const int slots = ND_THREADS / tpr;
+  long long want = ((long long)rows + slots * 8 - 1) / (slots * 8);
+  const int grid = (int)(want < sb_sm_count() ? (want < 1 ? 1 : want) : sb_sm_count());
+  const T* dyp = reinterpret_cast<const T*>(dy);
+  const T* wp = reinterpret_cast<const T*>(w);
+  T* dxp = reinterpret_cast<T*>(dx);
+#define SB_ND(KV) SB_CUDA(sb_launch(narrow_dgrad_kernel<T, KV>, dim3(grid), dim3(ND_THREADS), 0, s, 1, dyp, ldy, wp, n, bits, dxp, colsum, rows))
+  if (fan_out_real <= 4) SB_ND(4);
+  else if (fan_out_real <= 8) SB_ND(8);
+  else if (fan_out_real <= 10) SB_ND(10);
+  else if (fan_out_real <= 12) SB_ND(12);
+  else SB_ND(16);
+#undef SB_ND
+  SB_COUNT_LAUNCH();
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
 // grads[i] = sum over splits of partial[s][i]; deterministic order.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                      long long n, int splits) {
@@ -214,10 +387,12 @@ int blocks_for(long long n, int per_block, int cap = 0) {
 }
 
 // Split factor of a wgrad GEMM [out, in] with inner dimension = batch.  A GEMM with more than
-// 128 output rows runs on CTA pairs (256 x 256 tiles, 74 pairs): the factor that minimises
-// (waves of work items over the pairs) / splits, plus a charge per split for the partials' write
-// and reduction -- for a 1024 x 1024 layer at a batch of 262144, 9 splits (144 items, two full
-// waves) instead of 4 (64 items on 74 pairs, 14 % of the GPU idle); at 32768 rows still 4.  Narrow outputs run on single CTAs, one item each.
+// 128 output rows runs on CTA pairs (256 x 256 tiles, 74 pairs).  Model of its time, in k-blocks:
+// (waves of work items over the pairs) x (k-blocks per item + a fixed part per item for pipeline
+// fill and the tile's reduce-add).  For a 1024 x 1024 layer at a batch of 262144 that picks 9 splits
+// (144 items, two full waves) instead of 4 (64 items on 74 pairs, 14 % of the GPU idle), at 32768
+// rows still 4; a 256 x 256 layer (one tile) is cut into as many items as there are pairs, which
+// measured 23 us against 37 us with 11.  Narrow outputs run on single CTAs, one item each.
 int wgrad_splits(int out, int in, int batch, int in_dtype) {
   static int forced = -1;                  // SB_WGRAD_SPLITS=n in the environment fixes the factor (tuning runs)
   if (forced < 0) {
@@ -233,15 +408,14 @@ int wgrad_splits(int out, int in, int batch, int in_dtype) {
   if (out > 128) {
     const int tiles = ((out + 255) / 256) * ((in + 255) / 256);
     const int workers = sb_sm_count() / 2;
-    // One more split costs one more partial tile written and reduced (a few microseconds), against a
-    // full-K tile time that grows with the batch: about 4 k-blocks' worth.
-    const double per_split = 4.0 / (double)k_blocks;
+    // The fixed part of an item, in k-blocks (about 6 us against 0.55 us per k-block of a pair tile).
+    const int item_fixed = 10;
     int best = 1;
-    double best_cost = 1e30;
-    for (int s = 1; s <= 32 && s <= max_by_k; ++s) {
-      const int waves = (tiles * s + workers - 1) / workers;
-      const double cost = (double)waves / s + per_split * s;
-      if (cost < best_cost - 1e-12) {
+    long long best_cost = -1;
+    for (int s = 1; s <= 128 && s <= max_by_k; ++s) {
+      const long long waves = ((long long)tiles * s + workers - 1) / workers;
+      const long long cost = waves * ((k_blocks + s - 1) / s + item_fixed);
+      if (best_cost < 0 || cost < best_cost) {
         best_cost = cost;
         best = s;
       }
@@ -618,6 +792,13 @@ static int backward_impl(int n_layers, const int* sizes, int batch, float inv_gl
       // (fan_in = sizes[i] is its unpadded width: hidden widths are multiples of 8 and, here, of 32).
       const bool sum_cols = bits && with_bias;
       float* db_below = grads + off[2 * (i - 1) + 1];
+      if (bits && narrow_dgrad_ok(sizes[i + 1], fan_in, in_dtype) && st == in_dtype) {
+        // A head layer: the inner dimension is at most 16, nothing for the tensor cores to do.
+        const uint32_t* gate = reinterpret_cast<const uint32_t*>(relu_bits[i - 1]);
+        rc = in_dtype == SB_BF16
+                 ? narrow_dgrad_launch<__nv_bfloat16>(dy_cur, fan_out, w, sizes[i + 1], fan_in, gate, dy_next, sum_cols ? db_below : nullptr, batch, s)
+                 : narrow_dgrad_launch<__half>(dy_cur, fan_out, w, sizes[i + 1], fan_in, gate, dy_next, sum_cols ? db_below : nullptr, batch, s);
+      } else
       rc = sb_umma_gemm_launch(0, 0, 1.0f, dy_cur, w, 0.0f, dy_next, batch, fan_in, fan_out, in_dtype, st,
                                bits ? (SB_EPI_RELU_GRAD_MASK | (sum_cols ? SB_EPI_COLSUM_OUT : 0)) : SB_EPI_RELU_GRAD,
                                nullptr, nullptr, bits ? (const void*)relu_bits[i - 1] : h_in,
