@@ -180,6 +180,19 @@ colsum_kernel(const DyT* __restrict__ dy, float* __restrict__ db, int rows, int 
 // that the sign words of a column block (stored [N / 32, rows]) come as two 16-byte loads, and the
 // output leaves at HBM rate.  Column sums of the output (the bias gradient of the layer below) are
 // kept per thread over all its rows and added once per block and column.
+// Two fp32 fused multiply-adds in one instruction (the packed form sm_100 adds): c += a * b on register pairs.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void fma_f32x2(unsigned long long& c, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(a), "l"(b));
+}
+
 constexpr int ND_THREADS = 384;
 constexpr int ND_MAX_SLOTS = ND_THREADS / 32;
 template <typename T, int KV>
@@ -201,14 +214,14 @@ narrow_dgrad_kernel(const T* __restrict__ dy, int ldy, const T* __restrict__ w, 
   for (int cg0 = 0; cg0 < groups; cg0 += 128) {                 // n > 1024: one pass per 1024 columns
     const int cg = cg0 + t;
     const bool live = cg < groups && slot < slots;
-    float wr[KV][8];
+    unsigned long long wr[KV][4];            // the thread's 8 columns of W as four fp32 pairs per k
 #pragma unroll
     for (int k = 0; k < KV; ++k) {
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
       if (live) raw = *reinterpret_cast<const uint4*>(w + (long long)k * n + cg * 8);
       const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) wr[k][j] = (float)e[j];
+      for (int j = 0; j < 4; ++j) wr[k][j] = pack_f32x2((float)e[2 * j], (float)e[2 * j + 1]);
     }
     float cs[8];
 #pragma unroll
@@ -269,13 +282,16 @@ narrow_dgrad_kernel(const T* __restrict__ dy, int ldy, const T* __restrict__ w, 
               for (int j = 0; j < 8; ++j)
                 if (k8 + j < KV) d[k8 + j] = (float)e[j];
             }
+            unsigned long long acc2[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+            for (int k = 0; k < KV; ++k) {
+              const unsigned long long dd = pack_f32x2(d[k], d[k]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) fma_f32x2(acc2[j], dd, wr[k][j]);
+            }
             float acc[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-            for (int k = 0; k < KV; ++k)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc[j] = fmaf(d[k], wr[k][j], acc[j]);
+            for (int j = 0; j < 4; ++j) unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
             const uint32_t gb = gate[i] >> shift;
             uint4 out;
             T* o = reinterpret_cast<T*>(&out);
