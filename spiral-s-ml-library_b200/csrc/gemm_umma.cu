@@ -791,10 +791,10 @@ __shared__ HeadShared g_head;
 template <int W>
 __device__ __noinline__ void epilogue_head(uint32_t t_row, long long row, int M) {
   uint32_t raw[W];
-  if (W == 64) {
+  if constexpr (W == 64) {
     tmem_ld32(t_row, raw);
     tmem_ld32(t_row + 32u, raw + 32);
-  } else if (W == 32) {
+  } else if constexpr (W == 32) {
     tmem_ld32(t_row, raw);
   } else {
     tmem_ld16(t_row, raw);

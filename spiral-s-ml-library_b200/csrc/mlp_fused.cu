@@ -87,10 +87,10 @@ template <int W>
 __device__ __noinline__ void fused_head(const SbRowHead& h, const float* bias, float* out, uint32_t t_row, long long row,
                                         int batch) {
   uint32_t raw[W];
-  if (W == 64) {
+  if constexpr (W == 64) {
     tmem_ld32(t_row, raw);
     tmem_ld32(t_row + 32u, raw + 32);
-  } else if (W == 32) {
+  } else if constexpr (W == 32) {
     tmem_ld32(t_row, raw);
   } else {
     tmem_ld16(t_row, raw);
