@@ -77,6 +77,52 @@ __global__ void ce_grad_kernel(const float* __restrict__ probs, const float* __r
     const float* pr = probs + r * n;
     const float* tr = target + r * n;
     const uint8_t* mr = mask ? mask + r * n : nullptr;
+    if (LD > 0 && sizeof(DyT) == 2) {
+      // The whole row in registers first (an even row length keeps every row 8-byte aligned:
+      // probabilities and targets then come as two-float loads); then one or two 16-byte stores of
+      // the padded 16-bit row instead of LD two-byte ones 2 * LD bytes apart.
+      float pv[NACC], tv[NACC];
+      if ((n & 1) == 0) {
+#pragma unroll
+        for (int j = 0; j < NACC; j += 2) {
+          float2 a = make_float2(0.f, 0.f), b = a;
+          if (j < n) {
+            a = __ldg(reinterpret_cast<const float2*>(pr + j));
+            b = __ldg(reinterpret_cast<const float2*>(tr + j));
+          }
+          pv[j] = a.x; pv[j + 1] = a.y;
+          tv[j] = b.x; tv[j + 1] = b.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < NACC; ++j) {
+          pv[j] = j < n ? __ldg(pr + j) : 0.f;
+          tv[j] = j < n ? __ldg(tr + j) : 0.f;
+        }
+      }
+      bool legal[NACC];
+      float ts = 0.f;
+#pragma unroll
+      for (int j = 0; j < NACC; ++j) {
+        legal[j] = j < n && (!mr || mr[j]);
+        if (legal[j]) ts += tv[j];
+      }
+      __align__(16) DyT packed[NACC];
+#pragma unroll
+      for (int j = 0; j < NACC; ++j) {
+        float g = 0.f;
+        if (legal[j]) {
+          g = (pv[j] * ts - tv[j]) * inv_batch;
+          local -= tv[j] * __logf(fmaxf(pv[j], 1e-38f));
+        }
+        colacc[j] += g;
+        packed[j] = (DyT)g;
+      }
+      uint4* dst = reinterpret_cast<uint4*>(dy + r * ld);
+#pragma unroll
+      for (int q = 0; q < NACC / 8; ++q) dst[q] = reinterpret_cast<const uint4*>(packed)[q];
+      continue;
+    }
     float tsum = 0.f;
     for (int j = 0; j < n; ++j)
       if (!mr || mr[j]) tsum += tr[j];
