@@ -88,6 +88,34 @@ def test_backward_gradients(gpu, in_dtype, sizes, batch):
     assert not flat.any()
 
 
+@pytest.mark.parametrize("in_dtype,sizes,batch", [
+    ("bf16", [64, 1088, 7], 1001),       # 1088 columns: two passes of the head dgrad; odd batch: unaligned sign words
+    ("f16", [64, 96, 12], 777),          # 12 outputs, a row of three warps' worth of 16-byte groups
+    ("bf16", [32, 160, 16], 520),        # 16 outputs: the widest head the CUDA-core dgrad takes
+    ("bf16", [32, 128, 8], 4096),
+])
+def test_backward_gradients_head_widths(gpu, in_dtype, sizes, batch):
+    """The dgrad of a head with at most 16 outputs runs on the CUDA cores (one instance per width class,
+    sign words read 8 rows at a time, column sums per block): gradients against the oracle for the
+    widths, row lengths and batch sizes that take its different paths."""
+    net, ws, bs = build(gpu, sizes, batch, in_dtype, 14, training=True, bias_scale=0.05)
+    g = so.rng(15)
+    x = g.random((batch, sizes[0]), dtype=np.float32)
+    mask = (g.random((batch, sizes[-1])) < 0.7).astype(np.uint8)
+    mask[:, 0] = 1
+    target = so.random_target(16, mask)
+    dx, dm, dt = gpu.to_storage(x, in_dtype), gpu.DeviceArray.from_numpy(mask), gpu.DeviceArray.from_numpy(target)
+    net.forward(dx, dm, head_flags=8)
+    net.backward(dx, dm, dt)
+    got = net.split_flat(net.grads.numpy())
+    _, _, loss, want = so.mlp_train_step(x, [so.round_input(w, in_dtype) for w in ws], bs, mask, target, 0.0,
+                                         in_dtype=in_dtype, act_dtype=in_dtype)
+    assert abs(float(net.loss.numpy()[0]) - loss) <= 2e-3 * abs(loss)
+    for i, ((gw, gb), (ww, wb)) in enumerate(zip(got, want)):
+        assert so.rel_frobenius(gw, ww) <= TOL, "dW of layer %d" % i
+        assert so.rel_frobenius(gb, wb) <= 5e-3, "db of layer %d" % i
+
+
 def test_train_step_updates_master_and_compute_weights(gpu):
     sizes, batch, lr = [32, 256, 256, 256, 3], 4096, 1e-3
     net, ws, bs = build(gpu, sizes, batch, "bf16", 6, training=True)
