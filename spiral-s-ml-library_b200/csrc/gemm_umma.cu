@@ -39,8 +39,9 @@ namespace {
 
 constexpr int UG_BLOCK_M = 128;
 // Epilogue warps per CTA (template parameter EW of the kernel): 8 = two warps per TMEM lane quadrant, the
-// general form; 16 = four per quadrant, for 16-bit outputs of CTA-pair tiles whose K is so short that the
-// launch is all epilogue (the head layer's dgrad, K = 16: 277 -> 242 us at 262144 rows).  A warp takes
+// general form; 16 = four per quadrant, for 16-bit outputs of CTA-pair tiles whose K is so short (at most
+// two k-blocks: the narrow nets' layers) that the launch is all epilogue; measured on a 262144 x 1024
+// output with K = 16: 277 -> 242 us.  A warp takes
 // every (EW / 4)-th 32-column chunk and owns a staging slot of 32 KB / EW.  Measured: with a real main
 // loop (K = 1024) sixteen warps are 4 % SLOWER than eight although the drain alone is 10 % faster -- the
 // MMA-issuing thread shares its scheduler with twice as many busy warps and the tensor pipe waits for it.
