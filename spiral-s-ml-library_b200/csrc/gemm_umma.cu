@@ -2,11 +2,12 @@
 // fused epilogue.  Replaces matmul_tf32_template (ml/matmul/kernel.spi:25-240,
 // nvcuda::wmma m16n16k8 TF32 with one-deep cuda::memcpy_async prefetch).
 //
-// Structure of one CTA (320 threads = 10 warps, persistent over output tiles):
-//   warp 0, lane 0 : TMA producer.  Per k-block it arms full[stage] with the
+// Structure of one CTA (352 threads = 11 warps, persistent over output tiles):
+//   warp 0, lane 0 : TMA producer of A.  Per k-block it arms full[stage] with the
 //                    stage's byte count and issues plain 2-D tiled TMA loads
-//                    (128-byte swizzle) of the A and B tiles; a stage holds one
-//                    or two 128-byte sub-blocks of K per operand.
+//                    (128-byte swizzle) of the A tile; a stage holds one or two
+//                    128-byte sub-blocks of K per operand.
+//   warp 10, lane 0: TMA producer of B (the same loop, the B tile's loads).
 //   warp 1, lane 0 : MMA issuer.  Waits full[stage], issues 4 or 8 tcgen05.mma
 //                    (M=128, or 256 for a CTA pair; N=block_n; 32 bytes of K
 //                    each) on shared-memory descriptors, commits to
@@ -47,7 +48,7 @@ constexpr int UG_BLOCK_M = 128;
 // MMA-issuing thread shares its scheduler with twice as many busy warps and the tensor pipe waits for it.
 constexpr int UG_EPI_WARPS = 8;
 constexpr int UG_EPI_WARPS_MAX = 16;
-constexpr int ug_threads(int ew) { return 64 + 32 * ew; }   // producer warp, MMA warp, epilogue warps
+constexpr int ug_threads(int ew) { return 96 + 32 * ew; }   // A-producer warp, MMA warp, epilogue warps, B-producer warp
 constexpr int UG_MAX_STAGES = 8;
 constexpr int UG_SMEM_LIMIT = 227 * 1024;
 constexpr int UG_MAX_PEERS = 8;         // ranks whose copies of C one launch can add its tiles to
@@ -911,7 +912,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   sb_grid_dependency_wait();
   sb_grid_dependents_launch();
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 2 + EW) {
+    // Two producer threads: warp 0 arms the stage's barrier and loads A, the last warp loads B.  One thread
+    // issuing all four loads of a stage measured 3 % slower on main-loop-bound GEMMs (4096^3: 1307 ->
+    // 1346 TFLOP/s): a TMA instruction occupies its thread for long enough to matter.  A load whose
+    // bytes land before the barrier is armed is in order: the transaction count may run negative.
+    const bool do_a = warp == 0, do_b = !do_a;
     if (lane == 0) {
       // The issue loop of a single thread: keep it to a handful of instructions
       // per k-block (addresses advance by adds, nothing is recomputed).
@@ -949,10 +955,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           // In a pair only the leader arms its full barrier, with the bytes of both CTAs.
-          if (!PAIR || leader) mbar_arrive_expect_tx(full0_local + 8u * (uint32_t)stage, tx_bytes);
+          if (do_a && (!PAIR || leader)) mbar_arrive_expect_tx(full0_local + 8u * (uint32_t)stage, tx_bytes);
           const uint32_t full = full0 + 8u * (uint32_t)stage;
           const uint32_t b_dst = a_dst + a_stage_bytes;
-          if (!a_mn) {
+          if (!do_a) {
+          } else if (!a_mn) {
             for (int s = 0; s < subs; ++s) {
               if (PAIR) tma_load_2d_pair(a_dst + (uint32_t)s * a_sub_bytes, &tmap_a, k0 + s * mn_box_elems, m0, full);
               else tma_load_2d(a_dst + (uint32_t)s * a_sub_bytes, &tmap_a, k0 + s * mn_box_elems, m0, full);
@@ -963,7 +970,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               else tma_load_2d(a_dst + (uint32_t)i * mn_box_bytes, &tmap_a, m0 + i * mn_box_elems, k0, full);
             }
           }
-          if (!b_mn) {
+          if (!do_b) {
+          } else if (!b_mn) {
             for (int s = 0; s < subs; ++s) {
               if (PAIR) tma_load_2d_pair(b_dst + (uint32_t)s * b_sub_bytes, map_b, k0 + s * mn_box_elems, n0, full);
               else tma_load_2d(b_dst + (uint32_t)s * b_sub_bytes, map_b, k0 + s * mn_box_elems, n0, full);
@@ -1055,7 +1063,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (acc == 0) acc_phase ^= 1u;
       }
     }
-  } else {
+  } else if (warp < 2 + EW) {
     // Epilogue warps.  A warp may only read the TMEM lane quadrant given by its index
     // modulo 4; with 8 warps the two warps of a quadrant take alternate 32-column chunks.
     const int quad = warp & 3;
@@ -1138,7 +1146,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // Teardown.  Bulk stores of the epilogue must have completed; after an expired wait, give copies and MMAs in flight time to
   // land before shared and tensor memory are released.  In a pair neither CTA
   // may leave while its peer can still touch its shared memory or barriers.
-  if (warp >= 2 && lane == 0) bulk_wait_group<0>();
+  if (warp >= 2 && warp < 2 + EW && lane == 0) bulk_wait_group<0>();
   __syncwarp();
   tc_fence_before_sync();
   if (PAIR) cluster_sync_all(); else __syncthreads();
