@@ -736,7 +736,7 @@ def leduc_infer_asymptote(sb, so, peaks):
 # that kernel is the tensor pipe; the figure shows that its operands are read from DRAM once.  The
 # algorithmic bytes of the same launch are computed for every batch (dominant_launch_bytes).
 NCU_TRAFFIC = {("holdem_train", 262144): {
-    "bytes": 4 * (136400128 + 100214528),
+    "bytes": 4 * (136450560 + 100710656),
     "source": "ncu capture of the hidden-layer training forward at 65536 rows (dram__bytes_read.sum + "
               "dram__bytes_write.sum), scaled x4 by the rows: profiles/umma_gemm_kernel_holdem_layer_fwd_bits.md"}}
 # NVIDIA's dense (no 2:4 sparsity) tensor peaks of one B200, TFLOP/s.
